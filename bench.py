@@ -1,0 +1,319 @@
+"""Benchmark of the HetuTable hot path: lookup+update keys/s (preprocess + push_pull with real gradients).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--config cfg2_hybrid] [--impl ours|reference]
+
+One process per GPU (under torchrun for N > 1).  A step = preprocess(keys of batch k) then
+push_pull(gradients of batch k-1, dst of batch k) on one batch of synthetic keys.  Prints ONE JSON line.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+from hetuctr_b200.workloads import CONFIGS, KeySampler, random_owners, storage_with_cache  # noqa: E402
+
+METRIC = "lookup+update keys/s"
+UNIT = "keys/s"
+N_BATCHES = 6  # distinct pre-generated batches / gradient buffers, cycled
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--config", default="cfg2_hybrid", choices=sorted(CONFIGS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=20)
+    ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work in the cpu_baseline sample")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_workload(cfg, nrank, rank):
+    c = CONFIGS[cfg]
+    sampler = KeySampler(c["rows"], c["fields"], c["alpha"], c["ratio"])
+    root = random_owners(c["rows"], nrank)
+    cache_rows = int(c["rows"] * c["cache"]) if nrank > 1 else 0
+    storage = storage_with_cache(root, rank, sampler, cache_rows)
+    cfg_id = int(cfg[3])
+    rng = np.random.RandomState(1000 * cfg_id + rank)
+    batches = [sampler.batch(c["samples"], rng) for _ in range(N_BATCHES)]
+    return c, root, storage, batches
+
+
+def algorithmic_bytes(c, st):
+    """Algorithmic HBM bytes per launch of the two row-moving kernels (D = 4*width bytes per row):
+       reduce+apply+pack : B*D (gradients) + 2*D per locally stored unique row + (D+16) per pushed row
+       expand            : D per unique row + B*D (dst) + 4*B (batch->unique map)"""
+    D = 4 * c["width"]
+    B, U = st["batch"], st["unique"]
+    Bp, Up, P = st["prev_batch"], st["prev_unique"], st["pushed_rows"]
+    return {"reduce": Bp * D + Up * 2 * D + P * (D + 16), "expand": U * D + B * D + 4 * B}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import hetuctr_b200 as hb
+
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    c, root, storage, batches = make_workload(args.config, world, rank)
+    W, B = c["width"], c["samples"] * c["fields"]
+    addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    port = int(os.environ.get("MASTER_PORT", 29500)) + 101
+    hb.lib().hctr_seed(0)
+    table = hb.Table(rank, world, local, addr, port, c["rows"], W, c["pull_bound"], c["push_bound"], root, storage,
+                     (hb.INIT_NORMAL, 0.0, c["init_std"]), c["lr"], 0)
+    keys_dev = [torch.from_numpy(b).to(dev) for b in batches]
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+    grads = [torch.randn(B, W, device=dev, generator=g) * 0.01 for _ in range(N_BATCHES)]
+    dst = torch.empty(B, W, device=dev)
+    stream = torch.cuda.ExternalStream(table.stream(), device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def step(i, host=False):
+        j = i % N_BATCHES
+        if host:
+            table.preprocess(keys_host[j], B)
+            table.push_pull(grads_host[(j - 1) % N_BATCHES], dst_host)
+        else:
+            table.preprocess(keys_dev[j], B)
+            table.push_pull(grads[(j - 1) % N_BATCHES], dst)
+
+    # prime the pipeline (the first push_pull has no previous batch), then warm up
+    table.preprocess(keys_dev[-1], B)
+    table.push_pull(None, dst)
+    for i in range(args.warmup):
+        step(i)
+
+    table.profile(True)
+    table.phase_times(reset=True)
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()
+    launches0 = hb.lib().hctr_launch_count()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        step(i)
+    e1.record(stream)
+    barrier()
+    wall = time.perf_counter() - t0
+    ms = e0.elapsed_time(e1)
+    launches = hb.lib().hctr_launch_count() - launches0
+    clk = clocks.stop() if rank == 0 else None
+    phases = table.phase_times(reset=True)
+    table.profile(False)
+    stats = table.stats()
+
+    # end to end through the same calls with HOST buffers: keys, gradients and dst live in pinned host
+    # memory; every step copies keys + gradients in and the pulled rows out
+    keys_host = [torch.from_numpy(b).pin_memory().numpy() for b in batches]
+    grads_host = [x.cpu().pin_memory() for x in grads[:3]] * 2
+    dst_host = torch.empty(B, W).pin_memory()
+    for i in range(3):
+        step(i, host=True)
+    barrier()
+    f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    f0.record(stream)
+    for i in range(args.e2e_steps):
+        step(i, host=True)
+    f1.record(stream)
+    barrier()
+    e2e_ms = f0.elapsed_time(f1)
+
+    t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, e2e_ms = t.tolist()
+
+    out = None
+    if rank == 0:
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except OSError:
+            pass
+        peak = peaks.get("hbm_gbs", 6650.0)
+        peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+        alg = algorithmic_bytes(c, stats)
+        per_phase = {p: (v[0] / v[1] if v[1] else 0.0) for p, v in phases.items()}
+        dom = max(("reduce", "expand"), key=lambda p: per_phase[p])
+        achieved = alg[dom] / (per_phase[dom] * 1e-3) / 1e9 if per_phase[dom] > 0 else 0.0
+        traffic = None
+        tfile = os.path.join(ROOT, "profiles", "traffic.json")
+        if os.path.exists(tfile):
+            tj = json.load(open(tfile))
+            key = f"{args.config}:n{world}:{dom}"
+            if key in tj:
+                traffic = tj[key]["bytes_per_launch"]
+        out = {
+            "metric": METRIC, "value": world * B * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.config, "rows": c["rows"], "width": W, "keys_per_gpu_per_step": B,
+                       "unique_per_gpu_per_step": stats["unique"], "key_distribution":
+                       "uniform" if c["alpha"] is None else f"zipf({c['alpha']}) per field, {c['fields']} fields",
+                       "cache_fraction": c["cache"] if world > 1 else 0.0, "pull_bound": c["pull_bound"],
+                       "push_bound": c["push_bound"], "lr": c["lr"], "partition": f"random owners x{world}",
+                       "l2": f"{N_BATCHES} rotating batches; >= {2 * B * 4 * W / 1e6:.0f} MB streamed per step exceeds the 126 MB L2"
+                       if 2 * B * 4 * W > 126e6 else f"{N_BATCHES} rotating batches (per-step data smaller than L2)",
+                       "transport": "none (1 rank)" if world == 1 else "nccl"},
+            "e2e": {"value": world * B * args.e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": B * 8 + B * W * 4, "d2h_bytes_per_step": B * W * 4,
+                    "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps},
+            "gpu_launches": int(launches),
+            "roofline": {"bound": "hbm", "kernel": {"reduce": "grad_reduce_apply_pack", "expand": "expand_rows"}[dom],
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_src, "algorithmic_bytes_per_launch": alg[dom],
+                         "avg_launch_ms": per_phase[dom], "traffic": traffic},
+            "phase_ms_per_step": {p: phases[p][0] / args.steps for p in phases},
+            "wall_ms_per_step": wall * 1e3 / args.steps,
+            "clocks": clk,
+        }
+        if not args.no_cpu_baseline:
+            out["cpu_baseline"] = cpu_baseline(args, world)
+    table.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    return out
+
+
+def cpu_baseline(args, world, seconds=None):
+    """The CPU port of the same semantics (oracle, OpenMP build) on the host cores: all `world` logical ranks in
+    one process, same table size and batches, a bounded number of steps."""
+    from oracle import build as obuild
+    from oracle.hetu_oracle import World
+
+    obuild.build()
+    seconds = seconds or args.cpu_seconds
+    works = [make_workload(args.config, world, r) for r in range(world)]
+    c = works[0][0]
+    W, B = c["width"], c["samples"] * c["fields"]
+    ow = World(world, c["rows"], W, c["pull_bound"], c["push_bound"], c["lr"], works[0][1], [w[2] for w in works],
+               parallel=True)
+    rng = np.random.RandomState(99)
+    grad = (rng.standard_normal((B, W)) * 0.01).astype(np.float32)
+    ow.preprocess([w[3][0] for w in works])
+    ow.push_pull(None)
+    t0 = time.perf_counter()
+    steps = 0
+    while steps < 3 or (time.perf_counter() - t0 < seconds and steps < 5000):
+        ow.preprocess([w[3][(steps + 1) % N_BATCHES] for w in works])
+        ow.push_pull([grad] * world)
+        steps += 1
+    dt = time.perf_counter() - t0
+    return {"value": world * B * steps / dt, "unit": UNIT, "cores": ow.num_threads(), "kind": "port",
+            "sample": f"{steps} steps of {args.config} ({world} logical rank(s) in one process, zero-initialised table, "
+                      f"{dt:.1f} s)"}
+
+
+def run_reference(args):
+    """Reference arm.  The reference is GPU-only (CUDA + NCCL + ZMQ); its CPU stand-in here is the port of its
+    semantics in oracle/ run with all host threads."""
+    rank = int(os.environ.get("RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if rank != 0:
+        return None
+    c = CONFIGS[args.config]
+    B = c["samples"] * c["fields"]
+    t0 = time.perf_counter()
+    # --steps/--warmup scale the sample: about 0.1 s of CPU work per requested step, 10-60 s in total
+    cb = cpu_baseline(args, world, seconds=min(60.0, max(10.0, 0.1 * args.steps)))
+    steps = int(cb["sample"].split(" steps")[0])
+    return {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": world,
+            "steps": steps, "warmup": 1, "ms_per_step": world * B / cb["value"] * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.config, "rows": c["rows"], "width": c["width"],
+                       "keys_per_gpu_per_step": B},
+            "cpu_baseline": cb,
+            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "total_s": time.perf_counter() - t0}
+
+
+def main():
+    args = parse_args()
+    out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    if out is not None:
+        print(json.dumps(out), flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,744 @@
+#include "core/hetu_table.h"
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <iostream>
+
+#include "core/transport.h"
+#include "hctr_kernels.h"
+#include "utils/errors.h"
+
+namespace hetuCTR {
+
+namespace {
+unsigned long g_seed = 0;
+
+template <class... Args>
+void info(const HetuTable &t, Args... args) {
+  if (t.verbose_ >= 1) {
+    std::cout << "HetuTable rank " << t.rank_ << ": ";
+    (void)std::initializer_list<int>{(std::cout << args, 0)...};
+    std::cout << std::endl;
+  }
+}
+
+size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+}  // namespace
+
+void set_seed(unsigned long seed) { g_seed = seed; }
+unsigned long get_seed() { return g_seed; }
+
+void DevBuf::ensure(size_t want) {
+  if (want <= bytes) return;
+  release();
+  // round to 256 B so every buffer base keeps 16-byte (and TMA-friendly) alignment
+  want = round_up(want, 256);
+  HCTR_CUDA(cudaMalloc(&p, want));
+  bytes = want;
+}
+
+void DevBuf::release() {
+  if (p) cudaFree(p);
+  p = nullptr;
+  bytes = 0;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Construction.  Same order as the reference (csrc/core/table_initialize.cu:116-164): device check,
+// communicator, table layout, value init, batch descriptors.
+// ------------------------------------------------------------------------------------------------
+HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const std::string &ip, const int port,
+                     const size_t embedding_length, const size_t embedding_width, const version_t pull_bound,
+                     const version_t push_bound, const worker_t *root_id_arr, const size_t root_id_len,
+                     const index_t *storage_id_arr, const size_t storage_id_len, const Initializer &init,
+                     const embed_t learning_rate, const int verbose)
+    : rank_(rank),
+      nrank_(nrank),
+      device_id_(device_id),
+      kEmbeddingIDMax(embedding_length),
+      kEmbeddingWidth(embedding_width),
+      kStorageMax(storage_id_len),
+      learning_rate_(learning_rate),
+      pull_bound_(pull_bound),
+      push_bound_(push_bound),
+      verbose_(verbose) {
+  HCTR_CHECK(nrank >= 1 && nrank <= 256, "nrank must be in [1, 256] (owner ids are one byte)");
+  HCTR_CHECK(rank >= 0 && rank < nrank, "rank out of range");
+  HCTR_CHECK(embedding_width >= 1, "width must be positive");
+  HCTR_CHECK(root_id_len == embedding_length, "root_arr must have `length` entries");
+  HCTR_CHECK(embedding_length < (size_t)1 << 40, "length too large");
+  HCTR_CHECK(storage_id_len < (size_t)1 << 31, "at most 2^31-1 rows can be stored per rank");
+  int num_gpus = 0;
+  HCTR_CUDA(cudaGetDeviceCount(&num_gpus));
+  HCTR_CHECK(device_id >= 0 && device_id < num_gpus, "InCorrect device number.");
+  HCTR_CUDA(cudaSetDevice(device_id_));
+  HCTR_CUDA(cudaStreamCreateWithFlags(&stream_main_, cudaStreamNonBlocking));
+
+  try {
+    initComm(ip, port);
+    info(*this, "communicator ready");
+    initTable(root_id_arr, storage_id_arr);
+
+    int kind;
+    switch (init.type) {
+      case InitType::kZero: kind = 0; break;
+      case InitType::kNormal: kind = 1; break;
+      case InitType::kUniform: kind = 2; break;
+      case InitType::kTruncatedNormal: kind = 3; break;
+      default: throw std::runtime_error("Unknown initializer.");
+    }
+    HCTR_LAUNCH(hctr_initialize(d_embedding_.as<float>(), kStorageMax * kEmbeddingWidth, kind, init.param.first,
+                                init.param.second, (unsigned int)g_seed, stream_main_));
+    HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+    info(*this, "Table Init Successfully");
+
+    for (BatchDesc *b : {&cur_batch_, &prev_batch_}) {
+      b->seg.assign(nrank_ + 1, 0);
+      b->query_send.assign(nrank_, 0);
+      b->query_recv.assign(nrank_, 0);
+      b->push_send.assign(nrank_, 0);
+      b->push_recv.assign(nrank_, 0);
+      b->ret_send.assign(nrank_, 0);
+      b->ret_recv.assign(nrank_, 0);
+      reserveBatch(*b, 1);
+    }
+    reserveShared(1);
+    h_pinned_words_ = HCTR_META_WORDS + (size_t)nrank_ + 1 + 8 * (size_t)nrank_ + 8;
+    HCTR_CUDA(cudaMallocHost(&h_pinned_, h_pinned_words_ * sizeof(uint32_t)));
+  } catch (...) {
+    releaseAll();
+    throw;
+  }
+}
+
+void HetuTable::initComm(const std::string &ip, int port) {
+  if (nrank_ == 1) return;  // a single-rank table has nobody to talk to
+  transport_ = make_transport(rank_, nrank_, ip, port, verbose_);
+}
+
+// csrc/core/table_initialize.cu:66-114 — owner array, storage layout (cached rows first, stable),
+// key -> row table, versions, pending gradient state.
+void HetuTable::initTable(const worker_t *root, const index_t *storage) {
+  const size_t N = kEmbeddingIDMax, S = kStorageMax, W = kEmbeddingWidth;
+  length_pad_ = round_up(std::max<size_t>(N, 1), HCTR_BLOCK_KEYS);
+  d_root_.ensure(std::max<size_t>(N, 1));
+  HCTR_CUDA(cudaMemcpyAsync(d_root_.p, root, N, cudaMemcpyHostToDevice, stream_main_));
+  d_row_of_.ensure(std::max<size_t>(N, 1) * sizeof(int32_t));
+  d_err_.ensure(256);
+  HCTR_CUDA(cudaMemsetAsync(d_err_.p, 0, 256, stream_main_));
+  uint32_t *err = d_err_.as<uint32_t>();
+  unsigned long long *owned_cnt = reinterpret_cast<unsigned long long *>(d_err_.as<char>() + 64);
+
+  DevBuf raw, flags, before, scratch;
+  raw.ensure(std::max<size_t>(S, 1) * sizeof(index_t));
+  flags.ensure((S + 1) * sizeof(uint32_t));
+  before.ensure((S + 1) * sizeof(uint32_t));
+  scratch.ensure(hctr_scan_scratch_words(S + 1) * sizeof(uint32_t));
+  d_stored_keys_.ensure(std::max<size_t>(S, 1) * sizeof(index_t));
+  HCTR_CUDA(cudaMemcpyAsync(raw.p, storage, S * sizeof(index_t), cudaMemcpyHostToDevice, stream_main_));
+  HCTR_LAUNCH(hctr_storage_flags(raw.as<int64_t>(), S, N, d_root_.as<uint8_t>(), rank_, flags.as<uint32_t>(), err,
+                                 stream_main_));
+  HCTR_LAUNCH(hctr_scan_exclusive_u32(flags.as<uint32_t>(), before.as<uint32_t>(), S, nullptr,
+                                      scratch.as<uint32_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_storage_layout(raw.as<int64_t>(), S, flags.as<uint32_t>(), before.as<uint32_t>(),
+                                  d_stored_keys_.as<int64_t>(), stream_main_));
+  uint32_t n_cached = 0;
+  HCTR_CUDA(cudaMemcpyAsync(&n_cached, before.as<uint32_t>() + S, sizeof(uint32_t), cudaMemcpyDeviceToHost,
+                            stream_main_));
+  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+  kNonLocalStorageMax = n_cached;
+
+  d_version_.ensure(std::max<size_t>(S, 1) * sizeof(version_t));
+  d_updates_.ensure(std::max<size_t>(kNonLocalStorageMax, 1) * sizeof(version_t));
+  d_embedding_.ensure(std::max<size_t>(S * W, 1) * sizeof(embed_t));
+  d_gradient_.ensure(std::max<size_t>(kNonLocalStorageMax * W, 1) * sizeof(embed_t));
+  HCTR_CUDA(cudaMemsetAsync(d_gradient_.p, 0, d_gradient_.bytes, stream_main_));
+  HCTR_CUDA(cudaMemsetAsync(d_updates_.p, 0, d_updates_.bytes, stream_main_));
+  HCTR_LAUNCH(hctr_table_build(d_stored_keys_.as<int64_t>(), S, kNonLocalStorageMax, N, d_row_of_.as<int32_t>(),
+                               d_version_.as<int64_t>(), err, stream_main_));
+  HCTR_LAUNCH(hctr_count_owned(d_root_.as<uint8_t>(), N, rank_, owned_cnt, stream_main_));
+  uint32_t h_err = 0;
+  unsigned long long h_owned = 0;
+  HCTR_CUDA(cudaMemcpyAsync(&h_err, err, sizeof(h_err), cudaMemcpyDeviceToHost, stream_main_));
+  HCTR_CUDA(cudaMemcpyAsync(&h_owned, owned_cnt, sizeof(h_owned), cudaMemcpyDeviceToHost, stream_main_));
+  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+  raw.release();
+  flags.release();
+  before.release();
+  scratch.release();
+  HCTR_CUDA(cudaMemsetAsync(d_err_.p, 0, 256, stream_main_));
+  HCTR_CHECK(!(h_err & HCTR_ERR_KEY_RANGE), "storage_arr holds a key outside [0, length)");
+  HCTR_CHECK(!(h_err & HCTR_ERR_CAPACITY), "storage_arr lists a key twice");
+  // The owner answers every query for its rows (csrc/core/handle_query.cu:12-15 asserts it), so a
+  // rank must store all rows it owns.
+  HCTR_CHECK(h_owned == S - kNonLocalStorageMax, "storage_arr must contain every key whose root_arr entry is this rank");
+
+  // dedupe scratch over the (owner, key) space: all-zero at rest
+  const size_t words = (size_t)nrank_ * length_pad_ / HCTR_WORD_BITS;
+  const size_t blocks = (size_t)nrank_ * length_pad_ / HCTR_BLOCK_KEYS;
+  d_bits_.ensure(words * sizeof(unsigned long long));
+  d_word_base_.ensure(words * sizeof(uint32_t));
+  d_blk_cnt_.ensure((blocks + 1) * sizeof(uint32_t));
+  d_blk_base_.ensure((blocks + 1) * sizeof(uint32_t));
+  HCTR_CUDA(cudaMemsetAsync(d_bits_.p, 0, d_bits_.bytes, stream_main_));
+  HCTR_CUDA(cudaMemsetAsync(d_blk_cnt_.p, 0, d_blk_cnt_.bytes, stream_main_));
+  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+}
+
+void HetuTable::reserveBatch(BatchDesc &b, size_t batch) {
+  if (batch <= b.capacity) return;
+  if (b.capacity) info(*this, "ReAllocate cuda memory for batch ", b.capacity, "->", batch);
+  HCTR_CHECK(batch < (size_t)1 << 31, "batch too large");
+  b.keys.ensure(batch * sizeof(index_t));
+  b.idx_map.ensure(batch * sizeof(int32_t));
+  b.sorted_pos.ensure(batch * sizeof(uint32_t));
+  b.uniq.ensure(batch * sizeof(index_t));
+  b.uniq_owner.ensure(batch);
+  b.uniq_row.ensure(batch * sizeof(int32_t));
+  b.cnt.ensure((batch + 1) * sizeof(uint32_t));
+  b.run_start.ensure((batch + 1) * sizeof(uint32_t));
+  b.meta.ensure((HCTR_META_WORDS + nrank_ + 1) * sizeof(uint32_t));
+  b.capacity = batch;
+}
+
+void HetuTable::reserveShared(size_t batch) {
+  if (batch <= shared_capacity_) return;
+  const size_t blocks = (size_t)nrank_ * length_pad_ / HCTR_BLOCK_KEYS;
+  // receive side of a step can hold up to batch keys from every rank
+  const size_t scan_n = std::max(blocks, batch * (size_t)nrank_) + 2;
+  d_scan_.ensure(hctr_scan_scratch_words(scan_n) * sizeof(uint32_t));
+  d_sk_.ensure(batch * sizeof(unsigned long long));
+  d_rank_.ensure(batch * sizeof(uint32_t));
+  d_heavy_.ensure((batch / 32 + 2) * sizeof(uint32_t));
+  d_need_push_.ensure((batch + 1) * sizeof(uint32_t));
+  d_push_slot_.ensure((batch + 1) * sizeof(uint32_t));
+  d_push_count_.ensure((size_t)nrank_ * sizeof(uint32_t));
+  if (nrank_ > 1) {
+    const size_t n = nrank_;
+    d_cnt_s_.ensure(2 * n * sizeof(uint32_t));
+    d_cnt_r_.ensure(2 * n * sizeof(uint32_t));
+    d_retcnt_s_.ensure(n * sizeof(uint32_t));
+    d_retcnt_r_.ensure(n * sizeof(uint32_t));
+    d_seg_r_.ensure((n + 1) * sizeof(uint32_t));
+    d_qver_s_.ensure(batch * sizeof(version_t));
+    d_pkey_s_.ensure(batch * sizeof(index_t));
+    d_pupd_s_.ensure(batch * sizeof(version_t));
+    d_pval_s_.ensure(batch * kEmbeddingWidth * sizeof(embed_t));
+    d_flag_r_.ensure(batch + 16);
+    d_recv_slot_.ensure((batch + 1) * sizeof(uint32_t));
+  }
+  shared_capacity_ = batch;
+}
+
+// ------------------------------------------------------------------------------------------------
+// preprocess — csrc/core/hetu_gpu_table.cu:43-65
+// ------------------------------------------------------------------------------------------------
+void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
+  HCTR_CUDA(cudaSetDevice(device_id_));
+  std::swap(cur_batch_, prev_batch_);
+  BatchDesc &cur = cur_batch_, &prev = prev_batch_;
+  reserveBatch(cur, std::max<size_t>(batch_size, 1));
+  reserveShared(std::max<size_t>(batch_size, 1));
+  cur.batch_size = batch_size;
+  const int n = nrank_;
+  const size_t meta_words = HCTR_META_WORDS + n + 1;
+
+  HCTR_CUDA(cudaMemcpyAsync(cur.keys.p, data_ptr, sizeof(index_t) * batch_size, cudaMemcpyDefault, stream_main_));
+  HCTR_CUDA(cudaMemsetAsync(cur.meta.p, 0, meta_words * sizeof(uint32_t), stream_main_));
+
+  hctr_dedupe_args a;
+  a.keys = cur.keys.as<int64_t>();
+  a.batch = batch_size;
+  a.length = kEmbeddingIDMax;
+  a.length_pad = length_pad_;
+  a.nrank = n;
+  a.owner_of = d_root_.as<uint8_t>();
+  a.row_of = d_row_of_.as<int32_t>();
+  a.bits = d_bits_.as<unsigned long long>();
+  a.blk_cnt = d_blk_cnt_.as<uint32_t>();
+  a.blk_base = d_blk_base_.as<uint32_t>();
+  a.word_base = d_word_base_.as<uint32_t>();
+  a.scan_scratch = d_scan_.as<uint32_t>();
+  a.sk = d_sk_.as<unsigned long long>();
+  a.rank_in_run = d_rank_.as<uint32_t>();
+  a.heavy_list = d_heavy_.as<uint32_t>();
+  a.uniq = cur.uniq.as<int64_t>();
+  a.uniq_owner = cur.uniq_owner.as<uint8_t>();
+  a.uniq_row = cur.uniq_row.as<int32_t>();
+  a.cnt = cur.cnt.as<uint32_t>();
+  a.run_start = cur.run_start.as<uint32_t>();
+  a.sorted_pos = cur.sorted_pos.as<uint32_t>();
+  a.idx_map = cur.idx_map.as<int32_t>();
+  a.meta = cur.meta.as<uint32_t>();
+  int sp = tic(kPhDedupe);
+  HCTR_LAUNCH(hctr_dedupe_map(&a, stream_main_));
+  toc(sp);
+
+  // Push decision for the previous batch (csrc/core/preprocess.cu:167-182).  With one rank every
+  // row is owned, nothing is ever pushed.
+  const bool decide = n > 1 && prev.unique_size > 0;
+  if (decide) {
+    sp = tic(kPhPushDecide);
+    HCTR_LAUNCH(hctr_push_decide(prev.meta.as<uint32_t>(), n, rank_, prev.unique_size, prev.uniq_owner.as<uint8_t>(),
+                                 prev.uniq_row.as<int32_t>(), prev.cnt.as<uint32_t>(), d_updates_.as<int64_t>(),
+                                 push_bound_, d_need_push_.as<uint32_t>(), d_push_slot_.as<uint32_t>(),
+                                 d_scan_.as<uint32_t>(), d_push_count_.as<uint32_t>(), stream_main_));
+    toc(sp);
+  }
+
+  uint32_t *h_meta = h_pinned_;
+  uint32_t *h_cnt_s = h_pinned_ + meta_words;
+  uint32_t *h_cnt_r = h_cnt_s + 2 * n;
+  HCTR_CUDA(cudaMemcpyAsync(h_meta, cur.meta.p, meta_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+  if (n > 1) {
+    // One packed count exchange instead of the reference's two all2allExchangeShape rounds
+    // (csrc/core/preprocess.cu:135,176): per peer {keys I will query, rows I will push}.
+    HCTR_LAUNCH(hctr_pack_counts(cur.meta.as<uint32_t>(), decide ? d_push_count_.as<uint32_t>() : nullptr, n,
+                                 d_cnt_s_.as<uint32_t>(), stream_main_));
+    std::vector<XferItem> items;
+    for (int p = 0; p < n; p++)
+      items.push_back({p, d_cnt_s_.as<uint32_t>() + 2 * p, 8, d_cnt_r_.as<uint32_t>() + 2 * p, 8});
+    sp = tic(kPhExchange);
+    transport_->exchange(items, stream_main_);
+    toc(sp);
+    HCTR_CUDA(cudaMemcpyAsync(h_cnt_s, d_cnt_s_.p, 2 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+    HCTR_CUDA(cudaMemcpyAsync(h_cnt_r, d_cnt_r_.p, 2 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+  }
+  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+  collectSpans();
+
+  cur.unique_size = h_meta[HCTR_META_UNIQUE];
+  for (int p = 0; p <= n; p++) cur.seg[p] = h_meta[HCTR_META_SEG + p];
+  for (int p = 0; p < n; p++) {
+    cur.query_send[p] = cur.seg[p + 1] - cur.seg[p];
+    cur.query_recv[p] = n > 1 ? h_cnt_r[2 * p] : cur.query_send[p];
+    prev.push_send[p] = n > 1 ? h_cnt_s[2 * p + 1] : 0;
+    prev.push_recv[p] = n > 1 ? h_cnt_r[2 * p + 1] : 0;
+  }
+  if (h_meta[HCTR_META_ERR] & HCTR_ERR_KEY_RANGE) {
+    // leave a consistent (empty) batch behind, then report
+    cur.batch_size = 0;
+    cur.unique_size = 0;
+    throw std::runtime_error("preprocess: a key is outside [0, length) or its root_arr entry is >= nrank");
+  }
+}
+
+const void *HetuTable::stageIn(const void *ptr, size_t bytes, DevBuf &buf) {
+  cudaPointerAttributes attr;
+  cudaError_t e = cudaPointerGetAttributes(&attr, ptr);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    attr.type = cudaMemoryTypeUnregistered;
+  }
+  if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) return ptr;
+  buf.ensure(bytes);
+  HCTR_CUDA(cudaMemcpyAsync(buf.p, ptr, bytes, cudaMemcpyHostToDevice, stream_main_));
+  return buf.p;
+}
+
+// ------------------------------------------------------------------------------------------------
+// pushPull — csrc/core/hetu_gpu_table.cu:9-41
+// ------------------------------------------------------------------------------------------------
+void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
+  HCTR_CUDA(cudaSetDevice(device_id_));
+  BatchDesc &cur = cur_batch_, &prev = prev_batch_;
+  const int n = nrank_;
+  const size_t W = kEmbeddingWidth;
+
+  // No gradient = inference step: the previous batch is dropped (all ranks must do this together).
+  if (grad == nullptr) {
+    prev.batch_size = 0;
+    prev.unique_size = 0;
+    std::fill(prev.push_send.begin(), prev.push_send.end(), 0);
+    std::fill(prev.push_recv.begin(), prev.push_recv.end(), 0);
+  }
+
+  // dst (and grad) are normally device memory; host buffers are staged
+  embed_t *dst_dev = dst;
+  bool dst_staged = false;
+  if (cur.batch_size > 0) {
+    cudaPointerAttributes attr;
+    cudaError_t e = cudaPointerGetAttributes(&attr, dst);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      attr.type = cudaMemoryTypeUnregistered;
+    }
+    if (!(attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged)) {
+      d_stage_dst_.ensure(cur.batch_size * W * sizeof(embed_t));
+      dst_dev = d_stage_dst_.as<embed_t>();
+      dst_staged = true;
+    }
+  }
+  const embed_t *grad_dev = grad;
+  if (grad != nullptr && prev.batch_size > 0)
+    grad_dev = static_cast<const embed_t *>(stageIn(grad, prev.batch_size * W * sizeof(embed_t), d_stage_grad_));
+
+  size_t pushed = 0, push_recv = 0, q_recv = 0;
+  for (int p = 0; p < n; p++) {
+    pushed += prev.push_send[p];
+    push_recv += prev.push_recv[p];
+    q_recv += cur.query_recv[p];
+  }
+  stats_ = StepStats();
+  stats_.batch = cur.batch_size;
+  stats_.unique = cur.unique_size;
+  stats_.prev_batch = prev.batch_size;
+  stats_.prev_unique = prev.unique_size;
+  stats_.pushed_rows = pushed;
+  stats_.received_push_rows = push_recv;
+  stats_.queried_keys = q_recv;
+
+  // A. duplicate-gradient reduction + local apply + pack (generateGradient)
+  if (prev.unique_size > 0) {
+    hctr_reduce_args r;
+    r.n_unique = prev.unique_size;
+    r.width = W;
+    r.n_cached = kNonLocalStorageMax;
+    r.neg_lr = -learning_rate_;
+    r.grad = grad_dev;
+    r.run_start = prev.run_start.as<uint32_t>();
+    r.sorted_pos = prev.sorted_pos.as<uint32_t>();
+    r.uniq = prev.uniq.as<int64_t>();
+    r.uniq_row = prev.uniq_row.as<int32_t>();
+    r.need_push = n > 1 ? d_need_push_.as<uint32_t>() : nullptr;
+    r.push_slot = n > 1 ? d_push_slot_.as<uint32_t>() : nullptr;
+    r.embedding = d_embedding_.as<float>();
+    r.version = d_version_.as<int64_t>();
+    r.pending = d_gradient_.as<float>();
+    r.pending_cnt = d_updates_.as<int64_t>();
+    r.push_key = d_pkey_s_.as<int64_t>();
+    r.push_updates = d_pupd_s_.as<int64_t>();
+    r.push_val = d_pval_s_.as<float>();
+    int sp = tic(kPhReduce);
+    HCTR_LAUNCH(hctr_grad_reduce_apply_pack(&r, stream_main_));
+    toc(sp);
+  }
+
+  if (n == 1) {
+    // Single rank: every key is owned and stored here; the pull is a local gather.
+    int sp = tic(kPhExpand);
+    HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.idx_map.as<int32_t>(), cur.uniq_row.as<int32_t>(), nullptr,
+                                 nullptr, d_embedding_.as<float>(), dst_dev, stream_main_));
+    toc(sp);
+  } else {
+    const size_t U = cur.unique_size;
+    // B. query = (key, local version) for every unique key (generateQuery)
+    int sp = tic(kPhQuery);
+    HCTR_LAUNCH(hctr_query_versions(U, cur.uniq_row.as<int32_t>(), d_version_.as<int64_t>(),
+                                    d_qver_s_.as<int64_t>(), stream_main_));
+    toc(sp);
+
+    // exchange 1 (keys + versions) and exchange 3 (pushed ids, update counts, rows) in ONE group
+    d_qkey_r_.ensure(std::max<size_t>(q_recv, 1) * sizeof(index_t));
+    d_qver_r_.ensure(std::max<size_t>(q_recv, 1) * sizeof(version_t));
+    d_pkey_r_.ensure(std::max<size_t>(push_recv, 1) * sizeof(index_t));
+    d_pupd_r_.ensure(std::max<size_t>(push_recv, 1) * sizeof(version_t));
+    d_pval_r_.ensure(std::max<size_t>(push_recv * W, 1) * sizeof(embed_t));
+    d_flag_s_.ensure(q_recv + 16);
+    d_flag32_.ensure((std::max(q_recv, U) + 1) * sizeof(uint32_t));
+    d_ret_slot_.ensure((q_recv + 1) * sizeof(uint32_t));
+    {
+      size_t so = 0, ro = 0, pso = 0, pro = 0;
+      std::vector<XferItem> items;
+      for (int p = 0; p < n; p++) {
+        const size_t qs = cur.query_send[p], qr = cur.query_recv[p];
+        const size_t ps = prev.push_send[p], pr = prev.push_recv[p];
+        items.push_back({p, cur.uniq.as<int64_t>() + so, qs * 8, d_qkey_r_.as<int64_t>() + ro, qr * 8});
+        items.push_back({p, d_qver_s_.as<int64_t>() + so, qs * 8, d_qver_r_.as<int64_t>() + ro, qr * 8});
+        items.push_back({p, d_pkey_s_.as<int64_t>() + pso, ps * 8, d_pkey_r_.as<int64_t>() + pro, pr * 8});
+        items.push_back({p, d_pupd_s_.as<int64_t>() + pso, ps * 8, d_pupd_r_.as<int64_t>() + pro, pr * 8});
+        items.push_back({p, d_pval_s_.as<float>() + pso * W, ps * W * 4, d_pval_r_.as<float>() + pro * W, pr * W * 4});
+        so += qs;
+        ro += qr;
+        pso += ps;
+        pro += pr;
+      }
+      sp = tic(kPhExchange);
+      transport_->exchange(items, stream_main_);
+      toc(sp);
+    }
+
+    // C. owner applies pushed rows, one source after the other (handleGradient)
+    {
+      sp = tic(kPhOwnerUpdate);
+      size_t off = 0;
+      for (int p = 0; p < n; p++) {
+        const size_t c = prev.push_recv[p];
+        HCTR_LAUNCH(hctr_owner_update(c, W, d_pkey_r_.as<int64_t>() + off, d_pupd_r_.as<int64_t>() + off,
+                                      d_pval_r_.as<float>() + off * W, d_row_of_.as<int32_t>(), kEmbeddingIDMax,
+                                      kNonLocalStorageMax, d_embedding_.as<float>(), d_version_.as<int64_t>(),
+                                      d_err_.as<uint32_t>(), stream_main_));
+        off += c;
+      }
+      toc(sp);
+    }
+
+    // D. owner decides staleness, counts per requester, gathers rows (handleQuery)
+    uint32_t *h_seg = h_pinned_ + HCTR_META_WORDS + n + 1 + 4 * n;  // [n+1] receive-side segment starts
+    {
+      size_t acc = 0;
+      for (int p = 0; p <= n; p++) {
+        h_seg[p] = (uint32_t)acc;
+        if (p < n) acc += cur.query_recv[p];
+      }
+    }
+    HCTR_CUDA(cudaMemcpyAsync(d_seg_r_.p, h_seg, (n + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_main_));
+    sp = tic(kPhStaleGather);
+    HCTR_LAUNCH(hctr_stale_check(q_recv, n, rank_, d_seg_r_.as<uint32_t>(), d_qkey_r_.as<int64_t>(),
+                                 d_qver_r_.as<int64_t>(), d_row_of_.as<int32_t>(), kEmbeddingIDMax,
+                                 kNonLocalStorageMax, d_version_.as<int64_t>(), pull_bound_, d_flag_s_.as<uint8_t>(),
+                                 d_flag32_.as<uint32_t>(), d_ret_slot_.as<uint32_t>(), d_scan_.as<uint32_t>(),
+                                 d_retcnt_s_.as<uint32_t>(), d_err_.as<uint32_t>(), stream_main_));
+    // the number of rows to return is only known on the device; the return buffer is sized for the
+    // worst case (every queried key stale)
+    d_rver_s_.ensure(std::max<size_t>(q_recv, 1) * sizeof(version_t));
+    d_rval_s_.ensure(std::max<size_t>(q_recv * W, 1) * sizeof(embed_t));
+    HCTR_LAUNCH(hctr_gather_rows(q_recv, W, d_qkey_r_.as<int64_t>(), d_flag_s_.as<uint8_t>(),
+                                 d_ret_slot_.as<uint32_t>(), d_row_of_.as<int32_t>(), d_embedding_.as<float>(),
+                                 d_version_.as<int64_t>(), d_rval_s_.as<float>(), d_rver_s_.as<int64_t>(),
+                                 stream_main_));
+    toc(sp);
+
+    // flags travel back along the query route (one byte per key instead of the reference's int64,
+    // csrc/core/all2all.cu:89-101) together with the per-requester row counts
+    {
+      size_t so = 0, ro = 0;
+      std::vector<XferItem> items;
+      for (int p = 0; p < n; p++) {
+        const size_t qs = cur.query_send[p], qr = cur.query_recv[p];
+        items.push_back({p, d_flag_s_.as<uint8_t>() + ro, qr, d_flag_r_.as<uint8_t>() + so, qs});
+        items.push_back({p, d_retcnt_s_.as<uint32_t>() + p, 4, d_retcnt_r_.as<uint32_t>() + p, 4});
+        so += qs;
+        ro += qr;
+      }
+      sp = tic(kPhExchange);
+      transport_->exchange(items, stream_main_);
+      toc(sp);
+    }
+    uint32_t *h_ret_s = h_pinned_ + HCTR_META_WORDS + n + 1 + 5 * n + 1;
+    uint32_t *h_ret_r = h_ret_s + n;
+    uint32_t *h_err = h_ret_r + n;
+    HCTR_CUDA(cudaMemcpyAsync(h_ret_s, d_retcnt_s_.p, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+    HCTR_CUDA(cudaMemcpyAsync(h_ret_r, d_retcnt_r_.p, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+    HCTR_CUDA(cudaMemcpyAsync(h_err, d_err_.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+    // meanwhile: slots of the rows this rank will receive (scan of the flags it got back)
+    sp = tic(kPhRefresh);
+    HCTR_LAUNCH(hctr_recv_slots(U, d_flag_r_.as<uint8_t>(), d_flag32_.as<uint32_t>(), d_recv_slot_.as<uint32_t>(),
+                                d_scan_.as<uint32_t>(), stream_main_));
+    toc(sp);
+    HCTR_CUDA(cudaStreamSynchronize(stream_main_));  // the one mid-step host sync: NCCL needs the row counts
+
+    if (*h_err) {
+      HCTR_CUDA(cudaMemsetAsync(d_err_.p, 0, sizeof(uint32_t), stream_main_));
+      // keep the collective pattern intact on every rank, then report
+    }
+    size_t ret_total = 0, recv_total = 0;
+    for (int p = 0; p < n; p++) {
+      cur.ret_send[p] = h_ret_s[p];
+      cur.ret_recv[p] = h_ret_r[p];
+      ret_total += h_ret_s[p];
+      recv_total += h_ret_r[p];
+    }
+    stats_.returned_rows = ret_total;
+    stats_.received_rows = recv_total;
+    info(*this, "Total gradient update receive/push = ", push_recv, "/", pushed);
+    info(*this, "Total embedding fetching serve/query = ", ret_total, "/", recv_total);
+
+    // exchange 2: versions + rows of the stale keys (all2allReturnValue)
+    d_rver_r_.ensure(std::max<size_t>(recv_total, 1) * sizeof(version_t));
+    d_rval_r_.ensure(std::max<size_t>(recv_total * W, 1) * sizeof(embed_t));
+    {
+      size_t so = 0, ro = 0;
+      std::vector<XferItem> items;
+      for (int p = 0; p < n; p++) {
+        const size_t sn = cur.ret_send[p], rn = cur.ret_recv[p];
+        items.push_back({p, d_rver_s_.as<int64_t>() + so, sn * 8, d_rver_r_.as<int64_t>() + ro, rn * 8});
+        items.push_back({p, d_rval_s_.as<float>() + so * W, sn * W * 4, d_rval_r_.as<float>() + ro * W, rn * W * 4});
+        so += sn;
+        ro += rn;
+      }
+      sp = tic(kPhExchange);
+      transport_->exchange(items, stream_main_);
+      toc(sp);
+    }
+
+    // E. requester: refresh cached replicas, expand to batch order (writeBack)
+    sp = tic(kPhRefresh);
+    HCTR_LAUNCH(hctr_cache_refresh(U, W, d_flag_r_.as<uint8_t>(), d_recv_slot_.as<uint32_t>(),
+                                   cur.uniq_row.as<int32_t>(), d_rval_r_.as<float>(), d_rver_r_.as<int64_t>(),
+                                   d_gradient_.as<float>(), d_embedding_.as<float>(), d_version_.as<int64_t>(),
+                                   stream_main_));
+    toc(sp);
+    sp = tic(kPhExpand);
+    HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.idx_map.as<int32_t>(), cur.uniq_row.as<int32_t>(),
+                                 d_recv_slot_.as<uint32_t>(), d_rval_r_.as<float>(), d_embedding_.as<float>(), dst_dev,
+                                 stream_main_));
+    toc(sp);
+    if (*h_err) {
+      HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+      throw std::runtime_error("push_pull: a peer addressed a key to a rank that does not own it (root_arr differs between ranks?)");
+    }
+  }
+
+  if (dst_staged)
+    HCTR_CUDA(cudaMemcpyAsync(dst, dst_dev, cur.batch_size * W * sizeof(embed_t), cudaMemcpyDeviceToHost, stream_main_));
+  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+  collectSpans();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Profiling spans
+// ------------------------------------------------------------------------------------------------
+void HetuTable::setProfile(bool on) { profile_ = on; }
+
+int HetuTable::tic(int phase) {
+  if (!profile_) return -1;
+  if (spans_used_ == spans_.size()) {
+    Span s{phase, nullptr, nullptr};
+    HCTR_CUDA(cudaEventCreate(&s.a));
+    HCTR_CUDA(cudaEventCreate(&s.b));
+    spans_.push_back(s);
+  }
+  Span &s = spans_[spans_used_];
+  s.phase = phase;
+  HCTR_CUDA(cudaEventRecord(s.a, stream_main_));
+  return (int)spans_used_++;
+}
+
+void HetuTable::toc(int span) {
+  if (span < 0) return;
+  HCTR_CUDA(cudaEventRecord(spans_[span].b, stream_main_));
+}
+
+// call only after the stream has been synchronised
+void HetuTable::collectSpans() {
+  for (size_t i = 0; i < spans_used_; i++) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, spans_[i].a, spans_[i].b) == cudaSuccess) {
+      phase_ms_[spans_[i].phase] += ms;
+      phase_calls_[spans_[i].phase]++;
+    } else {
+      cudaGetLastError();
+    }
+  }
+  spans_used_ = 0;
+}
+
+void HetuTable::phaseTimes(double ms[kPhCount], long long calls[kPhCount], bool reset) {
+  for (int i = 0; i < kPhCount; i++) {
+    ms[i] = phase_ms_[i];
+    calls[i] = phase_calls_[i];
+    if (reset) phase_ms_[i] = 0, phase_calls_[i] = 0;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Introspection
+// ------------------------------------------------------------------------------------------------
+namespace {
+template <class T>
+long long copy_widen(const void *dev, size_t n, void *out, cudaStream_t s) {
+  if (!out) return (long long)n;
+  std::vector<T> tmp(n);
+  if (n) {
+    HCTR_CUDA(cudaMemcpyAsync(tmp.data(), dev, n * sizeof(T), cudaMemcpyDeviceToHost, s));
+    HCTR_CUDA(cudaStreamSynchronize(s));
+  }
+  long long *o = static_cast<long long *>(out);
+  for (size_t i = 0; i < n; i++) o[i] = (long long)tmp[i];
+  return (long long)n;
+}
+long long copy_sizes(const std::vector<size_t> &v, size_t n, void *out) {
+  if (out)
+    for (size_t i = 0; i < n; i++) static_cast<long long *>(out)[i] = (long long)v[i];
+  return (long long)n;
+}
+}  // namespace
+
+long long HetuTable::dump(const std::string &what, bool prev, void *out) {
+  HCTR_CUDA(cudaSetDevice(device_id_));
+  BatchDesc &b = prev ? prev_batch_ : cur_batch_;
+  const size_t B = b.batch_size, U = b.unique_size;
+  cudaStream_t s = stream_main_;
+  if (what == "unique_idx") return copy_widen<long long>(b.uniq.p, U, out, s);
+  if (what == "idx_map") return copy_widen<int32_t>(b.idx_map.p, B, out, s);
+  if (what == "sorted_arg") return copy_widen<uint32_t>(b.sorted_pos.p, B, out, s);
+  if (what == "run_length") return copy_widen<uint32_t>(b.run_start.p, B ? U + 1 : 1, out, s);
+  if (what == "root") return copy_widen<uint8_t>(b.uniq_owner.p, U, out, s);
+  if (what == "offset") return copy_widen<int32_t>(b.uniq_row.p, U, out, s);
+  if (what == "shape") return copy_sizes(b.query_send, nrank_, out);
+  if (what == "shape_exchanged") return copy_sizes(b.query_recv, nrank_, out);
+  if (what == "push_shape") return copy_sizes(b.push_send, nrank_, out);
+  if (what == "push_shape_exchanged") return copy_sizes(b.push_recv, nrank_, out);
+  if (what == "return_shape") return copy_sizes(b.ret_send, nrank_, out);
+  if (what == "return_shape_exchanged") return copy_sizes(b.ret_recv, nrank_, out);
+  if (what == "need_update") return copy_widen<uint32_t>(d_need_push_.p, prev_batch_.unique_size, out, s);
+  if (what == "version") return copy_widen<long long>(d_version_.p, kStorageMax, out, s);
+  if (what == "updates") return copy_widen<long long>(d_updates_.p, kNonLocalStorageMax, out, s);
+  if (what == "stored_keys") return copy_widen<long long>(d_stored_keys_.p, kStorageMax, out, s);
+  if (what == "embedding" || what == "gradient") {
+    const size_t n = (what == "embedding" ? kStorageMax : kNonLocalStorageMax) * kEmbeddingWidth;
+    if (out && n) {
+      HCTR_CUDA(cudaMemcpyAsync(out, what == "embedding" ? d_embedding_.p : d_gradient_.p, n * sizeof(embed_t),
+                                cudaMemcpyDeviceToHost, s));
+      HCTR_CUDA(cudaStreamSynchronize(s));
+    }
+    return (long long)n;
+  }
+  throw std::runtime_error("dump: unknown array " + what);
+}
+
+void HetuTable::setEmbedding(const embed_t *host_rows) {
+  HCTR_CUDA(cudaSetDevice(device_id_));
+  HCTR_CUDA(cudaMemcpyAsync(d_embedding_.p, host_rows, kStorageMax * kEmbeddingWidth * sizeof(embed_t),
+                            cudaMemcpyHostToDevice, stream_main_));
+  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+}
+
+// csrc/core/debug.cu:5-24 — same text formats
+std::string HetuTable::debugString() {
+  char buffer[1024];
+  std::snprintf(buffer, sizeof(buffer), "<HetuTable root/store/all=%ld/%ld/%ld>",
+                (long)(kStorageMax - kNonLocalStorageMax), (long)kStorageMax, (long)kEmbeddingIDMax);
+  return buffer;
+}
+
+std::string HetuTable::debugStringFull() {
+  char buffer[1024];
+  std::snprintf(buffer, sizeof(buffer),
+                "<HetuTable root/store/all=%ld/%ld/%ld rank=%d nrank=%d device_id=%d width=%ld push/pull=%lld/%lld>",
+                (long)(kStorageMax - kNonLocalStorageMax), (long)kStorageMax, (long)kEmbeddingIDMax, rank_, nrank_,
+                device_id_, (long)kEmbeddingWidth, push_bound_, pull_bound_);
+  return buffer;
+}
+
+HetuTable::~HetuTable() { releaseAll(); }
+
+void HetuTable::releaseAll() {
+  cudaSetDevice(device_id_);
+  if (stream_main_) cudaStreamSynchronize(stream_main_);
+  transport_.reset();
+  DevBuf *all[] = {&d_embedding_, &d_gradient_, &d_updates_, &d_version_, &d_root_, &d_row_of_, &d_stored_keys_,
+                   &d_bits_, &d_blk_cnt_, &d_blk_base_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_heavy_,
+                   &d_need_push_, &d_push_slot_, &d_push_count_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
+                   &d_qkey_r_, &d_qver_r_, &d_pkey_s_, &d_pupd_s_, &d_pval_s_, &d_pkey_r_, &d_pupd_r_, &d_pval_r_,
+                   &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,
+                   &d_retcnt_r_, &d_rver_s_, &d_rval_s_, &d_rver_r_, &d_rval_r_, &d_stage_grad_, &d_stage_dst_};
+  for (DevBuf *b : all) b->release();
+  for (BatchDesc *b : {&cur_batch_, &prev_batch_})
+    for (DevBuf *d : {&b->keys, &b->idx_map, &b->sorted_pos, &b->uniq, &b->uniq_owner, &b->uniq_row, &b->cnt,
+                      &b->run_start, &b->meta})
+      d->release();
+  for (Span &sp : spans_) {
+    cudaEventDestroy(sp.a);
+    cudaEventDestroy(sp.b);
+  }
+  spans_.clear();
+  if (h_pinned_) cudaFreeHost(h_pinned_);
+  h_pinned_ = nullptr;
+  if (stream_main_) cudaStreamDestroy(stream_main_);
+  stream_main_ = nullptr;
+}
+
+}  // namespace hetuCTR

@@ -1,0 +1,179 @@
+// HetuTable: one rank of a distributed GPU embedding table (host orchestration).
+//
+// Mirrors the reference's class of the same name (csrc/core/hetu_gpu_table.h:21-145): same
+// constructor arguments, same preprocess()/pushPull() call pattern and semantics, one table per
+// process/GPU.  The implementation underneath is new: all GPU work goes through the C-ABI launchers
+// of hctr_kernels.h, the key->row map is a dense array instead of a managed-memory hash map, and the
+// exchanges are packed into three NCCL groups per step with one mid-step host synchronisation.
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <limits>
+#include <memory>
+#include <string>
+#include <utility>
+#include <vector>
+
+namespace hetuCTR {
+
+class Transport;
+
+// csrc/core/types.h:12-28
+typedef float embed_t;
+typedef long long version_t;
+typedef long long index_t;
+typedef unsigned char worker_t;
+const index_t kInvalidIndex = -1;
+const version_t kInvalidVersion = std::numeric_limits<version_t>::min();
+
+// csrc/utils/initializer.h:8-25
+enum class InitType { kZero, kNormal, kUniform, kTruncatedNormal, kNone };
+struct Initializer {
+  Initializer(InitType _type, float a, float b) : type(_type), param(a, b) {}
+  InitType type;
+  std::pair<float, float> param;  // (mean, stddev) or (a, b)
+};
+
+// Process-wide seed used by tables constructed afterwards (hetuCTR.seed, csrc/pybind/pybind.cu:77).
+void set_seed(unsigned long seed);
+unsigned long get_seed();
+
+// Growable device allocation.
+struct DevBuf {
+  void *p = nullptr;
+  size_t bytes = 0;
+  void ensure(size_t want);  // grows (contents are NOT preserved); never shrinks
+  void release();
+  template <class T>
+  T *as() const { return static_cast<T *>(p); }
+};
+
+// Device-side description of one preprocessed batch (the reference's PreprocessData,
+// csrc/core/preprocess_struct.h:7-24, with 32-bit indices).
+struct BatchDesc {
+  size_t batch_size = 0;
+  size_t unique_size = 0;
+  size_t capacity = 0;
+  DevBuf keys, idx_map, sorted_pos, uniq, uniq_owner, uniq_row, cnt, run_start, meta;
+  std::vector<size_t> seg;         // [n+1] first unique of each owner
+  std::vector<size_t> query_send;  // [n] unique keys addressed to each owner
+  std::vector<size_t> query_recv;  // [n] keys each requester sends to me
+  std::vector<size_t> push_send;   // [n] rows of this batch's gradient pushed to each owner
+  std::vector<size_t> push_recv;   // [n]
+  std::vector<size_t> ret_send;    // [n] rows I return to each requester
+  std::vector<size_t> ret_recv;    // [n] rows each owner returns to me
+};
+
+struct StepStats {  // sizes of the last push_pull, for roofline arithmetic
+  size_t batch = 0, unique = 0, prev_batch = 0, prev_unique = 0;
+  size_t pushed_rows = 0, received_push_rows = 0, queried_keys = 0, returned_rows = 0, received_rows = 0;
+};
+
+// Phases timed with CUDA events on the table's stream when profiling is enabled.
+enum Phase {
+  kPhDedupe = 0,      // hctr_dedupe_map
+  kPhPushDecide,      // hctr_push_decide
+  kPhReduce,          // hctr_grad_reduce_apply_pack
+  kPhQuery,           // hctr_query_versions
+  kPhExchange,        // transport groups (all of a step)
+  kPhOwnerUpdate,     // hctr_owner_update (all sources)
+  kPhStaleGather,     // hctr_stale_check + hctr_gather_rows
+  kPhRefresh,         // hctr_recv_slots + hctr_cache_refresh
+  kPhExpand,          // hctr_expand_rows
+  kPhCount
+};
+
+class HetuTable {
+ public:
+  const int rank_;
+  const int nrank_;
+  const int device_id_;
+  const size_t kEmbeddingIDMax;
+  const size_t kEmbeddingWidth;
+  const size_t kStorageMax;
+  size_t kNonLocalStorageMax = 0;
+  const embed_t learning_rate_;
+  const version_t pull_bound_, push_bound_;
+  int verbose_;
+
+  HetuTable(const int rank, const int nrank, const int device_id, const std::string &ip, const int port,
+            const size_t embedding_length, const size_t embedding_width, const version_t pull_bound,
+            const version_t push_bound, const worker_t *root_id_arr, const size_t root_id_len,
+            const index_t *storage_id_arr, const size_t storage_id_len, const Initializer &init,
+            const embed_t learning_rate, const int verbose);
+  HetuTable(const HetuTable &) = delete;
+  HetuTable &operator=(const HetuTable &) = delete;
+  ~HetuTable();
+
+  // csrc/core/hetu_gpu_table.h:127-141.  data_ptr: host or device memory; grad/dst: device memory
+  // (host memory is also accepted and staged).  Both calls return after the stream has drained.
+  void preprocess(index_t *data_ptr, size_t batch_size);
+  void pushPull(embed_t *grad, embed_t *dst);
+
+  std::string debugString();
+  std::string debugStringFull();
+
+  // ---- extensions used by tests, benchmarks and tools -----------------------------------------
+  // Copies a named internal array to host memory as int64 (or float for "embedding"/"gradient");
+  // returns the element count; out may be null to query the size.  Names follow the reference's
+  // members: unique_idx, idx_map, sorted_arg, run_length, root, offset, shape, shape_exchanged,
+  // version, updates, stored_keys, need_update; prev selects the previous batch descriptor.
+  long long dump(const std::string &what, bool prev, void *out);
+  // Overwrites the local rows (local row order) from host memory.
+  void setEmbedding(const embed_t *host_rows);
+  const StepStats &stats() const { return stats_; }
+  // Per-phase device time.  While enabled, every phase is bracketed by two events on the table's
+  // stream; times are summed when the call that recorded them has drained the stream.
+  void setProfile(bool on);
+  void phaseTimes(double ms[kPhCount], long long calls[kPhCount], bool reset);
+  cudaStream_t stream() const { return stream_main_; }
+
+ private:
+  void initComm(const std::string &ip, int port);
+  void initTable(const worker_t *root, const index_t *storage);
+  void reserveBatch(BatchDesc &b, size_t batch);
+  void reserveShared(size_t batch);
+  void exchangeCounts();
+  void releaseAll();
+  const void *stageIn(const void *ptr, size_t bytes, DevBuf &buf);
+
+  cudaStream_t stream_main_ = nullptr;
+  std::unique_ptr<Transport> transport_;
+
+  // table state
+  DevBuf d_embedding_, d_gradient_, d_updates_, d_version_, d_root_, d_row_of_, d_stored_keys_;
+  size_t length_pad_ = 0;
+
+  // dedupe scratch (persistent, all-zero between calls) and per-step scratch
+  DevBuf d_bits_, d_blk_cnt_, d_blk_base_, d_word_base_, d_scan_, d_sk_, d_rank_, d_heavy_;
+  DevBuf d_need_push_, d_push_slot_, d_push_count_, d_err_;
+  size_t shared_capacity_ = 0;
+
+  // exchange buffers: *_s = send side, *_r = receive side
+  DevBuf d_cnt_s_, d_cnt_r_;                      // packed per-peer counts
+  DevBuf d_qver_s_, d_qkey_r_, d_qver_r_;         // query (keys are sent straight from the batch)
+  DevBuf d_pkey_s_, d_pupd_s_, d_pval_s_, d_pkey_r_, d_pupd_r_, d_pval_r_;  // pushed gradients
+  DevBuf d_flag_s_, d_flag_r_, d_flag32_, d_ret_slot_, d_recv_slot_, d_seg_r_;
+  DevBuf d_retcnt_s_, d_retcnt_r_;
+  DevBuf d_rver_s_, d_rval_s_, d_rver_r_, d_rval_r_;  // returned rows
+  DevBuf d_stage_grad_, d_stage_dst_;
+
+  uint32_t *h_pinned_ = nullptr;  // pinned mirror for counts read back from the device
+  size_t h_pinned_words_ = 0;
+
+  BatchDesc cur_batch_, prev_batch_;
+  StepStats stats_;
+
+  // profiling
+  struct Span { int phase; cudaEvent_t a, b; };
+  int tic(int phase);
+  void toc(int span);
+  void collectSpans();
+  bool profile_ = false;
+  std::vector<Span> spans_;
+  size_t spans_used_ = 0;
+  double phase_ms_[kPhCount] = {};
+  long long phase_calls_[kPhCount] = {};
+};
+
+}  // namespace hetuCTR

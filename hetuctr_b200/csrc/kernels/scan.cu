@@ -1,0 +1,110 @@
+// Exclusive prefix sum over 32-bit counts in three small launches (tile sums, scan of the tile
+// sums by one CTA, tile-local scan + base).  No spin-waits and no assumption on CTA dispatch
+// order; the inputs on this path are at most a few million entries and L2-resident.
+#include "common.cuh"
+
+namespace hctr {
+
+constexpr int kScanThreads = 1024;
+constexpr int kScanItems = HCTR_SCAN_TILE / kScanThreads;  // 4
+
+__device__ __forceinline__ u32 warp_incl_scan(u32 v) {
+  const unsigned lane = threadIdx.x & 31;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    u32 t = __shfl_up_sync(0xffffffffu, v, d);
+    if (lane >= (unsigned)d) v += t;
+  }
+  return v;
+}
+
+// Block-wide exclusive scan of one value per thread (1024 threads); returns the exclusive prefix and
+// the block total through `total`.
+__device__ __forceinline__ u32 block_excl_scan(u32 v, u32 *total) {
+  __shared__ u32 warp_sums[32];
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  u32 incl = warp_incl_scan(v);
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    u32 w = warp_sums[lane];
+    u32 wi = warp_incl_scan(w);
+    warp_sums[lane] = wi - w;  // exclusive over warps
+    if (lane == 31) *total = wi;
+  }
+  __syncthreads();
+  u32 r = incl - v + warp_sums[warp];
+  __syncthreads();
+  return r;
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_tile_sums(const u32 *__restrict__ in, size_t n_max,
+                                                               const u32 *__restrict__ n_dev,
+                                                               u32 *__restrict__ tile_sum) {
+  const size_t n = n_dev ? min((size_t)*n_dev, n_max) : n_max;
+  const size_t base = (size_t)blockIdx.x * HCTR_SCAN_TILE + (size_t)threadIdx.x * kScanItems;
+  u32 s = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++)
+    if (base + k < n) s += in[base + k];
+  __shared__ u32 total;
+  block_excl_scan(s, &total);
+  if (threadIdx.x == 0) tile_sum[blockIdx.x] = total;
+}
+
+// One CTA: exclusive scan of the tile sums in place, chunk by chunk with a running carry.
+__global__ void __launch_bounds__(kScanThreads) scan_tile_bases(u32 *__restrict__ tile_sum, size_t n_tiles) {
+  __shared__ u32 total;
+  u32 carry = 0;
+  for (size_t c = 0; c < n_tiles; c += kScanThreads) {
+    size_t i = c + threadIdx.x;
+    u32 v = i < n_tiles ? tile_sum[i] : 0;
+    u32 ex = block_excl_scan(v, &total);
+    if (i < n_tiles) tile_sum[i] = carry + ex;
+    carry += total;
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(kScanThreads) scan_apply(const u32 *__restrict__ in, u32 *__restrict__ out,
+                                                           size_t n_max, const u32 *__restrict__ n_dev,
+                                                           const u32 *__restrict__ tile_base) {
+  const size_t n = n_dev ? min((size_t)*n_dev, n_max) : n_max;
+  const size_t base = (size_t)blockIdx.x * HCTR_SCAN_TILE + (size_t)threadIdx.x * kScanItems;
+  u32 v[kScanItems];
+  u32 s = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++) {
+    v[k] = (base + k < n) ? in[base + k] : 0;
+    s += v[k];
+  }
+  __shared__ u32 total;
+  u32 ex = block_excl_scan(s, &total) + tile_base[blockIdx.x];
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++) {
+    if (base + k <= n) out[base + k] = ex;  // entry n receives the grand total
+    ex += v[k];
+  }
+}
+
+}  // namespace hctr
+
+using namespace hctr;
+
+unsigned long long hctr::g_launches = 0;
+
+extern "C" unsigned long long hctr_launch_count(void) { return __atomic_load_n(&hctr::g_launches, __ATOMIC_RELAXED); }
+
+extern "C" size_t hctr_scan_scratch_words(size_t n_max) { return (n_max + 1) / HCTR_SCAN_TILE + 2; }
+
+extern "C" int hctr_scan_exclusive_u32(const uint32_t *in, uint32_t *out, size_t n_max, const uint32_t *n_dev,
+                                       uint32_t *scratch, void *stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  // n+1 outputs: tiles cover [0, n_max]
+  const size_t tiles = (n_max + 1 + HCTR_SCAN_TILE - 1) / HCTR_SCAN_TILE;
+  scan_tile_sums<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, n_max, n_dev, scratch);
+  scan_tile_bases<<<1, kScanThreads, 0, s>>>(scratch, tiles);
+  scan_apply<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n_max, n_dev, scratch);
+  count_launches(3);
+  return launch_status();
+}

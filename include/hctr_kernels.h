@@ -1,0 +1,241 @@
+/*
+ * hctr_kernels.h — C-ABI launchers for the sm_100a kernels of the HetuTable hot path.
+ *
+ * Every function takes raw DEVICE pointers, sizes and a CUDA stream (passed as void*, it is a
+ * cudaStream_t), enqueues its kernels on that stream and returns 0 or a cudaError_t value.  Nothing
+ * here allocates, synchronises or touches host memory unless stated.  The host class (HetuTable)
+ * calls the GPU only through these entry points.
+ *
+ * Citations name the reference code each launcher replaces (paths inside the reference project).
+ *
+ * Conventions
+ *   key / version types : int64   (csrc/core/types.h:16,19)
+ *   owner               : uint8   (csrc/core/types.h:28)
+ *   values              : float   (csrc/core/types.h:12)
+ *   local row ids, batch positions, unique indices, counts : 32-bit on the device
+ *   HCTR_INVALID_ROW (-1)  = key not stored here    (kInvalidIndex,   csrc/core/types.h:22)
+ *   HCTR_INVALID_VERSION   = INT64_MIN              (kInvalidVersion, csrc/core/types.h:25)
+ */
+#ifndef HCTR_KERNELS_H_
+#define HCTR_KERNELS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define HCTR_INVALID_ROW (-1)
+#define HCTR_INVALID_VERSION INT64_MIN
+
+/* bits of the device error word */
+#define HCTR_ERR_KEY_RANGE 1u    /* a batch key is <0, >= length, or its owner id is >= nrank          */
+#define HCTR_ERR_NOT_OWNER 2u    /* an owner-side kernel met a key this rank does not store as owned   */
+#define HCTR_ERR_CAPACITY 4u     /* an internal list overflowed its reserved capacity                  */
+
+/* Keys of the dedupe bitmap are sort keys  sk = key + length_pad * owner  with length_pad = length
+ * rounded up to HCTR_BLOCK_KEYS, so every owner's range starts on a bitmap-block boundary. */
+#define HCTR_WORD_BITS 64
+#define HCTR_BLOCK_WORDS 64
+#define HCTR_BLOCK_KEYS 4096
+#define HCTR_SCAN_TILE 4096
+
+/* Kernels this library has enqueued since it was loaded (all launchers, all streams). */
+unsigned long long hctr_launch_count(void);
+
+/* Number of 32-bit scratch words hctr_scan_exclusive_u32 needs for n_max inputs. */
+size_t hctr_scan_scratch_words(size_t n_max);
+
+/* Exclusive prefix sum of 32-bit counts: out[i] = sum(in[0..i)), for i in [0, n]; out has n+1 entries.
+ * n = *n_dev when n_dev is non-null (a count that only exists on the device), else n_max; grids are
+ * sized from n_max.  `scratch` holds hctr_scan_scratch_words(n_max) words.  in == out is allowed.
+ * Replaces cub::DeviceScan::ExclusiveSum at csrc/core/preprocess.cu:124-125,173-174,
+ * csrc/core/handle_query.cu:56-57 and csrc/core/writeback.cu:45-46. */
+int hctr_scan_exclusive_u32(const uint32_t *in, uint32_t *out, size_t n_max, const uint32_t *n_dev,
+                            uint32_t *scratch, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Table build (set-up side of the path).
+ * ------------------------------------------------------------------------------------------- */
+
+/* row_of[key] = local row of every stored key, HCTR_INVALID_ROW elsewhere; version[row] = INT64_MIN for
+ * cached rows (row < n_cached), 0 for owned rows.  `stored_keys` is the storage list already put in
+ * layout order (cached rows first, each group in caller order).  Sets HCTR_ERR_KEY_RANGE for a key outside
+ * [0,length) and HCTR_ERR_CAPACITY for a key listed twice.
+ * Replaces the hash-map build and version fill of csrc/core/table_initialize.cu:84-87,108-112. */
+int hctr_table_build(const int64_t *stored_keys, size_t n_stored, size_t n_cached, size_t length,
+                     int32_t *row_of, int64_t *version, uint32_t *err, void *stream);
+
+/* Stable partition flags for the storage list: is_cached[i] = owner_of[storage[i]] != rank, and
+ * dst[i] = final local row (cached keys first, both groups in input order), given the exclusive scan
+ * `cached_before` of is_cached (n_stored+1 entries).  Replaces thrust::stable_partition at
+ * csrc/core/table_initialize.cu:76-81. */
+int hctr_storage_flags(const int64_t *storage, size_t n_stored, size_t length, const uint8_t *owner_of,
+                       int rank, uint32_t *is_cached, uint32_t *err, void *stream);
+int hctr_storage_layout(const int64_t *storage, size_t n_stored, const uint32_t *is_cached,
+                        const uint32_t *cached_before, int64_t *stored_keys, void *stream);
+
+/* Counts keys with owner_of[key]==rank (into *n_owned, a device word that must be zero on entry).
+ * Used to check that a rank stores every row it owns. */
+int hctr_count_owned(const uint8_t *owner_of, size_t length, int rank, unsigned long long *n_owned,
+                     void *stream);
+
+/* Fill `data[0..len)`: kind 0 = zeros, 1 = normal(a=mean,b=stddev), 2 = uniform[a,b),
+ * 3 = normal truncated to mean +- 2 stddev.  Element i is drawn from a minstd engine seeded with `seed` and
+ * advanced i steps, so values depend on the local element index only.
+ * Replaces csrc/utils/initializer.cu:11-103. */
+int hctr_initialize(float *data, size_t len, int kind, float a, float b, unsigned int seed, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Preprocess: dedupe + key -> (owner, local row) + batch -> unique map.
+ * Replaces preprocessIndex, csrc/core/preprocess.cu:11-141 (radix sort, run-length encode, scans,
+ * hash probes, binary searches) with bitmap ranking over the dense (owner, key) space.
+ * ------------------------------------------------------------------------------------------- */
+
+typedef struct hctr_dedupe_args {
+  /* inputs */
+  const int64_t *keys;      /* [B] batch keys (device) */
+  size_t batch;             /* B */
+  size_t length;            /* table length N */
+  size_t length_pad;        /* N rounded up to HCTR_BLOCK_KEYS */
+  int nrank;
+  const uint8_t *owner_of;  /* [N] */
+  const int32_t *row_of;    /* [N] */
+  /* persistent scratch, all-zero between calls */
+  unsigned long long *bits; /* [nrank*length_pad/64] */
+  uint32_t *blk_cnt;        /* [nrank*length_pad/4096 + 1] distinct keys per bitmap block */
+  /* scratch that needs no initial value */
+  uint32_t *blk_base;       /* [nblocks + 1] */
+  uint32_t *word_base;      /* [nrank*length_pad/64] */
+  uint32_t *scan_scratch;   /* hctr_scan_scratch_words(max(nblocks, B) + 1) */
+  unsigned long long *sk;   /* [B] sort keys */
+  uint32_t *rank_in_run;    /* [B] */
+  uint32_t *heavy_list;     /* [B/32 + 1] */
+  /* outputs */
+  int64_t *uniq;            /* [B] unique keys, owner-major, key ascending */
+  uint8_t *uniq_owner;      /* [B] */
+  int32_t *uniq_row;        /* [B] local row or HCTR_INVALID_ROW */
+  uint32_t *cnt;            /* [B+1] occurrences per unique */
+  uint32_t *run_start;      /* [B+1] exclusive scan of cnt */
+  uint32_t *sorted_pos;     /* [B] batch positions grouped by unique, ascending inside a group */
+  int32_t *idx_map;         /* [B] batch position -> unique index */
+  uint32_t *meta;           /* [HCTR_META_WORDS + nrank + 1]: see HCTR_META_* */
+} hctr_dedupe_args;
+
+#define HCTR_META_UNIQUE 0   /* number of unique keys U                         */
+#define HCTR_META_ERR 1      /* error word (HCTR_ERR_*)                         */
+#define HCTR_META_NHEAVY 2   /* scratch: number of long runs                    */
+#define HCTR_META_SEG 4      /* seg_start[0..nrank]: first unique of each owner */
+#define HCTR_META_WORDS 4
+
+/* Enqueues the whole dedupe pipeline.  On completion meta[HCTR_META_UNIQUE] = U, meta[HCTR_META_SEG+p]
+ * = index of the first unique key owned by p (entry nrank = U), and the bitmap scratch is all-zero
+ * again.  Keys out of range set HCTR_ERR_KEY_RANGE in meta[HCTR_META_ERR] and get idx_map = -1. */
+int hctr_dedupe_map(const hctr_dedupe_args *a, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Gradient push decision (previous batch).  Replaces decide_update_kernel + scan,
+ * csrc/core/preprocess.cu:148-182.
+ * ------------------------------------------------------------------------------------------- */
+
+/* need_push[u] = 0 if owner==rank; 1 if not stored; else pending_cnt[row] + cnt[u] > push_bound.
+ * Then push_slot = exclusive scan of need_push (U+1 entries) and push_count[p] = pushes to owner p.
+ * U is read from meta (device). */
+int hctr_push_decide(const uint32_t *meta, int nrank, int rank, size_t u_max, const uint8_t *uniq_owner,
+                     const int32_t *uniq_row, const uint32_t *cnt, const int64_t *pending_cnt,
+                     int64_t push_bound, uint32_t *need_push, uint32_t *push_slot,
+                     uint32_t *scan_scratch, uint32_t *push_count, void *stream);
+
+/* Packs the per-peer counts a rank announces after preprocess: out[2p] = unique keys of the current
+ * batch owned by p (from meta's segment starts), out[2p+1] = push_count[p] (0 when push_count is null).
+ * Feeds the count exchange that replaces all2allExchangeShape, csrc/core/all2all.cu:6-16. */
+int hctr_pack_counts(const uint32_t *meta, const uint32_t *push_count, int nrank, uint32_t *out, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Gradient aggregation + local SGD apply + pack of pushed rows (previous batch).
+ * Replaces gradient_index_kernel and gradient_reduction_kernel, csrc/core/generate_query.cu:8-89.
+ * ------------------------------------------------------------------------------------------- */
+
+typedef struct hctr_reduce_args {
+  size_t n_unique;            /* U of the previous batch (host value) */
+  size_t width;               /* W */
+  size_t n_cached;            /* rows [0,n_cached) are cached replicas */
+  float neg_lr;               /* -learning_rate */
+  const float *grad;          /* [B_prev, W] caller's gradients */
+  const uint32_t *run_start;  /* [U+1] */
+  const uint32_t *sorted_pos; /* [B_prev] */
+  const int64_t *uniq;        /* [U] */
+  const int32_t *uniq_row;    /* [U] */
+  const uint32_t *need_push;  /* [U] or null when nrank==1 */
+  const uint32_t *push_slot;  /* [U+1] or null */
+  float *embedding;           /* [S, W] */
+  int64_t *version;           /* [S] */
+  float *pending;             /* [n_cached, W] */
+  int64_t *pending_cnt;       /* [n_cached] */
+  int64_t *push_key;          /* [P] packed ids of pushed rows */
+  int64_t *push_updates;      /* [P] update counts */
+  float *push_val;            /* [P, W] */
+} hctr_reduce_args;
+
+int hctr_grad_reduce_apply_pack(const hctr_reduce_args *a, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Query generation.  Replaces lookup_version_kernel, csrc/core/generate_query.cu:91-106.
+ * ------------------------------------------------------------------------------------------- */
+int hctr_query_versions(size_t n_unique, const int32_t *uniq_row, const int64_t *version,
+                        int64_t *query_version, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Owner side.
+ * ------------------------------------------------------------------------------------------- */
+
+/* Apply `n_rows` pushed rows of ONE source rank: row = row_of[key]; version[row] += updates;
+ * embedding[row] += val.  Called once per source in rank order, which keeps the reference's
+ * conflict-free, deterministic apply order.  Replaces cvt_embedding_idx_2_offset and
+ * table_update_remote_kernel, csrc/core/handle_query.cu:81-116. */
+int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int64_t *updates,
+                      const float *val, const int32_t *row_of, size_t length, size_t n_cached,
+                      float *embedding, int64_t *version, uint32_t *err, void *stream);
+
+/* Staleness decision for `n_query` received (key, version) pairs, laid out as nrank consecutive
+ * segments whose starts are seg_start[0..nrank] (device, 32-bit).  stale = (v == INT64_MIN or
+ * v + pull_bound < version[row]) and the requester is not this rank.  Writes flags (one byte per key),
+ * ret_slot = exclusive scan of flags (n_query+1 entries) and ret_count[p] = rows to return to p.
+ * Replaces decide_outdated_kernel + scan + segmented reduce, csrc/core/handle_query.cu:7-61. */
+int hctr_stale_check(size_t n_query, int nrank, int rank, const uint32_t *seg_start, const int64_t *key,
+                     const int64_t *req_version, const int32_t *row_of, size_t length, size_t n_cached,
+                     const int64_t *version, int64_t pull_bound, uint8_t *flags, uint32_t *flags32,
+                     uint32_t *ret_slot, uint32_t *scan_scratch, uint32_t *ret_count, uint32_t *err,
+                     void *stream);
+
+/* Gather the flagged rows (+ versions) into the return buffer at ret_slot.  Replaces the compaction and
+ * write_return_value_kernel, csrc/core/handle_query.cu:24-40,74-77. */
+int hctr_gather_rows(size_t n_query, size_t width, const int64_t *key, const uint8_t *flags,
+                     const uint32_t *ret_slot, const int32_t *row_of, const float *embedding,
+                     const int64_t *version, float *ret_val, int64_t *ret_version, void *stream);
+
+/* ---------------------------------------------------------------------------------------------
+ * Requester side.  Replaces writeBack, csrc/core/writeback.cu:8-56.
+ * ------------------------------------------------------------------------------------------- */
+
+/* recv_slot = exclusive scan of the flags this rank got back for its unique keys (U+1 entries). */
+int hctr_recv_slots(size_t n_unique, const uint8_t *flags, uint32_t *flags32, uint32_t *recv_slot,
+                    uint32_t *scan_scratch, void *stream);
+
+/* For every flagged unique key that is cached here: embedding[row] = returned + pending[row];
+ * version[row] = returned version. */
+int hctr_cache_refresh(size_t n_unique, size_t width, const uint8_t *flags, const uint32_t *recv_slot,
+                       const int32_t *uniq_row, const float *recv_val, const int64_t *recv_version,
+                       const float *pending, float *embedding, int64_t *version, void *stream);
+
+/* dst[i] = row of keys[i]: from the local table when stored, else from the receive buffer.
+ * recv_slot / recv_val may be null when every key is stored locally (single-rank tables). */
+int hctr_expand_rows(size_t batch, size_t width, const int32_t *idx_map, const int32_t *uniq_row,
+                     const uint32_t *recv_slot, const float *recv_val, const float *embedding,
+                     float *dst, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HCTR_KERNELS_H_ */

@@ -1,0 +1,93 @@
+/*
+ * hctr_table.h — C-ABI of the table object: what a foreign-function binding of the reference's
+ * HetuTable would bind.  One handle = one rank of a distributed embedding table on one GPU.
+ *
+ * Each entry point mirrors a member of the reference's Python-facing class
+ * (csrc/pybind/pybind.cu:42-79, csrc/pybind/container.h:10-37, csrc/core/hetu_gpu_table.h:109-144);
+ * argument meaning and call protocol are the reference's.  Functions return 0 on success and -1 on
+ * error; hctr_last_error() then describes the failure (thread-local).
+ */
+#ifndef HCTR_TABLE_H_
+#define HCTR_TABLE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct hctr_table hctr_table;  /* opaque */
+typedef struct hctr_wait hctr_wait;    /* opaque handle of an asynchronous call */
+
+/* InitType, csrc/utils/initializer.h:8-14 and csrc/pybind/pybind.cu:53-57 */
+enum { HCTR_INIT_ZERO = 0, HCTR_INIT_NORMAL = 1, HCTR_INIT_UNIFORM = 2, HCTR_INIT_TRUNCATED_NORMAL = 3 };
+
+const char *hctr_last_error(void);
+
+/* hetuCTR.seed(n), csrc/pybind/pybind.cu:77: seed for tables created afterwards in this process. */
+void hctr_seed(unsigned long seed);
+
+/* hetuCTR.HetuTable(...), csrc/pybind/pybind.cu:9-36,62-69.  Collective over all `nrank` processes
+ * when nrank > 1 (TCP rendezvous on ip:port, then an NCCL communicator).  root_arr has `length`
+ * entries (owner of every key), storage_arr lists the keys this rank stores (owned + cached); both are
+ * host arrays read during construction only.  init_a/init_b are (mean, stddev) or (a, b).
+ * Returns NULL on error. */
+hctr_table *hctr_table_create(int rank, int nrank, int device_id, const char *ip, int port, size_t length,
+                              size_t width, int64_t pull_bound, int64_t push_bound, const uint8_t *root_arr,
+                              const int64_t *storage_arr, size_t storage_len, int init_type, float init_a,
+                              float init_b, float learning_rate, int verbose);
+
+/* ~HetuTable, csrc/core/table_initialize.cu:231-245 */
+void hctr_table_destroy(hctr_table *t);
+
+/* HetuTable.preprocess(data_ptr, n_keys), csrc/pybind/container.h:19-22: `keys` is host or device
+ * memory holding n_keys int64 keys.  Returns when the batch is ready. */
+int hctr_table_preprocess(hctr_table *t, const int64_t *keys, size_t n_keys);
+
+/* HetuTable.push_pull(grad_ptr, dst_ptr), csrc/pybind/container.h:14-17: grad = [n_keys_prev, width]
+ * gradients of the PREVIOUS batch (NULL = inference step, on all ranks together), dst = [n_keys_cur,
+ * width] output.  Device memory; host memory is accepted and staged.  Returns when dst is written. */
+int hctr_table_push_pull(hctr_table *t, const float *grad, float *dst);
+
+/* async_preprocess / async_push_pull / _waittype.wait(), csrc/pybind/container.h:24-34,
+ * csrc/pybind/pybind.cu:46-51: the same calls queued on the table's single worker thread, in order.
+ * hctr_wait_finish blocks, frees the handle and returns the call's status. */
+hctr_wait *hctr_table_preprocess_async(hctr_table *t, const int64_t *keys, size_t n_keys);
+hctr_wait *hctr_table_push_pull_async(hctr_table *t, const float *grad, float *dst);
+int hctr_wait_finish(hctr_wait *w);
+
+/* __repr__ / debug(), csrc/core/debug.cu:5-24.  Writes a NUL-terminated string, returns its length. */
+int hctr_table_repr(hctr_table *t, int full, char *buf, size_t buf_len);
+
+/* ---- extensions (no counterpart in the reference; used by parity tests and benchmarks) ---------- */
+
+/* Copies an internal array to host memory: as int64 for index/version arrays, float for "embedding"
+ * and "gradient".  Returns the element count (call with out = NULL to size the buffer), -1 on error.
+ * Names: unique_idx idx_map sorted_arg run_length root offset shape shape_exchanged push_shape
+ * push_shape_exchanged return_shape return_shape_exchanged need_update version updates stored_keys
+ * embedding gradient.  prev != 0 selects the previous batch. */
+long long hctr_table_dump(hctr_table *t, const char *what, int prev, void *out);
+
+/* Overwrites all local rows from host memory ([stored rows, width], local row order). */
+int hctr_table_set_embedding(hctr_table *t, const float *rows);
+
+/* Sizes of the last push_pull: {batch, unique, prev_batch, prev_unique, pushed_rows,
+ * received_push_rows, queried_keys, returned_rows, received_rows, stored_rows, cached_rows}. */
+int hctr_table_stats(hctr_table *t, long long out[11]);
+
+/* Per-phase device time.  While profiling is enabled each phase of preprocess/push_pull is bracketed by
+ * two CUDA events on the table's stream; hctr_table_phase_times returns the accumulated milliseconds and
+ * call counts per phase (and clears them when reset != 0).  Phase order: dedupe, push_decide, reduce,
+ * query, exchange, owner_update, stale_gather, refresh, expand. */
+#define HCTR_N_PHASES 9
+int hctr_table_profile(hctr_table *t, int enable);
+int hctr_table_phase_times(hctr_table *t, double ms[HCTR_N_PHASES], long long calls[HCTR_N_PHASES], int reset);
+
+/* The CUDA stream (cudaStream_t) the table enqueues its work on. */
+void *hctr_table_stream(hctr_table *t);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* HCTR_TABLE_H_ */

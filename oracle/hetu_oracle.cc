@@ -22,7 +22,9 @@
 
 #include <algorithm>
 #include <cstdint>
+#include <cstdlib>
 #include <cstring>
+#include <new>
 #include <limits>
 #include <numeric>
 #include <stdexcept>
@@ -55,6 +57,28 @@ inline version_t wadd(version_t a, version_t b) {
   return (version_t)((unsigned long long)a + (unsigned long long)b);
 }
 
+// Zero-initialised array whose pages are only touched when used (calloc): a 17 GB table of which a
+// benchmark sample touches a few hundred MB costs nothing to create.
+template <class T>
+struct ZeroBuf {
+  T *p = nullptr;
+  size_t n = 0;
+  ZeroBuf() {}
+  ZeroBuf(const ZeroBuf &) = delete;
+  ZeroBuf &operator=(const ZeroBuf &) = delete;
+  ~ZeroBuf() { std::free(p); }
+  void assign_zero(size_t count) {
+    std::free(p);
+    p = count ? static_cast<T *>(std::calloc(count, sizeof(T))) : nullptr;
+    if (count && !p) throw std::bad_alloc();
+    n = count;
+  }
+  size_t size() const { return n; }
+  T *begin() { return p; }
+  T &operator[](size_t i) { return p[i]; }
+  const T &operator[](size_t i) const { return p[i]; }
+};
+
 // csrc/core/preprocess_struct.h:7-24 — one batch descriptor.
 struct Batch {
   size_t batch_size = 0;
@@ -76,8 +100,8 @@ struct Rank {
   size_t nonlocal = 0;   // kNonLocalStorageMax
   std::vector<int32_t> row_of;       // dense stand-in for the key->row hash map; -1 = not stored
   std::vector<index_t> stored_keys;  // key of each local row
-  std::vector<embed_t> emb;          // d_embedding_
-  std::vector<embed_t> pend;         // d_gradient_ (cached rows only)
+  ZeroBuf<embed_t> emb;              // d_embedding_
+  ZeroBuf<embed_t> pend;             // d_gradient_ (cached rows only)
   std::vector<version_t> pend_cnt;   // d_updates_  (cached rows only)
   std::vector<version_t> ver;        // d_version_
   Batch cur, prev;
@@ -123,8 +147,8 @@ void set_storage(World &w, int r, const index_t *storage, size_t S) {
     if (w.owner[storage[i]] == r) k.stored_keys.push_back(storage[i]);
   k.row_of.assign(w.length, -1);
   for (size_t i = 0; i < S; i++) k.row_of[k.stored_keys[i]] = (int32_t)i;
-  k.emb.assign(S * w.width, 0.f);
-  k.pend.assign(k.nonlocal * w.width, 0.f);
+  k.emb.assign_zero(S * w.width);
+  k.pend.assign_zero(k.nonlocal * w.width);
   k.pend_cnt.assign(k.nonlocal, 0);
   k.ver.assign(S, 0);
   std::fill(k.ver.begin(), k.ver.begin() + k.nonlocal, kInvalidVersion);
@@ -408,7 +432,7 @@ void handle_query(World &w, Rank &k) {
         counts[src]++;
         k.update_prefix.push_back(id);
         k.ret_ver_s.push_back(gv);
-        k.ret_val_s.insert(k.ret_val_s.end(), k.emb.begin() + (size_t)row * W, k.emb.begin() + (size_t)(row + 1) * W);
+        k.ret_val_s.insert(k.ret_val_s.end(), k.emb.p + (size_t)row * W, k.emb.p + (size_t)(row + 1) * W);
       }
     }
   }
@@ -573,7 +597,7 @@ void *ho_world_create(int nrank, long long length, long long width, long long pu
   w->push_bound = push_bound;
   w->lr = learning_rate;
   w->owner.assign(root_arr, root_arr + length);
-  w->ranks.resize(nrank);
+  w->ranks = std::vector<Rank>(nrank);
   for (int r = 0; r < nrank; r++) w->ranks[r].rank = r;
   return w;
 }
@@ -589,7 +613,7 @@ int ho_set_storage(void *h, int rank, const long long *storage, long long n) {
 int ho_set_embedding(void *h, int rank, const float *emb) {
   return guarded([&] {
     Rank &k = ((World *)h)->ranks[rank];
-    std::copy(emb, emb + k.emb.size(), k.emb.begin());
+    std::copy(emb, emb + k.emb.size(), k.emb.p);
   });
 }
 
