@@ -30,13 +30,16 @@ N_BATCHES = 6  # distinct pre-generated batches / gradient buffers, cycled
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--config", default="cfg2_hybrid", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work in the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--width", type=int, default=0, help="override the row width (small ncu captures only)")
+    ap.add_argument("--rows", type=int, default=0,
+                    help="override the table length (small ncu captures only; the line is then not a bench value)")
     return ap.parse_args()
 
 
@@ -53,7 +56,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "200", "-i", str(self.gpu)], stdout=subprocess.PIPE,
+                                          "-lms", "50", "-i", str(self.gpu)], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -90,8 +93,12 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def make_workload(cfg, nrank, rank):
-    c = CONFIGS[cfg]
+def make_workload(cfg, nrank, rank, rows=0, width=0):
+    c = dict(CONFIGS[cfg])
+    if rows:
+        c["rows"] = rows
+    if width:
+        c["width"] = width
     sampler = KeySampler(c["rows"], c["fields"], c["alpha"], c["ratio"])
     root = random_owners(c["rows"], nrank)
     cache_rows = int(c["rows"] * c["cache"]) if nrank > 1 else 0
@@ -126,7 +133,7 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    c, root, storage, batches = make_workload(args.config, world, rank)
+    c, root, storage, batches = make_workload(args.config, world, rank, args.rows, args.width)
     W, B = c["width"], c["samples"] * c["fields"]
     addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
     port = int(os.environ.get("MASTER_PORT", 29500)) + 101
@@ -157,14 +164,14 @@ def run_ours(args):
     # prime the pipeline (the first push_pull has no previous batch), then warm up
     table.preprocess(keys_dev[-1], B)
     table.push_pull(None, dst)
+    clocks = ClockSampler(local)
+    if rank == 0:
+        clocks.start()  # sampling covers warm-up + timed region, both under the same load
     for i in range(args.warmup):
         step(i)
 
     table.profile(True)
     table.phase_times(reset=True)
-    clocks = ClockSampler(local)
-    if rank == 0:
-        clocks.start()
     launches0 = hb.lib().hctr_launch_count()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -227,7 +234,7 @@ def run_ours(args):
             "metric": METRIC, "value": world * B * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.config, "rows": c["rows"], "width": W, "keys_per_gpu_per_step": B,
+            "config": {"workload": args.config + (" (size overridden)" if args.rows or args.width else ""), "rows": c["rows"], "width": W, "keys_per_gpu_per_step": B,
                        "unique_per_gpu_per_step": stats["unique"], "key_distribution":
                        "uniform" if c["alpha"] is None else f"zipf({c['alpha']}) per field, {c['fields']} fields",
                        "cache_fraction": c["cache"] if world > 1 else 0.0, "pull_bound": c["pull_bound"],
@@ -301,7 +308,7 @@ def run_reference(args):
     return {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": world,
             "steps": steps, "warmup": 1, "ms_per_step": world * B / cb["value"] * 1e3, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.config, "rows": c["rows"], "width": c["width"],
+            "config": {"workload": args.config + (" (size overridden)" if args.rows or args.width else ""), "rows": c["rows"], "width": c["width"],
                        "keys_per_gpu_per_step": B},
             "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

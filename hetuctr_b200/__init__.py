@@ -29,6 +29,23 @@ _lib = None
 _mod = None
 
 
+def _preload_nccl():
+    """The library needs libnccl.so.2.  PyTorch wheels bundle their own (newer) copy under nvidia/nccl; if this
+    library pulled in the system copy first, a later `import torch` in the same process would fail to resolve
+    symbols of the newer one.  So when a bundled copy exists it is loaded first and both share it."""
+    try:
+        spec = importlib.util.find_spec("nvidia.nccl")
+    except (ImportError, ValueError):
+        spec = None
+    if spec and spec.submodule_search_locations:
+        for d in spec.submodule_search_locations:
+            cand = os.path.join(d, "lib", "libnccl.so.2")
+            if os.path.exists(cand):
+                ctypes.CDLL(cand, mode=ctypes.RTLD_GLOBAL)
+                return cand
+    return None
+
+
 def lib():
     """The C-ABI library as a ctypes.CDLL with argument types set."""
     global _lib
@@ -36,6 +53,7 @@ def lib():
         return _lib
     if not os.path.exists(LIB_PATH):
         raise ImportError(f"{LIB_PATH} is missing: build it with `python -m hetuctr_b200.build`")
+    _preload_nccl()
     L = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_GLOBAL)
     c = ctypes
     vp, sz, i64, i32 = c.c_void_p, c.c_size_t, c.c_int64, c.c_int

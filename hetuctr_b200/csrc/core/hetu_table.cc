@@ -74,6 +74,10 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
   HCTR_CHECK(device_id >= 0 && device_id < num_gpus, "InCorrect device number.");
   HCTR_CUDA(cudaSetDevice(device_id_));
   HCTR_CUDA(cudaStreamCreateWithFlags(&stream_main_, cudaStreamNonBlocking));
+  HCTR_CUDA(cudaStreamCreateWithFlags(&stream_side_, cudaStreamNonBlocking));
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_keys_, cudaEventDisableTiming | cudaEventBlockingSync));
 
   try {
     initComm(ip, port);
@@ -196,9 +200,10 @@ void HetuTable::reserveBatch(BatchDesc &b, size_t batch) {
   b.uniq.ensure(batch * sizeof(index_t));
   b.uniq_owner.ensure(batch);
   b.uniq_row.ensure(batch * sizeof(int32_t));
-  b.cnt.ensure((batch + 1) * sizeof(uint32_t));
   b.run_start.ensure((batch + 1) * sizeof(uint32_t));
   b.meta.ensure((HCTR_META_WORDS + nrank_ + 1) * sizeof(uint32_t));
+  b.pos_row.ensure(batch * sizeof(int32_t));
+  b.heavy.ensure((batch / 32 + 2) * sizeof(uint32_t));
   b.capacity = batch;
 }
 
@@ -210,7 +215,8 @@ void HetuTable::reserveShared(size_t batch) {
   d_scan_.ensure(hctr_scan_scratch_words(scan_n) * sizeof(uint32_t));
   d_sk_.ensure(batch * sizeof(unsigned long long));
   d_rank_.ensure(batch * sizeof(uint32_t));
-  d_heavy_.ensure((batch / 32 + 2) * sizeof(uint32_t));
+  d_cnt_.ensure((batch + 1) * sizeof(uint32_t));  // all-zero between calls, like the bitmap
+  HCTR_CUDA(cudaMemsetAsync(d_cnt_.p, 0, d_cnt_.bytes, stream_main_));
   d_need_push_.ensure((batch + 1) * sizeof(uint32_t));
   d_push_slot_.ensure((batch + 1) * sizeof(uint32_t));
   d_push_count_.ensure((size_t)nrank_ * sizeof(uint32_t));
@@ -236,6 +242,7 @@ void HetuTable::reserveShared(size_t batch) {
 // ------------------------------------------------------------------------------------------------
 void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   HCTR_CUDA(cudaSetDevice(device_id_));
+  finalizePending();
   std::swap(cur_batch_, prev_batch_);
   BatchDesc &cur = cur_batch_, &prev = prev_batch_;
   reserveBatch(cur, std::max<size_t>(batch_size, 1));
@@ -245,6 +252,7 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   const size_t meta_words = HCTR_META_WORDS + n + 1;
 
   HCTR_CUDA(cudaMemcpyAsync(cur.keys.p, data_ptr, sizeof(index_t) * batch_size, cudaMemcpyDefault, stream_main_));
+  HCTR_CUDA(cudaEventRecord(ev_keys_, stream_main_));
   HCTR_CUDA(cudaMemsetAsync(cur.meta.p, 0, meta_words * sizeof(uint32_t), stream_main_));
 
   hctr_dedupe_args a;
@@ -262,15 +270,19 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   a.scan_scratch = d_scan_.as<uint32_t>();
   a.sk = d_sk_.as<unsigned long long>();
   a.rank_in_run = d_rank_.as<uint32_t>();
-  a.heavy_list = d_heavy_.as<uint32_t>();
+  a.heavy_list = cur.heavy.as<uint32_t>();
+  a.pos_row = cur.pos_row.as<int32_t>();
   a.uniq = cur.uniq.as<int64_t>();
   a.uniq_owner = cur.uniq_owner.as<uint8_t>();
   a.uniq_row = cur.uniq_row.as<int32_t>();
-  a.cnt = cur.cnt.as<uint32_t>();
+  a.cnt = d_cnt_.as<uint32_t>();
   a.run_start = cur.run_start.as<uint32_t>();
   a.sorted_pos = cur.sorted_pos.as<uint32_t>();
   a.idx_map = cur.idx_map.as<int32_t>();
   a.meta = cur.meta.as<uint32_t>();
+  a.side_stream = stream_side_;
+  a.fork_event = ev_fork_;
+  a.join_event = ev_join_;
   int sp = tic(kPhDedupe);
   HCTR_LAUNCH(hctr_dedupe_map(&a, stream_main_));
   toc(sp);
@@ -281,7 +293,7 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   if (decide) {
     sp = tic(kPhPushDecide);
     HCTR_LAUNCH(hctr_push_decide(prev.meta.as<uint32_t>(), n, rank_, prev.unique_size, prev.uniq_owner.as<uint8_t>(),
-                                 prev.uniq_row.as<int32_t>(), prev.cnt.as<uint32_t>(), d_updates_.as<int64_t>(),
+                                 prev.uniq_row.as<int32_t>(), prev.run_start.as<uint32_t>(), d_updates_.as<int64_t>(),
                                  push_bound_, d_need_push_.as<uint32_t>(), d_push_slot_.as<uint32_t>(),
                                  d_scan_.as<uint32_t>(), d_push_count_.as<uint32_t>(), stream_main_));
     toc(sp);
@@ -305,10 +317,31 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
     HCTR_CUDA(cudaMemcpyAsync(h_cnt_s, d_cnt_s_.p, 2 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
     HCTR_CUDA(cudaMemcpyAsync(h_cnt_r, d_cnt_r_.p, 2 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
   }
+  if (n == 1) {
+    // Nothing on the host depends on the result before push_pull: wait only until the caller's key
+    // buffer has been consumed and let the rest of the pipeline run under the next call's launches.
+    // The batch's sizes (and a key-range error, if any) are picked up at the next synchronisation.
+    HCTR_CUDA(cudaEventSynchronize(ev_keys_));
+    cur.pending = true;
+    return;
+  }
   HCTR_CUDA(cudaStreamSynchronize(stream_main_));
   collectSpans();
+  finalizeBatch();
+}
 
+// Reads the counts the preprocess pipeline copied to pinned memory into the batch descriptors.
+// The stream must have drained.
+void HetuTable::finalizeBatch() {
+  BatchDesc &cur = cur_batch_, &prev = prev_batch_;
+  const int n = nrank_;
+  const size_t meta_words = HCTR_META_WORDS + n + 1;
+  const uint32_t *h_meta = h_pinned_;
+  const uint32_t *h_cnt_s = h_pinned_ + meta_words;
+  const uint32_t *h_cnt_r = h_cnt_s + 2 * n;
+  cur.pending = false;
   cur.unique_size = h_meta[HCTR_META_UNIQUE];
+  cur.n_heavy = h_meta[HCTR_META_NHEAVY];
   for (int p = 0; p <= n; p++) cur.seg[p] = h_meta[HCTR_META_SEG + p];
   for (int p = 0; p < n; p++) {
     cur.query_send[p] = cur.seg[p + 1] - cur.seg[p];
@@ -320,8 +353,16 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
     // leave a consistent (empty) batch behind, then report
     cur.batch_size = 0;
     cur.unique_size = 0;
+    cur.n_heavy = 0;
     throw std::runtime_error("preprocess: a key is outside [0, length) or its root_arr entry is >= nrank");
   }
+}
+
+void HetuTable::finalizePending() {
+  if (!cur_batch_.pending) return;
+  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+  collectSpans();
+  finalizeBatch();
 }
 
 const void *HetuTable::stageIn(const void *ptr, size_t bytes, DevBuf &buf) {
@@ -350,6 +391,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   if (grad == nullptr) {
     prev.batch_size = 0;
     prev.unique_size = 0;
+    prev.n_heavy = 0;
     std::fill(prev.push_send.begin(), prev.push_send.end(), 0);
     std::fill(prev.push_recv.begin(), prev.push_recv.end(), 0);
   }
@@ -399,6 +441,8 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     r.grad = grad_dev;
     r.run_start = prev.run_start.as<uint32_t>();
     r.sorted_pos = prev.sorted_pos.as<uint32_t>();
+    r.heavy_list = prev.heavy.as<uint32_t>();
+    r.n_heavy = prev.n_heavy;
     r.uniq = prev.uniq.as<int64_t>();
     r.uniq_row = prev.uniq_row.as<int32_t>();
     r.need_push = n > 1 ? d_need_push_.as<uint32_t>() : nullptr;
@@ -410,6 +454,10 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     r.push_key = d_pkey_s_.as<int64_t>();
     r.push_updates = d_pupd_s_.as<int64_t>();
     r.push_val = d_pval_s_.as<float>();
+    r.work_counter = d_err_.as<uint32_t>() + 32;
+    r.side_stream = stream_side_;
+    r.fork_event = ev_fork_;
+    r.join_event = ev_join_;
     int sp = tic(kPhReduce);
     HCTR_LAUNCH(hctr_grad_reduce_apply_pack(&r, stream_main_));
     toc(sp);
@@ -418,7 +466,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   if (n == 1) {
     // Single rank: every key is owned and stored here; the pull is a local gather.
     int sp = tic(kPhExpand);
-    HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.idx_map.as<int32_t>(), cur.uniq_row.as<int32_t>(), nullptr,
+    HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
                                  nullptr, d_embedding_.as<float>(), dst_dev, stream_main_));
     toc(sp);
   } else {
@@ -571,7 +619,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
                                    stream_main_));
     toc(sp);
     sp = tic(kPhExpand);
-    HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.idx_map.as<int32_t>(), cur.uniq_row.as<int32_t>(),
+    HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
                                  d_recv_slot_.as<uint32_t>(), d_rval_r_.as<float>(), d_embedding_.as<float>(), dst_dev,
                                  stream_main_));
     toc(sp);
@@ -585,6 +633,10 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     HCTR_CUDA(cudaMemcpyAsync(dst, dst_dev, cur.batch_size * W * sizeof(embed_t), cudaMemcpyDeviceToHost, stream_main_));
   HCTR_CUDA(cudaStreamSynchronize(stream_main_));
   collectSpans();
+  if (cur.pending) {
+    finalizeBatch();
+    stats_.unique = cur.unique_size;
+  }
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -658,6 +710,7 @@ long long copy_sizes(const std::vector<size_t> &v, size_t n, void *out) {
 
 long long HetuTable::dump(const std::string &what, bool prev, void *out) {
   HCTR_CUDA(cudaSetDevice(device_id_));
+  finalizePending();
   BatchDesc &b = prev ? prev_batch_ : cur_batch_;
   const size_t B = b.batch_size, U = b.unique_size;
   cudaStream_t s = stream_main_;
@@ -717,18 +770,19 @@ HetuTable::~HetuTable() { releaseAll(); }
 
 void HetuTable::releaseAll() {
   cudaSetDevice(device_id_);
+  if (stream_side_) cudaStreamSynchronize(stream_side_);
   if (stream_main_) cudaStreamSynchronize(stream_main_);
   transport_.reset();
   DevBuf *all[] = {&d_embedding_, &d_gradient_, &d_updates_, &d_version_, &d_root_, &d_row_of_, &d_stored_keys_,
-                   &d_bits_, &d_blk_cnt_, &d_blk_base_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_heavy_,
+                   &d_bits_, &d_blk_cnt_, &d_blk_base_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_cnt_,
                    &d_need_push_, &d_push_slot_, &d_push_count_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
                    &d_qkey_r_, &d_qver_r_, &d_pkey_s_, &d_pupd_s_, &d_pval_s_, &d_pkey_r_, &d_pupd_r_, &d_pval_r_,
                    &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,
                    &d_retcnt_r_, &d_rver_s_, &d_rval_s_, &d_rver_r_, &d_rval_r_, &d_stage_grad_, &d_stage_dst_};
   for (DevBuf *b : all) b->release();
   for (BatchDesc *b : {&cur_batch_, &prev_batch_})
-    for (DevBuf *d : {&b->keys, &b->idx_map, &b->sorted_pos, &b->uniq, &b->uniq_owner, &b->uniq_row, &b->cnt,
-                      &b->run_start, &b->meta})
+    for (DevBuf *d : {&b->keys, &b->idx_map, &b->sorted_pos, &b->uniq, &b->uniq_owner, &b->uniq_row,
+                      &b->run_start, &b->meta, &b->pos_row, &b->heavy})
       d->release();
   for (Span &sp : spans_) {
     cudaEventDestroy(sp.a);
@@ -737,6 +791,12 @@ void HetuTable::releaseAll() {
   spans_.clear();
   if (h_pinned_) cudaFreeHost(h_pinned_);
   h_pinned_ = nullptr;
+  if (ev_fork_) cudaEventDestroy(ev_fork_);
+  if (ev_join_) cudaEventDestroy(ev_join_);
+  if (ev_keys_) cudaEventDestroy(ev_keys_);
+  ev_fork_ = ev_join_ = ev_keys_ = nullptr;
+  if (stream_side_) cudaStreamDestroy(stream_side_);
+  stream_side_ = nullptr;
   if (stream_main_) cudaStreamDestroy(stream_main_);
   stream_main_ = nullptr;
 }

@@ -54,7 +54,9 @@ struct BatchDesc {
   size_t batch_size = 0;
   size_t unique_size = 0;
   size_t capacity = 0;
-  DevBuf keys, idx_map, sorted_pos, uniq, uniq_owner, uniq_row, cnt, run_start, meta;
+  size_t n_heavy = 0;  // runs longer than HCTR_LIGHT_RUN
+  bool pending = false;  // sizes not yet read back from the device (single-rank tables defer this)
+  DevBuf keys, idx_map, sorted_pos, uniq, uniq_owner, uniq_row, run_start, meta, pos_row, heavy;
   std::vector<size_t> seg;         // [n+1] first unique of each owner
   std::vector<size_t> query_send;  // [n] unique keys addressed to each owner
   std::vector<size_t> query_recv;  // [n] keys each requester sends to me
@@ -135,9 +137,13 @@ class HetuTable {
   void reserveShared(size_t batch);
   void exchangeCounts();
   void releaseAll();
+  void finalizeBatch();
+  void finalizePending();
   const void *stageIn(const void *ptr, size_t bytes, DevBuf &buf);
 
   cudaStream_t stream_main_ = nullptr;
+  cudaStream_t stream_side_ = nullptr;  // overlaps the long-run kernels with their short-run twins
+  cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr, ev_keys_ = nullptr;
   std::unique_ptr<Transport> transport_;
 
   // table state
@@ -145,7 +151,7 @@ class HetuTable {
   size_t length_pad_ = 0;
 
   // dedupe scratch (persistent, all-zero between calls) and per-step scratch
-  DevBuf d_bits_, d_blk_cnt_, d_blk_base_, d_word_base_, d_scan_, d_sk_, d_rank_, d_heavy_;
+  DevBuf d_bits_, d_blk_cnt_, d_blk_base_, d_word_base_, d_scan_, d_sk_, d_rank_, d_cnt_;
   DevBuf d_need_push_, d_push_slot_, d_push_count_, d_err_;
   size_t shared_capacity_ = 0;
 

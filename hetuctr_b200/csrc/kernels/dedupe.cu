@@ -4,38 +4,42 @@
 // The key space is dense ([0, length) with a 1-byte owner per key), so instead of sorting
 // (owner,key,position) triples the batch is RANKED through a bitmap over the sort-key space
 //     sk = key + length_pad * owner          (length_pad = length rounded up to 4096)
-//   mark     one bit per distinct sk (atomicOr); the first setter bumps its 4096-key block's count
+//   mark     one bit per distinct sk (atomicOr); the first setter bumps its 4096-key block's count.
+//            A 1/16 sample of the batch is marked by a first launch, so that in the main launch the
+//            duplicates of hot keys find their bit already set and skip the atomic.
 //   scan     block counts -> block bases                         (hctr_scan_exclusive_u32)
-//   extract  one warp per non-empty block: popcount prefix inside the block gives every set bit its
-//            rank = index in the sorted unique list; the warp writes unique key, owner, local row and
-//            the per-word base used by the next step
-//   rank     per batch position: unique index = word_base + popcount(bits below); an atomic counter
-//            per unique key hands out a slot inside the key's run
+//   extract  one warp per non-empty block: popcount prefix inside the block gives every 64-key word
+//            the rank of its first set bit = index in the sorted unique list
+//   rank     per batch position: unique index = word base + popcount(bits below); an atomic counter
+//            per unique key hands out a slot inside the key's run, and the position that draws slot 0
+//            writes the unique key, its owner and its local row
 //   scan     occurrences -> run starts
-//   scatter  positions into their runs; clears the bitmap words and block counts it touched
+//   scatter  positions into their runs; the slot-0 position also clears the bitmap word and counter
 //   order    each run is put in ascending position order so that gradient sums are taken in batch
-//            order (short runs in registers, long runs through a shared-memory position bitmap)
-// Work is O(batch) plus one pass over the block counts; nothing probes, nothing can overflow.
+//            order (runs up to 32 by one warp, longer runs through a shared-memory position bitmap)
+// Work is O(batch) plus one pass over the block counts; nothing probes, nothing can overflow, and
+// cost does not depend on how skewed the keys are.
 #include "common.cuh"
 
 namespace hctr {
 
 constexpr int kThreads = 256;
-constexpr u32 kLightRun = 32;              // runs up to this length are sorted by one thread
+constexpr u32 kLightRun = HCTR_LIGHT_RUN;  // runs up to this length are ordered by one warp
 constexpr int kHeavyWindowBits = 1 << 20;  // positions covered by one shared-memory window (128 KB)
 
-__global__ void __launch_bounds__(kThreads) dedupe_mark(hctr_dedupe_args a) {
-  const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
-  if (i == 0) a.meta[HCTR_META_NHEAVY] = 0;
-  if (i >= a.batch) return;
+// positions [first, first + count)
+__global__ void __launch_bounds__(kThreads) dedupe_mark(hctr_dedupe_args a, size_t first, size_t count) {
+  const size_t t = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  if (t >= count) return;
+  const size_t i = first + t;
   const long long key = a.keys[i];
-  if (key < 0 || (size_t)key >= a.length) {
-    atomicOr(&a.meta[HCTR_META_ERR], HCTR_ERR_KEY_RANGE);
-    a.sk[i] = ~0ull;
-    return;
+  unsigned o = 0;
+  bool ok = key >= 0 && (size_t)key < a.length;
+  if (ok) {
+    o = a.owner_of[key];
+    ok = o < (unsigned)a.nrank;
   }
-  const unsigned o = a.owner_of[key];
-  if (o >= (unsigned)a.nrank) {
+  if (!ok) {
     atomicOr(&a.meta[HCTR_META_ERR], HCTR_ERR_KEY_RANGE);
     a.sk[i] = ~0ull;
     return;
@@ -44,8 +48,7 @@ __global__ void __launch_bounds__(kThreads) dedupe_mark(hctr_dedupe_args a) {
   a.sk[i] = sk;
   const u64 bit = 1ull << (sk & 63);
   u64 *word = a.bits + (sk >> 6);
-  // duplicates of a hot key mostly see the bit already set and skip the atomic
-  if (*(volatile u64 *)word & bit) return;
+  if (*(volatile u64 *)word & bit) return;  // already marked (by the sample pass or an earlier duplicate)
   const u64 old = atomicOr(word, bit);
   if (!(old & bit)) atomicAdd(&a.blk_cnt[sk >> 12], 1u);
 }
@@ -62,10 +65,12 @@ __device__ __forceinline__ u32 warp_excl_scan_total(u32 v, u32 *total) {
   return incl - v;
 }
 
-// Each warp walks groups of 32 consecutive bitmap blocks; lanes fetch the 32 counts/bases at once and
-// the warp then expands the non-empty blocks one by one.
+// Each warp walks groups of `group` (1..32) consecutive bitmap blocks; lanes fetch the counts/bases of a
+// group at once and the warp then ranks the words of the non-empty blocks.  Small tables use group = 1
+// (one warp per block, maximum parallelism); huge, sparsely hit tables use 32 so that empty blocks
+// cost one coalesced load per 32.  Block counts are cleared on the way (they are consumed here).
 __global__ void __launch_bounds__(kThreads) dedupe_extract(hctr_dedupe_args a, size_t n_blocks,
-                                                           size_t blocks_per_owner) {
+                                                           size_t blocks_per_owner, unsigned group) {
   const unsigned lane = threadIdx.x & 31;
   const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const size_t n_warps = ((size_t)gridDim.x * kThreads) >> 5;
@@ -73,14 +78,14 @@ __global__ void __launch_bounds__(kThreads) dedupe_extract(hctr_dedupe_args a, s
     const u32 U = a.blk_base[n_blocks];
     a.meta[HCTR_META_UNIQUE] = U;
     a.meta[HCTR_META_SEG + a.nrank] = U;
-    a.cnt[U] = 0;
   }
-  for (size_t g = warp * 32; g < n_blocks; g += n_warps * 32) {
+  for (size_t g = warp * group; g < n_blocks; g += n_warps * group) {
     const size_t b = g + lane;
     u32 c = 0, base = 0;
-    if (b < n_blocks) {
+    if (lane < group && b < n_blocks) {
       c = a.blk_cnt[b];
       base = a.blk_base[b];
+      if (c) a.blk_cnt[b] = 0;
       if (b % blocks_per_owner == 0) a.meta[HCTR_META_SEG + b / blocks_per_owner] = base;
     }
     unsigned live = __ballot_sync(0xffffffffu, c != 0);
@@ -94,27 +99,8 @@ __global__ void __launch_bounds__(kThreads) dedupe_extract(hctr_dedupe_args a, s
       u32 t0, t1;
       const u32 e0 = warp_excl_scan_total(__popcll(x0), &t0);
       const u32 e1 = warp_excl_scan_total(__popcll(x1), &t1);
-      const u32 b0 = blk_base + e0, b1 = blk_base + t0 + e1;
-      a.word_base[w0] = b0;
-      a.word_base[w1] = b1;
-      const unsigned owner = (unsigned)(blk / blocks_per_owner);
-      const u64 owner_off = (u64)owner * a.length_pad;
-#pragma unroll
-      for (int h = 0; h < 2; h++) {
-        u64 x = h ? x1 : x0;
-        u32 u = h ? b1 : b0;
-        const u64 sk0 = (u64)(h ? w1 : w0) << 6;
-        while (x) {
-          const int bitpos = __ffsll((long long)x) - 1;
-          x &= x - 1;
-          const long long key = (long long)(sk0 + bitpos - owner_off);
-          a.uniq[u] = key;
-          a.uniq_owner[u] = (uint8_t)owner;
-          a.uniq_row[u] = a.row_of[key];
-          a.cnt[u] = 0;
-          u++;
-        }
-      }
+      a.word_base[w0] = blk_base + e0;
+      a.word_base[w1] = blk_base + t0 + e1;
     }
   }
 }
@@ -131,61 +117,58 @@ __global__ void __launch_bounds__(kThreads) dedupe_rank(hctr_dedupe_args a) {
   const u64 below = a.bits[w] & ((1ull << (sk & 63)) - 1);
   const u32 u = a.word_base[w] + __popcll(below);
   a.idx_map[i] = (int32_t)u;
-  a.rank_in_run[i] = atomicAdd(&a.cnt[u], 1u);
+  const u32 rk = atomicAdd(&a.cnt[u], 1u);
+  a.rank_in_run[i] = rk;
+  if (rk == 0) {  // exactly one position per unique key
+    const long long key = a.keys[i];
+    a.uniq[u] = key;
+    a.uniq_owner[u] = a.owner_of[key];
+    a.uniq_row[u] = a.row_of[key];
+  }
 }
 
 __global__ void __launch_bounds__(kThreads) dedupe_scatter(hctr_dedupe_args a) {
   const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
   if (i >= a.batch) return;
   const u64 sk = a.sk[i];
-  if (sk == ~0ull) return;
+  if (sk == ~0ull) {
+    a.pos_row[i] = HCTR_INVALID_ROW;
+    return;
+  }
   const u32 u = (u32)a.idx_map[i];
-  a.sorted_pos[a.run_start[u] + a.rank_in_run[i]] = (u32)i;
-  // leave the persistent scratch all-zero for the next batch
-  a.bits[sk >> 6] = 0;
-  a.blk_cnt[sk >> 12] = 0;
+  const u32 rk = a.rank_in_run[i];
+  a.sorted_pos[a.run_start[u] + rk] = (u32)i;
+  a.pos_row[i] = a.uniq_row[u];
+  if (rk == 0) {
+    // leave the persistent scratch all-zero for the next batch (once per unique key)
+    a.bits[sk >> 6] = 0;
+    a.cnt[u] = 0;
+  }
+  // exactly one position per run longer than kLightRun sees this slot: it queues the run as "long"
+  // (at most batch/33 such runs exist; the list holds batch/32 + 2 entries)
+  if (rk == kLightRun) a.heavy_list[atomicAdd(&a.meta[HCTR_META_NHEAVY], 1u)] = u;
 }
 
-// Runs of 2..kLightRun positions: one thread sorts its run in registers/local memory.
-// Longer runs are queued for dedupe_order_heavy.
+// Runs of 2..kLightRun positions: one warp per unique key, one position per lane; a lane's final
+// slot is the number of smaller positions in the run (positions are distinct).
 __global__ void __launch_bounds__(kThreads) dedupe_order_light(hctr_dedupe_args a) {
-  const size_t u = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  const size_t u = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const unsigned lane = threadIdx.x & 31;
   if (u >= a.meta[HCTR_META_UNIQUE]) return;
   const u32 l = a.run_start[u], len = a.run_start[u + 1] - l;
-  if (len < 2) return;
+  if (len < 2 || len > kLightRun) return;  // longer runs: dedupe_order_heavy
   u32 *p = a.sorted_pos + l;
-  if (len == 2) {
-    const u32 x = p[0], y = p[1];
-    if (x > y) {
-      p[0] = y;
-      p[1] = x;
-    }
-    return;
-  }
-  if (len > kLightRun) {
-    const u32 slot = atomicAdd(&a.meta[HCTR_META_NHEAVY], 1u);
-    a.heavy_list[slot] = (u32)u;  // at most batch/33 such runs exist; the list holds batch/32+1
-    return;
-  }
-  u32 v[kLightRun];
-  for (u32 k = 0; k < len; k++) v[k] = p[k];
-  for (u32 k = 1; k < len; k++) {  // insertion sort
-    const u32 x = v[k];
-    u32 j = k;
-    while (j > 0 && v[j - 1] > x) {
-      v[j] = v[j - 1];
-      j--;
-    }
-    v[j] = x;
-  }
-  for (u32 k = 0; k < len; k++) p[k] = v[k];
+  const u32 v = lane < len ? p[lane] : 0xffffffffu;
+  u32 slot = 0;
+  for (u32 k = 0; k < len; k++) slot += __shfl_sync(0xffffffffu, v, k) < v ? 1u : 0u;
+  if (lane < len) p[slot] = v;
 }
 
 // Long runs: a CTA sets one bit per position in a shared-memory bitmap (window by window when the
 // batch exceeds the window), then emits the set bits in order.  Cost per run is O(batch/32) word
 // operations, independent of the run length, so even "all keys equal" stays cheap.
-__global__ void __launch_bounds__(1024) dedupe_order_heavy(hctr_dedupe_args a) {
-  extern __shared__ u32 win[];  // kHeavyWindowBits / 32 words
+__global__ void __launch_bounds__(1024) dedupe_order_heavy(hctr_dedupe_args a, u32 window_bits) {
+  extern __shared__ u32 win[];  // window_bits / 32 words
   __shared__ u32 warp_tot[32];
   __shared__ u32 carry;
   const u32 n_heavy = a.meta[HCTR_META_NHEAVY];
@@ -201,8 +184,8 @@ __global__ void __launch_bounds__(1024) dedupe_order_heavy(hctr_dedupe_args a) {
     for (u32 k = tid; k < len; k += 1024) stage[k] = p[k];
     if (tid == 0) carry = 0;
     __syncthreads();
-    for (size_t w0 = 0; w0 < batch; w0 += kHeavyWindowBits) {
-      const u32 wbits = (u32)min((size_t)kHeavyWindowBits, batch - w0);
+    for (size_t w0 = 0; w0 < batch; w0 += window_bits) {
+      const u32 wbits = (u32)min((size_t)window_bits, batch - w0);
       const u32 wwords = (wbits + 31) / 32;
       for (u32 k = tid; k < wwords; k += 1024) win[k] = 0;
       __syncthreads();
@@ -267,23 +250,61 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
     attr_set = true;
   }
   const unsigned gb = grid_for(a.batch, kThreads);
-  dedupe_mark<<<gb, kThreads, 0, s>>>(a);
+  int launches = 0;
+  // sample pass over the first 1/16 of the batch, then the rest
+  const size_t sample = a.batch >= 4096 ? a.batch / 16 : 0;
+  if (sample) {
+    dedupe_mark<<<grid_for(sample, kThreads), kThreads, 0, s>>>(a, 0, sample);
+    launches++;
+  }
+  if (a.batch > sample) {
+    dedupe_mark<<<grid_for(a.batch - sample, kThreads), kThreads, 0, s>>>(a, sample, a.batch - sample);
+    launches++;
+  }
   int rc = hctr_scan_exclusive_u32(a.blk_cnt, a.blk_base, n_blocks, nullptr, a.scan_scratch, stream);
   if (rc) return rc;
   {
-    size_t warps = (n_blocks + 31) / 32;
+    // aim for one resident wave of warps (148 SMs x 64 warps); beyond that let warps take wider groups
+    const size_t target_warps = (size_t)kSMs * 64;
+    unsigned group = 1;
+    while (group < 32 && (n_blocks + group - 1) / group > target_warps) group *= 2;
+    size_t warps = (n_blocks + group - 1) / group;
     size_t ctas = (warps * 32 + kThreads - 1) / kThreads;
     const size_t cap = (size_t)kSMs * 8;
     if (ctas > cap) ctas = cap;
     if (ctas == 0) ctas = 1;
-    dedupe_extract<<<(unsigned)ctas, kThreads, 0, s>>>(a, n_blocks, blocks_per_owner);
+    dedupe_extract<<<(unsigned)ctas, kThreads, 0, s>>>(a, n_blocks, blocks_per_owner, group);
   }
   dedupe_rank<<<gb, kThreads, 0, s>>>(a);
   rc = hctr_scan_exclusive_u32(a.cnt, a.run_start, a.batch, a.meta + HCTR_META_UNIQUE, a.scan_scratch, stream);
   if (rc) return rc;
   dedupe_scatter<<<gb, kThreads, 0, s>>>(a);
-  dedupe_order_light<<<gb, kThreads, 0, s>>>(a);
-  dedupe_order_heavy<<<kSMs, 1024, kHeavyWindowBits / 8, s>>>(a);
-  count_launches(6);
+  // short and long runs are disjoint slices of sorted_pos: with a second stream the two ordering
+  // kernels overlap
+  cudaStream_t hs = s;
+  if (a.side_stream && a.fork_event && a.join_event) {
+    hs = (cudaStream_t)a.side_stream;
+    cudaError_t e = cudaEventRecord((cudaEvent_t)a.fork_event, s);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(hs, (cudaEvent_t)a.fork_event, 0);
+    if (e != cudaSuccess) return (int)e;
+  }
+  dedupe_order_light<<<grid_for(a.batch * 32, kThreads), kThreads, 0, s>>>(a);
+  {
+    // window = the batch when it fits (small windows let several CTAs share an SM)
+    size_t wbits = (a.batch + 1023) / 1024 * 1024;
+    if (wbits > (size_t)kHeavyWindowBits) wbits = kHeavyWindowBits;
+    if (wbits < 1024) wbits = 1024;
+    const size_t smem = wbits / 8;
+    size_t per_sm = (200 * 1024) / (smem + 1024);
+    if (per_sm > 2) per_sm = 2;  // 1024-thread CTAs: at most 2 per SM
+    if (per_sm < 1) per_sm = 1;
+    dedupe_order_heavy<<<(unsigned)(kSMs * per_sm), 1024, smem, hs>>>(a, (u32)wbits);
+  }
+  if (hs != s) {
+    cudaError_t e = cudaEventRecord((cudaEvent_t)a.join_event, hs);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, (cudaEvent_t)a.join_event, 0);
+    if (e != cudaSuccess) return (int)e;
+  }
+  count_launches(launches + 5);
   return launch_status();
 }

@@ -115,9 +115,13 @@ __global__ void __launch_bounds__(kThreads) cache_refresh(size_t n_unique, size_
 
 // dst[i] = row of batch key i.  Row reads use default caching (duplicates and the rows just updated
 // hit L2); dst is written once and never re-read by this path, so it is stored evict-first.
+// A group moves kExpandRows rows per iteration so that several independent row reads are in flight
+// per lane; the source row comes straight from the per-position row index computed at preprocess.
+constexpr int kExpandRows = 4;
+
 template <int LANES, bool VEC>
-__global__ void __launch_bounds__(kThreads) expand_rows(size_t batch, size_t width, const int32_t *__restrict__ idx_map,
-                                                        const int32_t *__restrict__ uniq_row,
+__global__ void __launch_bounds__(kThreads) expand_rows(size_t batch, size_t width, const int32_t *__restrict__ pos_row,
+                                                        const int32_t *__restrict__ idx_map,
                                                         const u32 *__restrict__ recv_slot,
                                                         const float *__restrict__ recv_val,
                                                         const float *__restrict__ embedding,
@@ -127,17 +131,31 @@ __global__ void __launch_bounds__(kThreads) expand_rows(size_t batch, size_t wid
   const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
   const unsigned gl = threadIdx.x % LANES;
   const size_t E = R::elems(width);
-  for (size_t i = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; i < batch; i += groups) {
-    const int32_t u = idx_map[i];
-    T *out = reinterpret_cast<T *>(dst) + i * E;
-    if (u < 0) {  // key was out of range: the host reports the error; leave a defined value
-      for (size_t c = gl; c < E; c += LANES) R::st_once(out + c, R::zero());
-      continue;
+  for (size_t i0 = (((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES) * kExpandRows; i0 < batch;
+       i0 += groups * kExpandRows) {
+    const T *src[kExpandRows];
+#pragma unroll
+    for (int k = 0; k < kExpandRows; k++) {
+      src[k] = nullptr;
+      const size_t i = i0 + k;
+      if (i < batch) {
+        const int32_t row = pos_row[i];
+        if (row >= 0) {
+          src[k] = reinterpret_cast<const T *>(embedding) + (size_t)row * E;
+        } else {
+          const int32_t u = idx_map[i];  // < 0: key was out of range (the host reports it); write zeros
+          if (u >= 0 && recv_slot) src[k] = reinterpret_cast<const T *>(recv_val) + (size_t)recv_slot[u] * E;
+        }
+      }
     }
-    const int32_t row = uniq_row[u];
-    const T *src = row >= 0 ? reinterpret_cast<const T *>(embedding) + (size_t)row * E
-                            : reinterpret_cast<const T *>(recv_val) + (size_t)recv_slot[u] * E;
-    for (size_t c = gl; c < E; c += LANES) R::st_once(out + c, src[c]);
+    for (size_t c = gl; c < E; c += LANES) {
+      T v[kExpandRows];
+#pragma unroll
+      for (int k = 0; k < kExpandRows; k++) v[k] = src[k] ? src[k][c] : R::zero();
+#pragma unroll
+      for (int k = 0; k < kExpandRows; k++)
+        if (i0 + k < batch) R::st_once(reinterpret_cast<T *>(dst) + (i0 + k) * E + c, v[k]);
+    }
   }
 }
 
@@ -220,7 +238,7 @@ extern "C" int hctr_cache_refresh(size_t n_unique, size_t width, const uint8_t *
   return launch_status();
 }
 
-extern "C" int hctr_expand_rows(size_t batch, size_t width, const int32_t *idx_map, const int32_t *uniq_row,
+extern "C" int hctr_expand_rows(size_t batch, size_t width, const int32_t *pos_row, const int32_t *idx_map,
                                 const uint32_t *recv_slot, const float *recv_val, const float *embedding,
                                 float *dst, void *stream) {
   cudaStream_t s = (cudaStream_t)stream;
@@ -228,10 +246,10 @@ extern "C" int hctr_expand_rows(size_t batch, size_t width, const int32_t *idx_m
   const bool al = host_aligned16(recv_val) && host_aligned16(embedding) && host_aligned16(dst);
 #define CALL(L, V)                                                                       \
   do {                                                                                   \
-    size_t g_ = ((size_t)batch * L + kThreads - 1) / kThreads;                           \
+    size_t g_ = (((size_t)batch + kExpandRows - 1) / kExpandRows * L + kThreads - 1) / kThreads; \
     const size_t cap_ = (size_t)kSMs * 32;                                               \
     if (g_ > cap_) g_ = cap_;                                                            \
-    expand_rows<L, V><<<(unsigned)g_, kThreads, 0, s>>>(batch, width, idx_map, uniq_row, \
+    expand_rows<L, V><<<(unsigned)g_, kThreads, 0, s>>>(batch, width, pos_row, idx_map,  \
                                                         recv_slot, recv_val, embedding, dst); \
   } while (0)
   HCTR_DISPATCH_ROWS(width, al, CALL);

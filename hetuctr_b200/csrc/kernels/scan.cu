@@ -1,5 +1,5 @@
-// Exclusive prefix sum over 32-bit counts in three small launches (tile sums, scan of the tile
-// sums by one CTA, tile-local scan + base).  No spin-waits and no assumption on CTA dispatch
+// Exclusive prefix sum over 32-bit counts in two small launches (tile sums; tile-local scan + the sum
+// of the preceding tile sums, which every CTA adds up for itself).  No spin-waits and no assumption on CTA dispatch
 // order; the inputs on this path are at most a few million entries and L2-resident.
 #include "common.cuh"
 
@@ -52,23 +52,9 @@ __global__ void __launch_bounds__(kScanThreads) scan_tile_sums(const u32 *__rest
   if (threadIdx.x == 0) tile_sum[blockIdx.x] = total;
 }
 
-// One CTA: exclusive scan of the tile sums in place, chunk by chunk with a running carry.
-__global__ void __launch_bounds__(kScanThreads) scan_tile_bases(u32 *__restrict__ tile_sum, size_t n_tiles) {
-  __shared__ u32 total;
-  u32 carry = 0;
-  for (size_t c = 0; c < n_tiles; c += kScanThreads) {
-    size_t i = c + threadIdx.x;
-    u32 v = i < n_tiles ? tile_sum[i] : 0;
-    u32 ex = block_excl_scan(v, &total);
-    if (i < n_tiles) tile_sum[i] = carry + ex;
-    carry += total;
-    __syncthreads();
-  }
-}
-
 __global__ void __launch_bounds__(kScanThreads) scan_apply(const u32 *__restrict__ in, u32 *__restrict__ out,
                                                            size_t n_max, const u32 *__restrict__ n_dev,
-                                                           const u32 *__restrict__ tile_base) {
+                                                           const u32 *__restrict__ tile_sum) {
   const size_t n = n_dev ? min((size_t)*n_dev, n_max) : n_max;
   const size_t base = (size_t)blockIdx.x * HCTR_SCAN_TILE + (size_t)threadIdx.x * kScanItems;
   u32 v[kScanItems];
@@ -79,7 +65,12 @@ __global__ void __launch_bounds__(kScanThreads) scan_apply(const u32 *__restrict
     s += v[k];
   }
   __shared__ u32 total;
-  u32 ex = block_excl_scan(s, &total) + tile_base[blockIdx.x];
+  // base of this tile = sum of the tile sums before it (at most a few hundred values, L2-resident)
+  u32 before = 0;
+  for (unsigned t = threadIdx.x; t < blockIdx.x; t += kScanThreads) before += tile_sum[t];
+  __shared__ u32 base_total;
+  block_excl_scan(before, &base_total);
+  u32 ex = block_excl_scan(s, &total) + base_total;
 #pragma unroll
   for (int k = 0; k < kScanItems; k++) {
     if (base + k <= n) out[base + k] = ex;  // entry n receives the grand total
@@ -103,8 +94,7 @@ extern "C" int hctr_scan_exclusive_u32(const uint32_t *in, uint32_t *out, size_t
   // n+1 outputs: tiles cover [0, n_max]
   const size_t tiles = (n_max + 1 + HCTR_SCAN_TILE - 1) / HCTR_SCAN_TILE;
   scan_tile_sums<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, n_max, n_dev, scratch);
-  scan_tile_bases<<<1, kScanThreads, 0, s>>>(scratch, tiles);
   scan_apply<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n_max, n_dev, scratch);
-  count_launches(3);
+  count_launches(2);
   return launch_status();
 }

@@ -10,7 +10,7 @@ constexpr int kThreads = 256;
 __global__ void __launch_bounds__(kThreads) push_decide(const u32 *__restrict__ meta, int rank,
                                                         const uint8_t *__restrict__ uniq_owner,
                                                         const int32_t *__restrict__ uniq_row,
-                                                        const u32 *__restrict__ cnt,
+                                                        const u32 *__restrict__ run_start,
                                                         const long long *__restrict__ pending_cnt,
                                                         long long push_bound, u32 *__restrict__ need_push) {
   const size_t u = (size_t)blockIdx.x * kThreads + threadIdx.x;
@@ -19,7 +19,7 @@ __global__ void __launch_bounds__(kThreads) push_decide(const u32 *__restrict__ 
   const int32_t row = uniq_row[u];
   if (uniq_owner[u] == rank) need = 0;
   else if (row < 0) need = 1;
-  else need = (pending_cnt[row] + (long long)cnt[u] <= push_bound) ? 0u : 1u;
+  else need = (pending_cnt[row] + (long long)(run_start[u + 1] - run_start[u]) <= push_bound) ? 0u : 1u;
   need_push[u] = need;
 }
 
@@ -33,52 +33,92 @@ __global__ void push_counts(const u32 *__restrict__ meta, int nrank, const u32 *
 }
 
 // ---- reduce + apply + pack -------------------------------------------------------------------
-// One group of LANES lanes per unique key of the previous batch.  The duplicate sum runs over the
-// key's positions in ascending batch order, then one multiply by -lr: the reference's order of
-// operations (csrc/core/generate_query.cu:34-40), so single-rank results are bit-identical.
-template <int LANES, bool VEC>
-__global__ void __launch_bounds__(kThreads) grad_reduce_apply_pack(hctr_reduce_args a) {
-  typedef RowT<VEC> R;
-  typedef typename R::T T;
-  const size_t gid = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES;
-  const unsigned gl = threadIdx.x % LANES;
-  if (gid >= a.n_unique) return;
-  const size_t u = gid;
-  const int32_t row = a.uniq_row[u];
-  const bool need = a.need_push ? a.need_push[u] != 0 : false;
-  int type;
-  if (row < 0) type = 0;                           // not stored: push the batch sum
-  else if ((size_t)row >= a.n_cached) type = 1;    // owned: apply
-  else type = need ? 2 : 3;                        // cached: apply + accumulate (+ push and clear)
-  const u32 l = a.run_start[u], r = a.run_start[u + 1];
-  const size_t slot = need ? a.push_slot[u] : 0;
+// For every unique key of the previous batch: s = (sum of its gradient rows, in ascending batch
+// position) * (-lr), then the update its storage class asks for.  The sum order and the single
+// multiply are the reference's (csrc/core/generate_query.cu:34-40), so results are bit-identical
+// to a sequential evaluation.
+//   type 0  not stored      -> push s
+//   type 1  owned           -> emb += s, version += count
+//   type 2  cached, push    -> emb += s, pending += s, push pending, clear it, version += pending count
+//   type 3  cached, hold    -> emb += s, pending += s, pending count += count
 
-  if (gl == 0) {
-    long long c = (long long)(r - l);
-    if (type == 1) a.version[row] = (long long)((u64)a.version[row] + (u64)c);
-    else if (type >= 2) {
-      long long pc = a.pending_cnt[row] + c;
-      if (type == 2) {
+struct RowTarget {
+  int type;
+  size_t slot;
+  int32_t row;
+};
+
+// bookkeeping of one unique key (one thread): versions, pending counts, packed id + update count
+__device__ __forceinline__ RowTarget reduce_bookkeeping(const hctr_reduce_args &a, size_t u, u32 count, bool lead) {
+  RowTarget t;
+  t.row = a.uniq_row[u];
+  const bool need = a.need_push ? a.need_push[u] != 0 : false;
+  if (t.row < 0) t.type = 0;
+  else if ((size_t)t.row >= a.n_cached) t.type = 1;
+  else t.type = need ? 2 : 3;
+  t.slot = need ? a.push_slot[u] : 0;
+  if (lead) {
+    long long c = (long long)count;
+    if (t.type == 1) a.version[t.row] = (long long)((u64)a.version[t.row] + (u64)c);
+    else if (t.type >= 2) {
+      long long pc = a.pending_cnt[t.row] + c;
+      if (t.type == 2) {
         c = pc;
         pc = 0;
-        a.version[row] = (long long)((u64)a.version[row] + (u64)c);
+        a.version[t.row] = (long long)((u64)a.version[t.row] + (u64)c);
       }
-      a.pending_cnt[row] = pc;
+      a.pending_cnt[t.row] = pc;
     }
     if (need) {
-      a.push_key[slot] = a.uniq[u];
-      a.push_updates[slot] = c;
+      a.push_key[t.slot] = a.uniq[u];
+      a.push_updates[t.slot] = c;
     }
   }
+  return t;
+}
 
+template <class R>
+__device__ __forceinline__ void reduce_apply(const RowTarget &t, typename R::T sum, typename R::T *emb,
+                                             typename R::T *pend, typename R::T *out, size_t c) {
+  if (t.type == 0) {
+    out[c] = sum;
+  } else {
+    emb[c] = R::add(emb[c], sum);
+    if (t.type >= 2) {
+      const typename R::T p = R::add(pend[c], sum);
+      if (t.type == 2) {
+        out[c] = p;
+        pend[c] = R::zero();
+      } else {
+        pend[c] = p;
+      }
+    }
+  }
+}
+
+// Short runs (<= HCTR_LIGHT_RUN positions): one group of LANES lanes per unique key.
+template <int LANES, bool VEC>
+__global__ void __launch_bounds__(kThreads) grad_reduce_short(hctr_reduce_args a) {
+  typedef RowT<VEC> R;
+  typedef typename R::T T;
+  const size_t u = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES;
+  const unsigned gl = threadIdx.x % LANES;
+  if (u >= a.n_unique) return;
+  const u32 l = a.run_start[u], r = a.run_start[u + 1];
+  if (r - l > HCTR_LIGHT_RUN) return;  // handled by grad_reduce_long
+  const RowTarget t = reduce_bookkeeping(a, u, r - l, gl == 0);
   const size_t E = R::elems(a.width);
   const T *grad = reinterpret_cast<const T *>(a.grad);
-  T *emb = reinterpret_cast<T *>(a.embedding) + (row >= 0 ? (size_t)row * E : 0);
-  T *pend = reinterpret_cast<T *>(a.pending) + (type >= 2 ? (size_t)row * E : 0);
-  T *out = reinterpret_cast<T *>(a.push_val) + slot * E;
+  T *emb = reinterpret_cast<T *>(a.embedding) + (t.row >= 0 ? (size_t)t.row * E : 0);
+  T *pend = reinterpret_cast<T *>(a.pending) + (t.type >= 2 ? (size_t)t.row * E : 0);
+  T *out = reinterpret_cast<T *>(a.push_val) + t.slot * E;
   for (size_t c = gl; c < E; c += LANES) {
     T sum = R::zero();
     u32 j = l;
+    // the table row does not depend on the gradient chain: start its load first
+    T e_old = R::zero(), p_old = R::zero();
+    if (t.type != 0) e_old = emb[c];
+    if (t.type >= 2) p_old = pend[c];
     // 4 independent loads in flight per lane; adds stay in position order
     for (; j + 4 <= r; j += 4) {
       const T g0 = R::ld_once(grad + (size_t)a.sorted_pos[j] * E + c);
@@ -89,18 +129,119 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_apply_pack(hctr_reduce_a
     }
     for (; j < r; j++) sum = R::add(sum, R::ld_once(grad + (size_t)a.sorted_pos[j] * E + c));
     sum = R::scale(sum, a.neg_lr);
-    if (type == 0) {
+    if (t.type == 0) {
       out[c] = sum;
     } else {
-      emb[c] = R::add(emb[c], sum);
-      if (type >= 2) {
-        const T p = R::add(pend[c], sum);
-        if (type == 2) {
+      emb[c] = R::add(e_old, sum);
+      if (t.type >= 2) {
+        const T p = R::add(p_old, sum);
+        if (t.type == 2) {
           out[c] = p;
           pend[c] = R::zero();
         } else {
           pend[c] = p;
         }
+      }
+    }
+  }
+}
+
+// Long runs (hot keys, up to the whole batch): one CTA per key.  All threads stream the key's
+// gradient rows into a ring of shared-memory stages with cp.async (16-byte copies, several stages in
+// flight), and one thread per row element adds the staged rows in order.  The sequential sum of a
+// 1000-row run becomes shared-memory-latency bound instead of DRAM-latency bound, without
+// reassociating it.  CTAs take keys from a shared counter, so a CTA that drew short runs moves on.
+constexpr int kLongThreads = 256;
+constexpr int kLongWarps = kLongThreads / 32;
+constexpr int kLongStages = 4;
+constexpr int kLongStageBytes = 16 * 1024;
+constexpr int kLongPosChunk = 2048;  // positions staged in shared memory at a time
+
+template <bool VEC>
+__device__ __forceinline__ void cp_async_elem(void *smem_dst, const void *gsrc) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
+  if (VEC) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gsrc) : "memory");
+  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gsrc) : "memory");
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kLongThreads) grad_reduce_long(hctr_reduce_args a, u32 n_heavy, u32 *work_counter) {
+  typedef RowT<VEC> R;
+  typedef typename R::T T;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ u32 pos_s[kLongPosChunk];
+  __shared__ u32 next_item;
+  const size_t E = R::elems(a.width);  // T elements per row
+  const size_t W = a.width;            // floats per row
+  const u32 rows_per_stage = (u32)max((size_t)1, (size_t)kLongStageBytes / (W * sizeof(float)));
+  const size_t stage_elems = (size_t)rows_per_stage * E;
+  const size_t stage_floats = (size_t)rows_per_stage * W;
+  T *stage = reinterpret_cast<T *>(smem_raw);
+  const float *stage_f = reinterpret_cast<const float *>(smem_raw);
+  const T *grad = reinterpret_cast<const T *>(a.grad);
+  const unsigned tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // lanes per row for the copies: a power of two <= 32 covering the row when it is narrow
+  unsigned lpr = 32;
+  while (lpr > 1 && (size_t)(lpr / 2) >= E) lpr /= 2;
+  const unsigned rows_per_warp_iter = 32 / lpr, sub = lane / lpr, sl = lane % lpr;
+
+  for (;;) {
+    __syncthreads();
+    if (tid == 0) next_item = atomicAdd(work_counter, 1u);
+    __syncthreads();
+    const u32 h = next_item;
+    if (h >= n_heavy) break;
+    const size_t u = a.heavy_list[h];
+    const u32 l = a.run_start[u], len = a.run_start[u + 1] - l;
+    const RowTarget t = reduce_bookkeeping(a, u, len, tid == 0);
+    // columns are processed in slabs of up to 4 per thread (width <= 1024 needs a single pass)
+    for (size_t col0 = 0; col0 < W; col0 += 4 * kLongThreads) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (u32 p0 = 0; p0 < len; p0 += kLongPosChunk) {
+        const u32 plen = min((u32)kLongPosChunk, len - p0);
+        __syncthreads();
+        for (u32 k = tid; k < plen; k += kLongThreads) pos_s[k] = a.sorted_pos[l + p0 + k];
+        __syncthreads();
+        const u32 n_tiles = (plen + rows_per_stage - 1) / rows_per_stage;
+        auto issue = [&](u32 tile) {
+          if (tile < n_tiles) {
+            const u32 r0 = tile * rows_per_stage;
+            const u32 nr = min(rows_per_stage, plen - r0);
+            T *dst = stage + (size_t)(tile % kLongStages) * stage_elems;
+            for (u32 rr = warp * rows_per_warp_iter + sub; rr < nr; rr += kLongWarps * rows_per_warp_iter) {
+              const T *src = grad + (size_t)pos_s[r0 + rr] * E;
+              for (size_t cc = sl; cc < E; cc += lpr) cp_async_elem<VEC>(dst + (size_t)rr * E + cc, src + cc);
+            }
+          }
+          asm volatile("cp.async.commit_group;\n" ::: "memory");  // one group per tile slot, even if empty
+        };
+        for (int p = 0; p < kLongStages - 1; p++) issue(p);
+        for (u32 tile = 0; tile < n_tiles; tile++) {
+          issue(tile + kLongStages - 1);
+          asm volatile("cp.async.wait_group %0;\n" ::"n"(kLongStages - 1) : "memory");
+          __syncthreads();  // every thread's copies of this tile have landed
+          const u32 nr = min(rows_per_stage, plen - tile * rows_per_stage);
+          const float *src = stage_f + (size_t)(tile % kLongStages) * stage_floats;
+#pragma unroll
+          for (int k = 0; k < 4; k++) {
+            const size_t col = col0 + tid + (size_t)k * kLongThreads;
+            if (col < W) {
+              float sacc = acc[k];
+              for (u32 rr = 0; rr < nr; rr++) sacc = __fadd_rn(sacc, src[(size_t)rr * W + col]);
+              acc[k] = sacc;
+            }
+          }
+          __syncthreads();  // the stage may be refilled by the next issue
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+      }
+      float *emb = a.embedding + (t.row >= 0 ? (size_t)t.row * W : 0);
+      float *pend = a.pending + (t.type >= 2 ? (size_t)t.row * W : 0);
+      float *out = a.push_val + t.slot * W;
+#pragma unroll
+      for (int k = 0; k < 4; k++) {
+        const size_t col = col0 + tid + (size_t)k * kLongThreads;
+        if (col < W) reduce_apply<RowT<false>>(t, __fmul_rn(acc[k], a.neg_lr), emb, pend, out, col);
       }
     }
   }
@@ -138,13 +279,13 @@ __global__ void __launch_bounds__(kThreads) owner_update(size_t n_rows, size_t w
 using namespace hctr;
 
 extern "C" int hctr_push_decide(const uint32_t *meta, int nrank, int rank, size_t u_max,
-                                const uint8_t *uniq_owner, const int32_t *uniq_row, const uint32_t *cnt,
+                                const uint8_t *uniq_owner, const int32_t *uniq_row, const uint32_t *run_start,
                                 const int64_t *pending_cnt, int64_t push_bound, uint32_t *need_push,
                                 uint32_t *push_slot, uint32_t *scan_scratch, uint32_t *push_count,
                                 void *stream) {
   cudaStream_t s = (cudaStream_t)stream;
   if (nrank > 1024) return (int)cudaErrorInvalidValue;
-  push_decide<<<grid_for(u_max, kThreads), kThreads, 0, s>>>(meta, rank, uniq_owner, uniq_row, cnt,
+  push_decide<<<grid_for(u_max, kThreads), kThreads, 0, s>>>(meta, rank, uniq_owner, uniq_row, run_start,
                                                               (const long long *)pending_cnt, push_bound,
                                                               need_push);
   int rc = hctr_scan_exclusive_u32(need_push, push_slot, u_max, meta + HCTR_META_UNIQUE, scan_scratch, stream);
@@ -160,11 +301,48 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
   if (a.n_unique == 0) return 0;
   const bool al = host_aligned16(a.grad) && host_aligned16(a.embedding) && host_aligned16(a.pending) &&
                   host_aligned16(a.push_val);
+  if (a.n_heavy > 0 && a.side_stream && a.fork_event && a.join_event) {
+    cudaError_t e = cudaEventRecord((cudaEvent_t)a.fork_event, s);
+    if (e != cudaSuccess) return (int)e;
+  }
 #define CALL(L, V) \
-  grad_reduce_apply_pack<L, V><<<grid_for(a.n_unique * L, kThreads), kThreads, 0, s>>>(a)
+  grad_reduce_short<L, V><<<grid_for(a.n_unique * L, kThreads), kThreads, 0, s>>>(a)
   HCTR_DISPATCH_ROWS(a.width, al, CALL);
 #undef CALL
   count_launches(1);
+  if (a.n_heavy > 0) {
+    static bool attr_set = false;
+    const int smem = kLongStages * kLongStageBytes + 4096;  // + slack for rows wider than a stage
+    size_t need = (size_t)kLongStages * max((size_t)kLongStageBytes, a.width * sizeof(float));
+    if (need > 200 * 1024) return (int)cudaErrorInvalidValue;  // rows wider than 12800 floats
+    if (!attr_set) {
+      cudaError_t e1 = cudaFuncSetAttribute(grad_reduce_long<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      cudaError_t e2 = cudaFuncSetAttribute(grad_reduce_long<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (e1 != cudaSuccess) return (int)e1;
+      if (e2 != cudaSuccess) return (int)e2;
+      attr_set = true;
+    }
+    (void)smem;
+    // The long-run kernel touches other keys than the short-run kernel, so the two may overlap: when
+    // the caller provides a second stream and two events, the long runs are forked onto it.
+    cudaStream_t ls = s;
+    if (a.side_stream && a.fork_event && a.join_event) {
+      ls = (cudaStream_t)a.side_stream;
+      cudaError_t e = cudaStreamWaitEvent(ls, (cudaEvent_t)a.fork_event, 0);
+      if (e != cudaSuccess) return (int)e;
+    }
+    cudaError_t em = cudaMemsetAsync(a.work_counter, 0, sizeof(u32), ls);
+    if (em != cudaSuccess) return (int)em;
+    const unsigned grid = (unsigned)min((size_t)a.n_heavy, (size_t)kSMs * 3);
+    if (al && a.width % 4 == 0) grad_reduce_long<true><<<grid, kLongThreads, need, ls>>>(a, (u32)a.n_heavy, a.work_counter);
+    else grad_reduce_long<false><<<grid, kLongThreads, need, ls>>>(a, (u32)a.n_heavy, a.work_counter);
+    count_launches(1);
+    if (ls != s) {
+      cudaError_t e = cudaEventRecord((cudaEvent_t)a.join_event, ls);
+      if (e == cudaSuccess) e = cudaStreamWaitEvent(s, (cudaEvent_t)a.join_event, 0);
+      if (e != cudaSuccess) return (int)e;
+    }
+  }
   return launch_status();
 }
 

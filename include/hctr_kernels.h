@@ -40,6 +40,7 @@ extern "C" {
 #define HCTR_BLOCK_WORDS 64
 #define HCTR_BLOCK_KEYS 4096
 #define HCTR_SCAN_TILE 4096
+#define HCTR_LIGHT_RUN 32 /* runs up to this many positions are "short" */
 
 /* Kernels this library has enqueued since it was loaded (all launchers, all streams). */
 unsigned long long hctr_launch_count(void);
@@ -105,27 +106,33 @@ typedef struct hctr_dedupe_args {
   /* persistent scratch, all-zero between calls */
   unsigned long long *bits; /* [nrank*length_pad/64] */
   uint32_t *blk_cnt;        /* [nrank*length_pad/4096 + 1] distinct keys per bitmap block */
+  uint32_t *cnt;            /* [B+1] occurrences per unique key (consumed by the run-start scan) */
   /* scratch that needs no initial value */
   uint32_t *blk_base;       /* [nblocks + 1] */
   uint32_t *word_base;      /* [nrank*length_pad/64] */
   uint32_t *scan_scratch;   /* hctr_scan_scratch_words(max(nblocks, B) + 1) */
   unsigned long long *sk;   /* [B] sort keys */
   uint32_t *rank_in_run;    /* [B] */
-  uint32_t *heavy_list;     /* [B/32 + 1] */
   /* outputs */
   int64_t *uniq;            /* [B] unique keys, owner-major, key ascending */
   uint8_t *uniq_owner;      /* [B] */
   int32_t *uniq_row;        /* [B] local row or HCTR_INVALID_ROW */
-  uint32_t *cnt;            /* [B+1] occurrences per unique */
-  uint32_t *run_start;      /* [B+1] exclusive scan of cnt */
+  uint32_t *run_start;      /* [B+1] first slot of each unique key's run in sorted_pos; entry U = batch */
   uint32_t *sorted_pos;     /* [B] batch positions grouped by unique, ascending inside a group */
   int32_t *idx_map;         /* [B] batch position -> unique index */
+  int32_t *pos_row;         /* [B] batch position -> local row or HCTR_INVALID_ROW */
+  uint32_t *heavy_list;     /* [B/32 + 2] unique indices whose run is longer than HCTR_LIGHT_RUN */
   uint32_t *meta;           /* [HCTR_META_WORDS + nrank + 1]: see HCTR_META_* */
+  /* optional: a second stream (cudaStream_t) and two events (cudaEvent_t) that let the two run-ordering
+   * kernels overlap; null = everything on the call's stream */
+  void *side_stream;
+  void *fork_event;
+  void *join_event;
 } hctr_dedupe_args;
 
 #define HCTR_META_UNIQUE 0   /* number of unique keys U                         */
 #define HCTR_META_ERR 1      /* error word (HCTR_ERR_*)                         */
-#define HCTR_META_NHEAVY 2   /* scratch: number of long runs                    */
+#define HCTR_META_NHEAVY 2   /* number of runs longer than HCTR_LIGHT_RUN       */
 #define HCTR_META_SEG 4      /* seg_start[0..nrank]: first unique of each owner */
 #define HCTR_META_WORDS 4
 
@@ -139,11 +146,12 @@ int hctr_dedupe_map(const hctr_dedupe_args *a, void *stream);
  * csrc/core/preprocess.cu:148-182.
  * ------------------------------------------------------------------------------------------- */
 
-/* need_push[u] = 0 if owner==rank; 1 if not stored; else pending_cnt[row] + cnt[u] > push_bound.
+/* need_push[u] = 0 if owner==rank; 1 if not stored; else pending_cnt[row] + occurrences(u) > push_bound,
+ * with occurrences(u) = run_start[u+1] - run_start[u].
  * Then push_slot = exclusive scan of need_push (U+1 entries) and push_count[p] = pushes to owner p.
  * U is read from meta (device). */
 int hctr_push_decide(const uint32_t *meta, int nrank, int rank, size_t u_max, const uint8_t *uniq_owner,
-                     const int32_t *uniq_row, const uint32_t *cnt, const int64_t *pending_cnt,
+                     const int32_t *uniq_row, const uint32_t *run_start, const int64_t *pending_cnt,
                      int64_t push_bound, uint32_t *need_push, uint32_t *push_slot,
                      uint32_t *scan_scratch, uint32_t *push_count, void *stream);
 
@@ -165,6 +173,8 @@ typedef struct hctr_reduce_args {
   const float *grad;          /* [B_prev, W] caller's gradients */
   const uint32_t *run_start;  /* [U+1] */
   const uint32_t *sorted_pos; /* [B_prev] */
+  const uint32_t *heavy_list; /* unique indices whose run is longer than HCTR_LIGHT_RUN */
+  size_t n_heavy;             /* entries in heavy_list (host value) */
   const int64_t *uniq;        /* [U] */
   const int32_t *uniq_row;    /* [U] */
   const uint32_t *need_push;  /* [U] or null when nrank==1 */
@@ -176,6 +186,12 @@ typedef struct hctr_reduce_args {
   int64_t *push_key;          /* [P] packed ids of pushed rows */
   int64_t *push_updates;      /* [P] update counts */
   float *push_val;            /* [P, W] */
+  uint32_t *work_counter;     /* one device word of scratch (needed when n_heavy > 0) */
+  /* optional: a second stream (cudaStream_t) and two events (cudaEvent_t, timing disabled) that let
+   * the long-run kernel overlap the short-run kernel; null = everything on the call's stream */
+  void *side_stream;
+  void *fork_event;
+  void *join_event;
 } hctr_reduce_args;
 
 int hctr_grad_reduce_apply_pack(const hctr_reduce_args *a, void *stream);
@@ -229,9 +245,10 @@ int hctr_cache_refresh(size_t n_unique, size_t width, const uint8_t *flags, cons
                        const int32_t *uniq_row, const float *recv_val, const int64_t *recv_version,
                        const float *pending, float *embedding, int64_t *version, void *stream);
 
-/* dst[i] = row of keys[i]: from the local table when stored, else from the receive buffer.
- * recv_slot / recv_val may be null when every key is stored locally (single-rank tables). */
-int hctr_expand_rows(size_t batch, size_t width, const int32_t *idx_map, const int32_t *uniq_row,
+/* dst[i] = row of keys[i]: from the local table when stored (pos_row[i] >= 0), else from the receive
+ * buffer at recv_slot[idx_map[i]].  recv_slot / recv_val may be null when every key is stored locally
+ * (single-rank tables). */
+int hctr_expand_rows(size_t batch, size_t width, const int32_t *pos_row, const int32_t *idx_map,
                      const uint32_t *recv_slot, const float *recv_val, const float *embedding,
                      float *dst, void *stream);
 

@@ -127,10 +127,15 @@ def test_out_of_range_key_raises_and_table_recovers(oracle_mod):
     N, W = 300, 4
     root = np.zeros(N, dtype=np.uint8)
     gw, ow = make_worlds(oracle_mod, 1, N, W, 0, 0, 0.1, root, [np.arange(N)])
-    with pytest.raises(RuntimeError):
+    # A single-rank table reports a bad key from the first call that synchronises with the device
+    # (push_pull, or the next preprocess); multi-rank tables report it from preprocess itself.
+    with pytest.raises(RuntimeError, match="outside"):
         gw.preprocess([[1, 2, N, 5]])
-    with pytest.raises(RuntimeError):
+        gw.push_pull(None)
+    with pytest.raises(RuntimeError, match="outside"):
         gw.preprocess([[-1]])
+        gw.preprocess([[1]])
+    gw.push_pull(None)
     rng = np.random.RandomState(6)
     batches = [[rng.randint(N, size=64)] for _ in range(3)]
     grads = [None] + [[rng.normal(0, 1, size=(64, W)).astype(np.float32)] for _ in range(2)]
