@@ -74,7 +74,12 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
   HCTR_CHECK(device_id >= 0 && device_id < num_gpus, "InCorrect device number.");
   HCTR_CUDA(cudaSetDevice(device_id_));
   HCTR_CUDA(cudaStreamCreateWithFlags(&stream_main_, cudaStreamNonBlocking));
-  HCTR_CUDA(cudaStreamCreateWithFlags(&stream_side_, cudaStreamNonBlocking));
+  {
+    // the side stream carries the few long-run CTAs that should start ahead of the bulk kernels
+    int lo = 0, hi = 0;
+    HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_side_, cudaStreamNonBlocking, hi));
+  }
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_keys_, cudaEventDisableTiming | cudaEventBlockingSync));
@@ -186,7 +191,9 @@ void HetuTable::initTable(const worker_t *root, const index_t *storage) {
   d_blk_cnt_.ensure((blocks + 1) * sizeof(uint32_t));
   d_blk_base_.ensure((blocks + 1) * sizeof(uint32_t));
   HCTR_CUDA(cudaMemsetAsync(d_bits_.p, 0, d_bits_.bytes, stream_main_));
+  d_blk_flag_.ensure(blocks + 1);
   HCTR_CUDA(cudaMemsetAsync(d_blk_cnt_.p, 0, d_blk_cnt_.bytes, stream_main_));
+  HCTR_CUDA(cudaMemsetAsync(d_blk_flag_.p, 0, d_blk_flag_.bytes, stream_main_));
   HCTR_CUDA(cudaStreamSynchronize(stream_main_));
 }
 
@@ -265,6 +272,7 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   a.row_of = d_row_of_.as<int32_t>();
   a.bits = d_bits_.as<unsigned long long>();
   a.blk_cnt = d_blk_cnt_.as<uint32_t>();
+  a.blk_flag = d_blk_flag_.as<uint8_t>();
   a.blk_base = d_blk_base_.as<uint32_t>();
   a.word_base = d_word_base_.as<uint32_t>();
   a.scan_scratch = d_scan_.as<uint32_t>();
@@ -774,7 +782,7 @@ void HetuTable::releaseAll() {
   if (stream_main_) cudaStreamSynchronize(stream_main_);
   transport_.reset();
   DevBuf *all[] = {&d_embedding_, &d_gradient_, &d_updates_, &d_version_, &d_root_, &d_row_of_, &d_stored_keys_,
-                   &d_bits_, &d_blk_cnt_, &d_blk_base_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_cnt_,
+                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_blk_base_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_cnt_,
                    &d_need_push_, &d_push_slot_, &d_push_count_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
                    &d_qkey_r_, &d_qver_r_, &d_pkey_s_, &d_pupd_s_, &d_pval_s_, &d_pkey_r_, &d_pupd_r_, &d_pval_r_,
                    &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,

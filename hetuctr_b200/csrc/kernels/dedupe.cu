@@ -4,9 +4,10 @@
 // The key space is dense ([0, length) with a 1-byte owner per key), so instead of sorting
 // (owner,key,position) triples the batch is RANKED through a bitmap over the sort-key space
 //     sk = key + length_pad * owner          (length_pad = length rounded up to 4096)
-//   mark     one bit per distinct sk (atomicOr); the first setter bumps its 4096-key block's count.
-//            A 1/16 sample of the batch is marked by a first launch, so that in the main launch the
-//            duplicates of hot keys find their bit already set and skip the atomic.
+//   mark     one bit per distinct sk (atomicOr); the first setter flags its 4096-key block as touched
+//   count    one warp per touched block: popcount of its 64 words = distinct keys in the block
+//            (counting by popcount instead of an atomic per key keeps dense blocks - small
+//            vocabularies are contiguous key ranges - from serialising on one counter)
 //   scan     block counts -> block bases                         (hctr_scan_exclusive_u32)
 //   extract  one warp per non-empty block: popcount prefix inside the block gives every 64-key word
 //            the rank of its first set bit = index in the sorted unique list
@@ -27,15 +28,15 @@ constexpr int kThreads = 256;
 constexpr u32 kLightRun = HCTR_LIGHT_RUN;  // runs up to this length are ordered by one warp
 constexpr int kHeavyWindowBits = 1 << 20;  // positions covered by one shared-memory window (128 KB)
 
-// positions [first, first + count)
-__global__ void __launch_bounds__(kThreads) dedupe_mark(hctr_dedupe_args a, size_t first, size_t count) {
-  const size_t t = (size_t)blockIdx.x * kThreads + threadIdx.x;
-  if (t >= count) return;
-  const size_t i = first + t;
+// The kernel is a chain of dependent memory operations per position (key -> owner -> bitmap word ->
+// atomic), so it is latency-bound; a single-rank table skips the owner lookup (every key is rank 0's).
+__global__ void __launch_bounds__(kThreads) dedupe_mark(hctr_dedupe_args a) {
+  const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i >= a.batch) return;
   const long long key = a.keys[i];
   unsigned o = 0;
   bool ok = key >= 0 && (size_t)key < a.length;
-  if (ok) {
+  if (ok && a.nrank > 1) {
     o = a.owner_of[key];
     ok = o < (unsigned)a.nrank;
   }
@@ -46,11 +47,42 @@ __global__ void __launch_bounds__(kThreads) dedupe_mark(hctr_dedupe_args a, size
   }
   const u64 sk = (u64)key + (u64)a.length_pad * o;
   a.sk[i] = sk;
-  const u64 bit = 1ull << (sk & 63);
-  u64 *word = a.bits + (sk >> 6);
-  if (*(volatile u64 *)word & bit) return;  // already marked (by the sample pass or an earlier duplicate)
-  const u64 old = atomicOr(word, bit);
-  if (!(old & bit)) atomicAdd(&a.blk_cnt[sk >> 12], 1u);
+  // the bitmap is addressed as 32-bit words here (little-endian halves of the 64-bit words)
+  const u32 bit = 1u << (sk & 31);
+  u32 *word = reinterpret_cast<u32 *>(a.bits) + (sk >> 5);
+  // Pre-check with an ordinary (L1-cacheable) load: a stale "unset" only costs a redundant atomic, and
+  // the thousands of positions that hit the few cache lines of a small vocabulary are served by L1
+  // instead of queueing on one L2 slice.
+  if (*word & bit) return;  // already marked by an earlier duplicate
+  const u32 old = atomicOr(word, bit);
+  if (!(old & bit)) a.blk_flag[sk >> 12] = 1;
+}
+
+// blk_cnt[b] = popcount of block b's 64 words for touched blocks (flag consumed), 0 elsewhere.
+__global__ void __launch_bounds__(kThreads) dedupe_count(hctr_dedupe_args a, size_t n_blocks, unsigned group) {
+  const unsigned lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const size_t n_warps = ((size_t)gridDim.x * kThreads) >> 5;
+  for (size_t g = warp * group; g < n_blocks; g += n_warps * group) {
+    const size_t b = g + lane;
+    bool touched = false;
+    if (lane < group && b < n_blocks) {
+      touched = a.blk_flag[b] != 0;
+      if (touched) a.blk_flag[b] = 0;
+      else a.blk_cnt[b] = 0;
+    }
+    unsigned live = __ballot_sync(0xffffffffu, touched);
+    while (live) {
+      const int src = __ffs(live) - 1;
+      live &= live - 1;
+      const size_t blk = g + src;
+      const size_t w0 = blk * HCTR_BLOCK_WORDS + lane;
+      u32 c = __popcll(a.bits[w0]) + __popcll(a.bits[w0 + 32]);
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
+      if (lane == 0) a.blk_cnt[blk] = c;
+    }
+  }
 }
 
 __device__ __forceinline__ u32 warp_excl_scan_total(u32 v, u32 *total) {
@@ -68,7 +100,7 @@ __device__ __forceinline__ u32 warp_excl_scan_total(u32 v, u32 *total) {
 // Each warp walks groups of `group` (1..32) consecutive bitmap blocks; lanes fetch the counts/bases of a
 // group at once and the warp then ranks the words of the non-empty blocks.  Small tables use group = 1
 // (one warp per block, maximum parallelism); huge, sparsely hit tables use 32 so that empty blocks
-// cost one coalesced load per 32.  Block counts are cleared on the way (they are consumed here).
+// cost one coalesced load per 32.
 __global__ void __launch_bounds__(kThreads) dedupe_extract(hctr_dedupe_args a, size_t n_blocks,
                                                            size_t blocks_per_owner, unsigned group) {
   const unsigned lane = threadIdx.x & 31;
@@ -85,7 +117,6 @@ __global__ void __launch_bounds__(kThreads) dedupe_extract(hctr_dedupe_args a, s
     if (lane < group && b < n_blocks) {
       c = a.blk_cnt[b];
       base = a.blk_base[b];
-      if (c) a.blk_cnt[b] = 0;
       if (b % blocks_per_owner == 0) a.meta[HCTR_META_SEG + b / blocks_per_owner] = base;
     }
     unsigned live = __ballot_sync(0xffffffffu, c != 0);
@@ -149,19 +180,33 @@ __global__ void __launch_bounds__(kThreads) dedupe_scatter(hctr_dedupe_args a) {
   if (rk == kLightRun) a.heavy_list[atomicAdd(&a.meta[HCTR_META_NHEAVY], 1u)] = u;
 }
 
-// Runs of 2..kLightRun positions: one warp per unique key, one position per lane; a lane's final
-// slot is the number of smaller positions in the run (positions are distinct).
+// Runs of 2..kLightRun positions.  A warp takes 32 consecutive unique keys (run bounds fetched
+// coalesced, one key per lane), then orders the runs that need it one after the other: one position
+// per lane, a lane's final slot = number of smaller positions in the run (positions are distinct).
 __global__ void __launch_bounds__(kThreads) dedupe_order_light(hctr_dedupe_args a) {
-  const size_t u = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
   const unsigned lane = threadIdx.x & 31;
-  if (u >= a.meta[HCTR_META_UNIQUE]) return;
-  const u32 l = a.run_start[u], len = a.run_start[u + 1] - l;
-  if (len < 2 || len > kLightRun) return;  // longer runs: dedupe_order_heavy
-  u32 *p = a.sorted_pos + l;
-  const u32 v = lane < len ? p[lane] : 0xffffffffu;
-  u32 slot = 0;
-  for (u32 k = 0; k < len; k++) slot += __shfl_sync(0xffffffffu, v, k) < v ? 1u : 0u;
-  if (lane < len) p[slot] = v;
+  const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const size_t n_warps = ((size_t)gridDim.x * kThreads) >> 5;
+  const size_t U = a.meta[HCTR_META_UNIQUE];
+  for (size_t u0 = warp * 32; u0 < U; u0 += n_warps * 32) {
+    const size_t u = u0 + lane;
+    u32 l = 0, len = 0;
+    if (u < U) {
+      l = a.run_start[u];
+      len = a.run_start[u + 1] - l;
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, len >= 2 && len <= kLightRun);  // longer: dedupe_order_heavy
+    while (todo) {
+      const int src = __ffs(todo) - 1;
+      todo &= todo - 1;
+      const u32 rl = __shfl_sync(0xffffffffu, l, src), rlen = __shfl_sync(0xffffffffu, len, src);
+      u32 *p = a.sorted_pos + rl;
+      const u32 v = lane < rlen ? p[lane] : 0xffffffffu;
+      u32 slot = 0;
+      for (u32 k = 0; k < rlen; k++) slot += __shfl_sync(0xffffffffu, v, k) < v ? 1u : 0u;
+      if (lane < rlen) p[slot] = v;
+    }
+  }
 }
 
 // Long runs: a CTA sets one bit per position in a shared-memory bitmap (window by window when the
@@ -250,31 +295,18 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
     attr_set = true;
   }
   const unsigned gb = grid_for(a.batch, kThreads);
-  int launches = 0;
-  // sample pass over the first 1/16 of the batch, then the rest
-  const size_t sample = a.batch >= 4096 ? a.batch / 16 : 0;
-  if (sample) {
-    dedupe_mark<<<grid_for(sample, kThreads), kThreads, 0, s>>>(a, 0, sample);
-    launches++;
-  }
-  if (a.batch > sample) {
-    dedupe_mark<<<grid_for(a.batch - sample, kThreads), kThreads, 0, s>>>(a, sample, a.batch - sample);
-    launches++;
-  }
+  dedupe_mark<<<gb, kThreads, 0, s>>>(a);
+  // aim for one resident wave of warps (148 SMs x 64 warps); beyond that let warps take wider groups
+  const size_t target_warps = (size_t)kSMs * 64;
+  unsigned group = 1;
+  while (group < 32 && (n_blocks + group - 1) / group > target_warps) group *= 2;
+  size_t blk_ctas = (((n_blocks + group - 1) / group) * 32 + kThreads - 1) / kThreads;
+  if (blk_ctas > (size_t)kSMs * 8) blk_ctas = (size_t)kSMs * 8;
+  if (blk_ctas == 0) blk_ctas = 1;
+  dedupe_count<<<(unsigned)blk_ctas, kThreads, 0, s>>>(a, n_blocks, group);
   int rc = hctr_scan_exclusive_u32(a.blk_cnt, a.blk_base, n_blocks, nullptr, a.scan_scratch, stream);
   if (rc) return rc;
-  {
-    // aim for one resident wave of warps (148 SMs x 64 warps); beyond that let warps take wider groups
-    const size_t target_warps = (size_t)kSMs * 64;
-    unsigned group = 1;
-    while (group < 32 && (n_blocks + group - 1) / group > target_warps) group *= 2;
-    size_t warps = (n_blocks + group - 1) / group;
-    size_t ctas = (warps * 32 + kThreads - 1) / kThreads;
-    const size_t cap = (size_t)kSMs * 8;
-    if (ctas > cap) ctas = cap;
-    if (ctas == 0) ctas = 1;
-    dedupe_extract<<<(unsigned)ctas, kThreads, 0, s>>>(a, n_blocks, blocks_per_owner, group);
-  }
+  dedupe_extract<<<(unsigned)blk_ctas, kThreads, 0, s>>>(a, n_blocks, blocks_per_owner, group);
   dedupe_rank<<<gb, kThreads, 0, s>>>(a);
   rc = hctr_scan_exclusive_u32(a.cnt, a.run_start, a.batch, a.meta + HCTR_META_UNIQUE, a.scan_scratch, stream);
   if (rc) return rc;
@@ -288,7 +320,12 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
     if (e == cudaSuccess) e = cudaStreamWaitEvent(hs, (cudaEvent_t)a.fork_event, 0);
     if (e != cudaSuccess) return (int)e;
   }
-  dedupe_order_light<<<grid_for(a.batch * 32, kThreads), kThreads, 0, s>>>(a);
+  {
+    size_t ctas = ((a.batch + 31) / 32 * 32 + kThreads - 1) / kThreads;  // one warp per 32 unique keys
+    if (ctas > (size_t)kSMs * 8) ctas = (size_t)kSMs * 8;
+    if (ctas == 0) ctas = 1;
+    dedupe_order_light<<<(unsigned)ctas, kThreads, 0, s>>>(a);
+  }
   {
     // window = the batch when it fits (small windows let several CTAs share an SM)
     size_t wbits = (a.batch + 1023) / 1024 * 1024;
@@ -305,6 +342,6 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
     if (e == cudaSuccess) e = cudaStreamWaitEvent(s, (cudaEvent_t)a.join_event, 0);
     if (e != cudaSuccess) return (int)e;
   }
-  count_launches(launches + 5);
+  count_launches(7);
   return launch_status();
 }

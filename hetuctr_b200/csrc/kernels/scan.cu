@@ -78,6 +78,32 @@ __global__ void __launch_bounds__(kScanThreads) scan_apply(const u32 *__restrict
   }
 }
 
+// Small inputs (a few tiles): one CTA walks the tiles with a running carry, one launch in total.
+__global__ void __launch_bounds__(kScanThreads) scan_single_cta(const u32 *__restrict__ in, u32 *__restrict__ out,
+                                                                size_t n_max, const u32 *__restrict__ n_dev) {
+  const size_t n = n_dev ? min((size_t)*n_dev, n_max) : n_max;
+  __shared__ u32 total;
+  u32 carry = 0;
+  for (size_t t0 = 0; t0 <= n; t0 += HCTR_SCAN_TILE) {
+    const size_t base = t0 + (size_t)threadIdx.x * kScanItems;
+    u32 v[kScanItems];
+    u32 s = 0;
+#pragma unroll
+    for (int k = 0; k < kScanItems; k++) {
+      v[k] = (base + k < n) ? in[base + k] : 0;
+      s += v[k];
+    }
+    u32 ex = block_excl_scan(s, &total) + carry;
+#pragma unroll
+    for (int k = 0; k < kScanItems; k++) {
+      if (base + k <= n) out[base + k] = ex;
+      ex += v[k];
+    }
+    carry += total;
+    __syncthreads();
+  }
+}
+
 }  // namespace hctr
 
 using namespace hctr;
@@ -93,6 +119,11 @@ extern "C" int hctr_scan_exclusive_u32(const uint32_t *in, uint32_t *out, size_t
   cudaStream_t s = (cudaStream_t)stream;
   // n+1 outputs: tiles cover [0, n_max]
   const size_t tiles = (n_max + 1 + HCTR_SCAN_TILE - 1) / HCTR_SCAN_TILE;
+  if (tiles <= 4) {
+    scan_single_cta<<<1, kScanThreads, 0, s>>>(in, out, n_max, n_dev);
+    count_launches(1);
+    return launch_status();
+  }
   scan_tile_sums<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, n_max, n_dev, scratch);
   scan_apply<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n_max, n_dev, scratch);
   count_launches(2);

@@ -146,6 +146,105 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short(hctr_reduce_args a
   }
 }
 
+// Short runs, rows of at least 32 float4 (width >= 128): a warp takes kWideChunk consecutive unique
+// keys.  Run bounds, rows, push slots and first positions are fetched by the first lanes (one key per
+// lane) and the per-key bookkeeping runs one key per lane; the warp then walks the keys, and while it
+// sums and applies key k the first gradient row and the table row of the next key are already in
+// flight.  The chunk is small so that a batch still yields enough warps to fill every SM.
+constexpr unsigned kWideChunk = 8;
+__global__ void __launch_bounds__(kThreads) grad_reduce_short_wide(hctr_reduce_args a) {
+  typedef RowT<true> R;
+  typedef float4 T;
+  const unsigned lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const size_t n_warps = ((size_t)gridDim.x * kThreads) >> 5;
+  const size_t E = a.width / 4;
+  const T *grad = reinterpret_cast<const T *>(a.grad);
+  T *emb_base = reinterpret_cast<T *>(a.embedding);
+  T *pend_base = reinterpret_cast<T *>(a.pending);
+  T *out_base = reinterpret_cast<T *>(a.push_val);
+  for (size_t u0 = warp * kWideChunk; u0 < a.n_unique; u0 += n_warps * kWideChunk) {
+    const size_t my_u = u0 + lane;
+    u32 l = 0, len = 0, p0 = 0, slot = 0;
+    int row = 0, type = -1;  // type -1: nothing to do for this lane's key
+    if (lane < kWideChunk && my_u < a.n_unique) {
+      l = a.run_start[my_u];
+      len = a.run_start[my_u + 1] - l;
+      if (len > 0 && len <= HCTR_LIGHT_RUN) {
+        p0 = a.sorted_pos[l];
+        const RowTarget t = reduce_bookkeeping(a, my_u, len, true);
+        row = t.row;
+        type = t.type;
+        slot = (u32)t.slot;
+      }
+    }
+    unsigned todo = __ballot_sync(0xffffffffu, type >= 0);
+    if (!todo) continue;
+    // prefetch for the first key
+    int k = __ffs(todo) - 1;
+    todo &= todo - 1;
+    T g_next, e_next;
+    {
+      const u32 pk = __shfl_sync(0xffffffffu, p0, k);
+      const int rk = __shfl_sync(0xffffffffu, row, k), tk = __shfl_sync(0xffffffffu, type, k);
+      g_next = R::ld_once(grad + (size_t)pk * E + lane);
+      e_next = tk != 0 ? emb_base[(size_t)rk * E + lane] : R::zero();
+    }
+    while (k >= 0) {
+      const u32 lk = __shfl_sync(0xffffffffu, l, k), lenk = __shfl_sync(0xffffffffu, len, k);
+      const u32 slotk = __shfl_sync(0xffffffffu, slot, k);
+      const int rowk = __shfl_sync(0xffffffffu, row, k), typek = __shfl_sync(0xffffffffu, type, k);
+      const T g0 = g_next, e0 = e_next;
+      const int kn = todo ? __ffs(todo) - 1 : -1;
+      todo &= todo - 1;
+      if (kn >= 0) {
+        const u32 pk = __shfl_sync(0xffffffffu, p0, kn);
+        const int rk = __shfl_sync(0xffffffffu, row, kn), tk = __shfl_sync(0xffffffffu, type, kn);
+        g_next = R::ld_once(grad + (size_t)pk * E + lane);
+        e_next = tk != 0 ? emb_base[(size_t)rk * E + lane] : R::zero();
+      }
+      T *emb = emb_base + (typek != 0 ? (size_t)rowk * E : 0);
+      T *pend = pend_base + (typek >= 2 ? (size_t)rowk * E : 0);
+      T *out = out_base + (size_t)slotk * E;
+      for (size_t c = lane; c < E; c += 32) {
+        T sum, e_old;
+        if (c == lane) {
+          sum = R::add(R::zero(), g0);
+          e_old = e0;
+        } else {
+          sum = R::add(R::zero(), R::ld_once(grad + (size_t)a.sorted_pos[lk] * E + c));
+          e_old = typek != 0 ? emb[c] : R::zero();
+        }
+        u32 j = 1;
+        for (; j + 4 <= lenk; j += 4) {
+          const T g1 = R::ld_once(grad + (size_t)a.sorted_pos[lk + j] * E + c);
+          const T g2 = R::ld_once(grad + (size_t)a.sorted_pos[lk + j + 1] * E + c);
+          const T g3 = R::ld_once(grad + (size_t)a.sorted_pos[lk + j + 2] * E + c);
+          const T g4 = R::ld_once(grad + (size_t)a.sorted_pos[lk + j + 3] * E + c);
+          sum = R::add(R::add(R::add(R::add(sum, g1), g2), g3), g4);
+        }
+        for (; j < lenk; j++) sum = R::add(sum, R::ld_once(grad + (size_t)a.sorted_pos[lk + j] * E + c));
+        sum = R::scale(sum, a.neg_lr);
+        if (typek == 0) {
+          out[c] = sum;
+        } else {
+          emb[c] = R::add(e_old, sum);
+          if (typek >= 2) {
+            const T p = R::add(pend[c], sum);
+            if (typek == 2) {
+              out[c] = p;
+              pend[c] = R::zero();
+            } else {
+              pend[c] = p;
+            }
+          }
+        }
+      }
+      k = kn;
+    }
+  }
+}
+
 // Long runs (hot keys, up to the whole batch): one CTA per key.  All threads stream the key's
 // gradient rows into a ring of shared-memory stages with cp.async (16-byte copies, several stages in
 // flight), and one thread per row element adds the staged rows in order.  The sequential sum of a
@@ -156,6 +255,7 @@ constexpr int kLongWarps = kLongThreads / 32;
 constexpr int kLongStages = 4;
 constexpr int kLongStageBytes = 16 * 1024;
 constexpr int kLongPosChunk = 2048;  // positions staged in shared memory at a time
+constexpr u32 kVeryLongRun = 256;     // runs at least this long are started first
 
 template <bool VEC>
 __device__ __forceinline__ void cp_async_elem(void *smem_dst, const void *gsrc) {
@@ -185,24 +285,31 @@ __global__ void __launch_bounds__(kLongThreads) grad_reduce_long(hctr_reduce_arg
   while (lpr > 1 && (size_t)(lpr / 2) >= E) lpr /= 2;
   const unsigned rows_per_warp_iter = 32 / lpr, sub = lane / lpr, sl = lane % lpr;
 
-  for (;;) {
+  // two passes over the list: the longest runs bound the kernel's duration, so they start first
+  for (int pass = 0; pass < 2;) {
     __syncthreads();
-    if (tid == 0) next_item = atomicAdd(work_counter, 1u);
+    if (tid == 0) next_item = atomicAdd(work_counter + pass, 1u);
     __syncthreads();
     const u32 h = next_item;
-    if (h >= n_heavy) break;
+    if (h >= n_heavy) {
+      pass++;
+      continue;
+    }
     const size_t u = a.heavy_list[h];
     const u32 l = a.run_start[u], len = a.run_start[u + 1] - l;
+    if ((len >= kVeryLongRun) != (pass == 0)) continue;
     const RowTarget t = reduce_bookkeeping(a, u, len, tid == 0);
     // columns are processed in slabs of up to 4 per thread (width <= 1024 needs a single pass)
     for (size_t col0 = 0; col0 < W; col0 += 4 * kLongThreads) {
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       for (u32 p0 = 0; p0 < len; p0 += kLongPosChunk) {
         const u32 plen = min((u32)kLongPosChunk, len - p0);
-        __syncthreads();
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        __syncthreads();  // previous chunk fully consumed before its positions and stages are reused
         for (u32 k = tid; k < plen; k += kLongThreads) pos_s[k] = a.sorted_pos[l + p0 + k];
         __syncthreads();
         const u32 n_tiles = (plen + rows_per_stage - 1) / rows_per_stage;
+        const u32 E32 = (u32)E, W32 = (u32)W;
         auto issue = [&](u32 tile) {
           if (tile < n_tiles) {
             const u32 r0 = tile * rows_per_stage;
@@ -210,28 +317,40 @@ __global__ void __launch_bounds__(kLongThreads) grad_reduce_long(hctr_reduce_arg
             T *dst = stage + (size_t)(tile % kLongStages) * stage_elems;
             for (u32 rr = warp * rows_per_warp_iter + sub; rr < nr; rr += kLongWarps * rows_per_warp_iter) {
               const T *src = grad + (size_t)pos_s[r0 + rr] * E;
-              for (size_t cc = sl; cc < E; cc += lpr) cp_async_elem<VEC>(dst + (size_t)rr * E + cc, src + cc);
+              T *d = dst + rr * E32;
+              for (u32 cc = sl; cc < E32; cc += lpr) cp_async_elem<VEC>(d + cc, src + cc);
             }
           }
           asm volatile("cp.async.commit_group;\n" ::: "memory");  // one group per tile slot, even if empty
         };
         for (int p = 0; p < kLongStages - 1; p++) issue(p);
         for (u32 tile = 0; tile < n_tiles; tile++) {
+          // groups in flight: tiles tile .. tile+S-2; all but the newest S-2 done => this tile landed
+          asm volatile("cp.async.wait_group %0;\n" ::"n"(kLongStages - 2) : "memory");
+          // one barrier per tile: every thread's copies of this tile are visible, and every thread has
+          // finished adding the previous tile, whose stage the next issue overwrites
+          __syncthreads();
           issue(tile + kLongStages - 1);
-          asm volatile("cp.async.wait_group %0;\n" ::"n"(kLongStages - 1) : "memory");
-          __syncthreads();  // every thread's copies of this tile have landed
           const u32 nr = min(rows_per_stage, plen - tile * rows_per_stage);
           const float *src = stage_f + (size_t)(tile % kLongStages) * stage_floats;
 #pragma unroll
           for (int k = 0; k < 4; k++) {
-            const size_t col = col0 + tid + (size_t)k * kLongThreads;
-            if (col < W) {
+            const u32 col = (u32)col0 + tid + (u32)k * kLongThreads;
+            if (col < W32) {
+              const float *sc = src + col;
               float sacc = acc[k];
-              for (u32 rr = 0; rr < nr; rr++) sacc = __fadd_rn(sacc, src[(size_t)rr * W + col]);
+              u32 rr = 0;
+              for (; rr + 8 <= nr; rr += 8) {
+                float v[8];
+#pragma unroll
+                for (int q = 0; q < 8; q++) v[q] = sc[(rr + q) * W32];
+#pragma unroll
+                for (int q = 0; q < 8; q++) sacc = __fadd_rn(sacc, v[q]);
+              }
+              for (; rr < nr; rr++) sacc = __fadd_rn(sacc, sc[rr * W32]);
               acc[k] = sacc;
             }
           }
-          __syncthreads();  // the stage may be refilled by the next issue
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
       }
@@ -305,10 +424,17 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
     cudaError_t e = cudaEventRecord((cudaEvent_t)a.fork_event, s);
     if (e != cudaSuccess) return (int)e;
   }
+  if (al && a.width % 4 == 0 && a.width >= 128) {
+    size_t ctas = ((a.n_unique + kWideChunk - 1) / kWideChunk * 32 + kThreads - 1) / kThreads;
+    const size_t cap = (size_t)kSMs * 8;
+    if (ctas > cap) ctas = cap;
+    grad_reduce_short_wide<<<(unsigned)ctas, kThreads, 0, s>>>(a);
+  } else {
 #define CALL(L, V) \
   grad_reduce_short<L, V><<<grid_for(a.n_unique * L, kThreads), kThreads, 0, s>>>(a)
-  HCTR_DISPATCH_ROWS(a.width, al, CALL);
+    HCTR_DISPATCH_ROWS(a.width, al, CALL);
 #undef CALL
+  }
   count_launches(1);
   if (a.n_heavy > 0) {
     static bool attr_set = false;
@@ -331,9 +457,9 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
       cudaError_t e = cudaStreamWaitEvent(ls, (cudaEvent_t)a.fork_event, 0);
       if (e != cudaSuccess) return (int)e;
     }
-    cudaError_t em = cudaMemsetAsync(a.work_counter, 0, sizeof(u32), ls);
+    cudaError_t em = cudaMemsetAsync(a.work_counter, 0, 2 * sizeof(u32), ls);
     if (em != cudaSuccess) return (int)em;
-    const unsigned grid = (unsigned)min((size_t)a.n_heavy, (size_t)kSMs * 3);
+    const unsigned grid = (unsigned)min((size_t)a.n_heavy, (size_t)kSMs * (need > 100 * 1024 ? 1 : 3));
     if (al && a.width % 4 == 0) grad_reduce_long<true><<<grid, kLongThreads, need, ls>>>(a, (u32)a.n_heavy, a.work_counter);
     else grad_reduce_long<false><<<grid, kLongThreads, need, ls>>>(a, (u32)a.n_heavy, a.work_counter);
     count_launches(1);

@@ -105,9 +105,10 @@ typedef struct hctr_dedupe_args {
   const int32_t *row_of;    /* [N] */
   /* persistent scratch, all-zero between calls */
   unsigned long long *bits; /* [nrank*length_pad/64] */
-  uint32_t *blk_cnt;        /* [nrank*length_pad/4096 + 1] distinct keys per bitmap block */
+  uint8_t *blk_flag;        /* [nrank*length_pad/4096] block touched by this batch */
   uint32_t *cnt;            /* [B+1] occurrences per unique key (consumed by the run-start scan) */
   /* scratch that needs no initial value */
+  uint32_t *blk_cnt;        /* [nblocks + 1] distinct keys per bitmap block */
   uint32_t *blk_base;       /* [nblocks + 1] */
   uint32_t *word_base;      /* [nrank*length_pad/64] */
   uint32_t *scan_scratch;   /* hctr_scan_scratch_words(max(nblocks, B) + 1) */
@@ -186,7 +187,7 @@ typedef struct hctr_reduce_args {
   int64_t *push_key;          /* [P] packed ids of pushed rows */
   int64_t *push_updates;      /* [P] update counts */
   float *push_val;            /* [P, W] */
-  uint32_t *work_counter;     /* one device word of scratch (needed when n_heavy > 0) */
+  uint32_t *work_counter;     /* two device words of scratch (needed when n_heavy > 0) */
   /* optional: a second stream (cudaStream_t) and two events (cudaEvent_t, timing disabled) that let
    * the long-run kernel overlap the short-run kernel; null = everything on the call's stream */
   void *side_stream;

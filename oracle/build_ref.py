@@ -1,0 +1,67 @@
+"""Builds the REFERENCE's own implementation as a checker (TEST INFRASTRUCTURE, never shipped).
+
+  python oracle/build_ref.py [--reference /root/reference]
+
+Compiles the reference's sources where they lie (nothing is copied into this repository) for sm_100a and links
+them with oracle/ref_binding.cu into oracle/_ref/hetuCTR_ref<ext>.so.  The reference's ZMQ rendezvous cannot be
+built here (no zmq.h); oracle/ref_shim/utils/rendezvous.h, found first on the include path, substitutes this
+repository's POSIX-socket TCPRendezvous, which has the same constructor and broadcast().  -DNDEBUG turns the
+reference's device-side asserts off so that a bad key cannot trap a shared GPU.
+"""
+import concurrent.futures
+import os
+import subprocess
+import sys
+import sysconfig
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+OUT = os.path.join(HERE, "_ref")
+MODULE = os.path.join(OUT, "hetuCTR_ref" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+REF_SOURCES = ["core/hetu_gpu_table.cu", "core/preprocess.cu", "core/preprocess_sturct.cu", "core/generate_query.cu",
+               "core/handle_query.cu", "core/writeback.cu", "core/all2all.cu", "core/table_initialize.cu",
+               "core/debug.cu", "utils/initializer.cu"]
+
+
+def build(reference="/root/reference", force=False, verbose=False):
+    csrc = os.path.join(reference, "csrc")
+    if not os.path.isdir(csrc):
+        raise RuntimeError(f"reference sources not found at {csrc}")
+    if os.path.exists(MODULE) and not force:
+        return MODULE
+    import pybind11
+    os.makedirs(os.path.join(OUT, "obj"), exist_ok=True)
+    inc = ["-I", os.path.join(HERE, "ref_shim"), "-I", csrc, "-I", pybind11.get_include(),
+           "-I", sysconfig.get_paths()["include"]]
+    flags = ["-std=c++17", "-O3", "-w", "-DNDEBUG", "-gencode", "arch=compute_100a,code=sm_100a",
+             "-Xcompiler", "-fPIC", *inc]
+    jobs, objs = [], []
+    for src in REF_SOURCES:
+        obj = os.path.join(OUT, "obj", src.replace("/", "_") + ".o")
+        objs.append(obj)
+        jobs.append(["nvcc", *flags, "-c", os.path.join(csrc, src), "-o", obj])
+    obj = os.path.join(OUT, "obj", "ref_binding.o")
+    objs.append(obj)
+    jobs.append(["nvcc", *flags, "-c", os.path.join(HERE, "ref_binding.cu"), "-o", obj])
+    obj = os.path.join(OUT, "obj", "rendezvous.o")
+    objs.append(obj)
+    jobs.append(["g++", "-O2", "-std=c++17", "-fPIC", "-I", os.path.join(ROOT, "hetuctr_b200", "csrc"), "-c",
+                 os.path.join(ROOT, "hetuctr_b200", "csrc", "utils", "rendezvous.cc"), "-o", obj])
+
+    def run(cmd):
+        if verbose:
+            print(" ".join(cmd), flush=True)
+        r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("reference build step failed:\n" + " ".join(cmd) + "\n" + r.stdout[-4000:])
+
+    with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
+        list(ex.map(run, jobs))
+    run(["nvcc", "-shared", "-o", MODULE, *objs, "-lnccl"])
+    return MODULE
+
+
+if __name__ == "__main__":
+    ref = sys.argv[sys.argv.index("--reference") + 1] if "--reference" in sys.argv else "/root/reference"
+    print(build(ref, force="--force" in sys.argv, verbose=True))
