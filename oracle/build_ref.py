@@ -5,7 +5,9 @@
 Compiles the reference's sources where they lie (nothing is copied into this repository) for sm_100a and links
 them with oracle/ref_binding.cu into oracle/_ref/hetuCTR_ref<ext>.so.  The reference's ZMQ rendezvous cannot be
 built here (no zmq.h); oracle/ref_shim/utils/rendezvous.h, found first on the include path, substitutes this
-repository's POSIX-socket TCPRendezvous, which has the same constructor and broadcast().  -DNDEBUG turns the
+repository's POSIX-socket TCPRendezvous, which has the same constructor and broadcast().  The reference also
+launches empty grids, which the CUDA runtime of this image rejects: ref_empty_launch_shim.cc skips those at link
+level.  -DNDEBUG turns the
 reference's device-side asserts off so that a bad key cannot trap a shared GPU.
 """
 import concurrent.futures
@@ -56,9 +58,17 @@ def build(reference="/root/reference", force=False, verbose=False):
         if r.returncode != 0:
             raise RuntimeError("reference build step failed:\n" + " ".join(cmd) + "\n" + r.stdout[-4000:])
 
+    obj = os.path.join(OUT, "obj", "empty_launch_shim.o")
+    objs.append(obj)
+    jobs.append(["g++", "-O2", "-std=c++17", "-fPIC", "-I", "/usr/local/cuda/include", "-c",
+                 os.path.join(HERE, "ref_empty_launch_shim.cc"), "-o", obj])
+
     with concurrent.futures.ThreadPoolExecutor(max_workers=8) as ex:
         list(ex.map(run, jobs))
-    run(["nvcc", "-shared", "-o", MODULE, *objs, "-lnccl"])
+    # shared CUDA runtime + -Bsymbolic: the module's own launch hook (ref_empty_launch_shim.cc) is the one its
+    # kernels' launch stubs call, and it forwards to the runtime library
+    run(["nvcc", "-shared", "-cudart", "shared", "-o", MODULE, *objs, "-lnccl", "-ldl", "-Xlinker", "-Bsymbolic",
+         "-Xlinker", "-rpath,/usr/local/cuda/lib64"])
     return MODULE
 
 

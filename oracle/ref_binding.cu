@@ -10,6 +10,7 @@
 
 #include <memory>
 #include <string>
+#include <algorithm>
 #include <vector>
 
 #include "core/hetu_gpu_table.h"
@@ -90,6 +91,30 @@ PYBIND11_MODULE(hetuCTR_ref, m) {
              py::gil_scoped_release rel;
              t.pushPull(reinterpret_cast<embed_t *>(grad), reinterpret_cast<embed_t *>(dst));
            })
+      // numpy in / numpy out: the binding stages gradients and pulled rows itself, so a driver script needs
+      // no other CUDA library in the process
+      .def("push_pull_np",
+           [](HetuTable &t, py::object grad, size_t n_cur) {
+             cudaSetDevice(t.device_id_);
+             const size_t W = t.kEmbeddingWidth;
+             float *d_grad = nullptr, *d_dst = nullptr;
+             if (!grad.is_none()) {
+               auto g = grad.cast<py::array_t<float, py::array::c_style | py::array::forcecast>>();
+               cudaMalloc(&d_grad, std::max<size_t>(g.size(), 1) * sizeof(float));
+               cudaMemcpy(d_grad, g.data(), g.size() * sizeof(float), cudaMemcpyHostToDevice);
+             }
+             cudaMalloc(&d_dst, std::max<size_t>(n_cur * W, 1) * sizeof(float));
+             {
+               py::gil_scoped_release rel;
+               t.pushPull(d_grad, d_dst);
+             }
+             py::array_t<float> out({n_cur, W});
+             cudaMemcpy(out.mutable_data(), d_dst, n_cur * W * sizeof(float), cudaMemcpyDeviceToHost);
+             cudaFree(d_grad);
+             cudaFree(d_dst);
+             return out;
+           },
+           py::arg("grad"), py::arg("n_cur"))
       .def("set_embedding",
            [](HetuTable &t, py::array_t<float, py::array::c_style | py::array::forcecast> rows) {
              cudaSetDevice(t.device_id_);

@@ -21,26 +21,21 @@ import cases  # noqa: E402
 
 
 def worker(name, rank, port, q):
-    import torch
     import hetuCTR_ref as ref
 
     c, root, storage, emb, keys, grads = cases.make_inputs(name)
     n, W = c["nrank"], c["width"]
-    torch.cuda.set_device(rank)
     t = ref.HetuTable(rank=rank, nrank=n, device_id=rank, ip="127.0.0.1", port=port, length=c["length"], width=W,
                       pull_bound=c["pull"], push_bound=c["push"], root_arr=root, storage_arr=storage[rank],
                       init_kind=0, init_a=0.0, init_b=0.0, learning_rate=c["lr"], verbose=0)
     out = {}
     t.set_embedding(cases.layout_rows(root, storage[rank], rank, emb[rank]))
-    dst = torch.zeros(c["batch"], W, device="cuda")
     for s in range(c["steps"]):
         k = keys[s][rank]
         t.preprocess(k.ctypes.data, k.size)
         for a in cases.INDEX_ARRAYS:
             out[f"s{s}_r{rank}_{a}"] = t.dump(a)
-        g = 0 if grads[s] is None else torch.from_numpy(grads[s][rank]).cuda()
-        t.push_pull(0 if grads[s] is None else g.data_ptr(), dst.data_ptr())
-        out[f"s{s}_r{rank}_dst"] = dst.cpu().numpy().copy()
+        out[f"s{s}_r{rank}_dst"] = t.push_pull_np(None if grads[s] is None else grads[s][rank], k.size)
     for a in cases.STATE_ARRAYS:
         out[f"final_r{rank}_{a}"] = t.dump(a)
     q.put(out)
@@ -76,8 +71,15 @@ def record_init(outdir):
     print("recorded init values")
 
 
+def gpu_count():
+    import subprocess
+    try:
+        return len(subprocess.run(["nvidia-smi", "-L"], stdout=subprocess.PIPE, text=True).stdout.strip().splitlines())
+    except OSError:
+        return 0
+
+
 if __name__ == "__main__":
-    import torch
     args = sys.argv[1:]
     outdir = HERE
     if "--out" in args:
@@ -86,7 +88,7 @@ if __name__ == "__main__":
         del args[i:i + 2]
     os.makedirs(outdir, exist_ok=True)
     names = args or list(cases.CASES)
-    ngpu = torch.cuda.device_count()
+    ngpu = gpu_count()
     port = 24100
     for name in names:
         if cases.CASES[name]["nrank"] > ngpu:

@@ -115,10 +115,11 @@ def test_multi_process_nccl_matches_oracle(oracle_mod, name, tmp_path):
     got = [np.load(o) for o in outs]
     for s in range(c["steps"]):
         w.preprocess(keys[s])
-        dst = w.push_pull(grads[s])
         for r in range(n):
             for a in cases.INDEX_ARRAYS:
                 assert np.array_equal(got[r][f"s{s}_r{r}_{a}"], w.get(r, a)), f"{name} step {s} rank {r}: {a}"
+        dst = w.push_pull(grads[s])
+        for r in range(n):
             assert np.array_equal(got[r][f"s{s}_r{r}_dst"], dst[r]), f"{name} step {s} rank {r}: pulled rows"
     for r in range(n):
         assert np.array_equal(got[r][f"final_r{r}_version"], w.get(r, "version"))
