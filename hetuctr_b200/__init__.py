@@ -77,6 +77,7 @@ def lib():
     L.hctr_table_stats.argtypes = [vp, vp]
     L.hctr_table_stream.restype = vp
     L.hctr_table_stream.argtypes = [vp]
+    L.hctr_rendezvous_broadcast.argtypes = [i32, i32, c.c_char_p, i32, vp, sz, c.c_double]
     L.hctr_table_profile.argtypes = [vp, i32]
     L.hctr_table_phase_times.argtypes = [vp, vp, vp, i32]
     L.hctr_launch_count.restype = c.c_ulonglong

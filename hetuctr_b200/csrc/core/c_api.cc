@@ -6,6 +6,7 @@
 
 #include "core/hetu_table.h"
 #include "hctr_table.h"
+#include "utils/rendezvous.h"
 #include "utils/thread_pool.h"
 
 using hetuCTR::HetuTable;
@@ -156,6 +157,14 @@ int hctr_table_phase_times(hctr_table *t, double ms[HCTR_N_PHASES], long long ca
   static_assert(HCTR_N_PHASES == hetuCTR::kPhCount, "phase list out of sync");
   t->impl->phaseTimes(ms, calls, reset != 0);
   return 0;
+}
+
+int hctr_rendezvous_broadcast(int rank, int nrank, const char *ip, int port, void *data, size_t len,
+                              double timeout_s) {
+  return guarded([&] {
+    hetuCTR::TCPRendezvous tcp(rank, nrank, ip ? ip : "", port, timeout_s);
+    tcp.broadcast(data, len);
+  });
 }
 
 void *hctr_table_stream(hctr_table *t) { return (void *)t->impl->stream(); }

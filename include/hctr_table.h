@@ -84,6 +84,13 @@ int hctr_table_stats(hctr_table *t, long long out[11]);
 int hctr_table_profile(hctr_table *t, int enable);
 int hctr_table_phase_times(hctr_table *t, double ms[HCTR_N_PHASES], long long calls[HCTR_N_PHASES], int reset);
 
+/* The bootstrap broadcast used when a multi-rank table is constructed, exposed for tests and tools: copies
+ * `len` bytes at `data` from rank 0 to every rank over TCP (rank 0 listens on ip:port).  Returns -1 with a
+ * message in hctr_last_error() if a rank does not show up within timeout_s seconds.  Same role as the
+ * reference's TCPRendezvous::broadcast, csrc/utils/rendezvous.cc:42-64 (which blocks forever instead). */
+int hctr_rendezvous_broadcast(int rank, int nrank, const char *ip, int port, void *data, size_t len,
+                              double timeout_s);
+
 /* The CUDA stream (cudaStream_t) the table enqueues its work on. */
 void *hctr_table_stream(hctr_table *t);
 
