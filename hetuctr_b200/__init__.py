@@ -81,6 +81,9 @@ def lib():
     L.hctr_table_profile.argtypes = [vp, i32]
     L.hctr_table_phase_times.argtypes = [vp, vp, vp, i32]
     L.hctr_launch_count.restype = c.c_ulonglong
+    L.hctr_scan_exclusive_u32.argtypes = [vp, vp, sz, vp, vp, vp]
+    L.hctr_scan_exclusive_u32_noalloc.argtypes = [vp, vp, sz, vp]
+    L.hctr_noalloc_last_error.restype = c.c_char_p
     L.hctr_scan_scratch_words.restype = sz
     L.hctr_scan_scratch_words.argtypes = [sz]
     _lib = L

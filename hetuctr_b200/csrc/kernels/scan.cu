@@ -1,6 +1,8 @@
 // Exclusive prefix sum over 32-bit counts in two small launches (tile sums; tile-local scan + the sum
 // of the preceding tile sums, which every CTA adds up for itself).  No spin-waits and no assumption on CTA dispatch
 // order; the inputs on this path are at most a few million entries and L2-resident.
+#include <cstdio>
+
 #include "common.cuh"
 
 namespace hctr {
@@ -126,6 +128,67 @@ extern "C" int hctr_scan_exclusive_u32(const uint32_t *in, uint32_t *out, size_t
   }
   scan_tile_sums<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, n_max, n_dev, scratch);
   scan_apply<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n_max, n_dev, scratch);
+  count_launches(2);
+  return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// Prefix sum for callers that must not allocate.
+//
+// Some hosts of this library cannot call cudaMalloc at the point where they need a scan: code running
+// inside a framework's memory-pool callback, a real-time loop whose latency budget excludes the
+// driver's allocator lock, or a plugin that is only handed input/output buffers and has no allocator
+// of its own.  For them the tile-sum scratch of the scan lives in a file-scope device array that
+// every GPU loading this library holds until the process exits (64 KB).
+//
+// Host code cannot pass `g_noalloc_scan_scratch` to a kernel: in host code that name is only a handle
+// of the symbol, not a device address.  The address is obtained once per device with
+// cudaGetSymbolAddress, with that device current, and cached.
+// ------------------------------------------------------------------------------------------------
+namespace hctr {
+constexpr size_t kNoAllocScratchWords = HCTR_NOALLOC_SCAN_MAX / HCTR_SCAN_TILE + 2;
+static __device__ __align__(256) u32 g_noalloc_scan_scratch[kNoAllocScratchWords];
+constexpr int kMaxDevices = 64;
+static u32 *g_noalloc_scratch_addr[kMaxDevices] = {};
+static thread_local char g_noalloc_error[256] = "";
+}  // namespace hctr
+
+extern "C" const char *hctr_noalloc_last_error(void) { return g_noalloc_error; }
+
+extern "C" int hctr_scan_exclusive_u32_noalloc(const uint32_t *in, uint32_t *out, size_t n, void *stream) {
+  g_noalloc_error[0] = 0;
+  if (n > (size_t)HCTR_NOALLOC_SCAN_MAX) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error),
+             "hctr_scan_exclusive_u32_noalloc: n = %zu exceeds the built-in scratch (at most %zu elements); "
+             "use hctr_scan_exclusive_u32 with caller-provided scratch",
+             n, (size_t)HCTR_NOALLOC_SCAN_MAX);
+    return (int)cudaErrorInvalidValue;
+  }
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+    snprintf(g_noalloc_error, sizeof(g_noalloc_error), "hctr_scan_exclusive_u32_noalloc: no usable current device");
+    return (int)(e != cudaSuccess ? e : cudaErrorInvalidDevice);
+  }
+  // First call on this device: look the scratch array's device address up (no allocation happens).
+  u32 *scratch = __atomic_load_n(&g_noalloc_scratch_addr[dev], __ATOMIC_ACQUIRE);
+  if (!scratch) {
+    void *p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scan_scratch);
+    if (e != cudaSuccess || !p) {
+      snprintf(g_noalloc_error, sizeof(g_noalloc_error), "hctr_scan_exclusive_u32_noalloc: cudaGetSymbolAddress failed: %s",
+               cudaGetErrorString(e));
+      return (int)(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
+    }
+    scratch = static_cast<u32 *>(p);
+    __atomic_store_n(&g_noalloc_scratch_addr[dev], scratch, __ATOMIC_RELEASE);
+  }
+  cudaStream_t s = (cudaStream_t)stream;
+  const size_t tiles = (n + 1 + HCTR_SCAN_TILE - 1) / HCTR_SCAN_TILE;
+  // Every tile sum the second kernel reads is written by the first one in the same call, so nothing in the
+  // shared scratch has to start at zero and what an earlier call left there is never read.
+  scan_tile_sums<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, n, nullptr, scratch);
+  scan_apply<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n, nullptr, scratch);
   count_launches(2);
   return launch_status();
 }

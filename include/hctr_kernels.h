@@ -56,6 +56,24 @@ size_t hctr_scan_scratch_words(size_t n_max);
 int hctr_scan_exclusive_u32(const uint32_t *in, uint32_t *out, size_t n_max, const uint32_t *n_dev,
                             uint32_t *scratch, void *stream);
 
+/* Exclusive prefix sum for callers that cannot allocate device memory.  (No counterpart in the
+ * reference: it sizes and allocates cub temp storage itself, csrc/core/table_initialize.cu:166-177.)
+ *
+ * Same result as hctr_scan_exclusive_u32 for n <= HCTR_NOALLOC_SCAN_MAX elements (out has n+1 entries,
+ * in == out allowed), but the scratch is a fixed array inside the library, so the call performs no
+ * cudaMalloc/cudaFree.  It is meant for callers such as allocator callbacks of a host framework,
+ * latency-critical loops that must stay clear of the driver's allocation lock, or plugins that only
+ * receive input and output buffers.
+ *  - Larger n is refused: returns cudaErrorInvalidValue and hctr_noalloc_last_error() says why.
+ *  - The first call on each device looks up the array's device address (with that device current); make
+ *    that first call before any stream capture starts.
+ *  - All calls on one device share the one array: calls that may overlap on the GPU (different streams
+ *    without ordering between them) race on it.  Nothing in it needs clearing between calls.
+ *  - Every GPU that loads the library holds the array (64 KB) until the process exits. */
+#define HCTR_NOALLOC_SCAN_MAX (1u << 26)
+int hctr_scan_exclusive_u32_noalloc(const uint32_t *in, uint32_t *out, size_t n, void *stream);
+const char *hctr_noalloc_last_error(void);
+
 /* ---------------------------------------------------------------------------------------------
  * Table build (set-up side of the path).
  * ------------------------------------------------------------------------------------------- */
