@@ -241,7 +241,7 @@ def run_ours(args):
                        "push_bound": c["push_bound"], "lr": c["lr"], "partition": f"random owners x{world}",
                        "l2": f"{N_BATCHES} rotating batches; >= {2 * B * 4 * W / 1e6:.0f} MB streamed per step exceeds the 126 MB L2"
                        if 2 * B * 4 * W > 126e6 else f"{N_BATCHES} rotating batches (per-step data smaller than L2)",
-                       "transport": "none (1 rank)" if world == 1 else "nccl"},
+                       "transport": table.exchange_name()},
             "e2e": {"value": world * B * args.e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": B * 8 + B * W * 4, "d2h_bytes_per_step": B * W * 4,
                     "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps},
@@ -292,27 +292,103 @@ def cpu_baseline(args, world, seconds=None):
                       f"{dt:.1f} s)"}
 
 
+def _ref_module():
+    """The reference's own CUDA build (oracle/_ref), or None when it is not there / cannot load."""
+    path = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.isdir(path):
+        return None
+    sys.path.insert(0, path)
+    try:
+        import hetuCTR_ref
+        return hetuCTR_ref
+    except Exception:  # noqa: BLE001 - fall back to the CPU port
+        return None
+
+
+def _gpu_present():
+    try:
+        return subprocess.run(["nvidia-smi", "-L"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL).returncode == 0
+    except OSError:
+        return False
+
+
 def run_reference(args):
-    """Reference arm.  The reference is GPU-only (CUDA + NCCL + ZMQ); its CPU stand-in here is the port of its
-    semantics in oracle/ run with all host threads."""
+    """Reference arm.  The reference is GPU-only: when its own CUDA build (oracle/_ref, compiled from the reference's
+    sources by oracle/build_ref.py) loads on this box it is what gets timed — same config, same synthetic batches,
+    its own preprocess()/pushPull() — one process per GPU.  Otherwise the CPU port of its semantics (oracle/, all host
+    threads) stands in.  No PyTorch in these processes: the reference build links its own CUDA runtime."""
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
-    if rank != 0:
-        return None
+    local = int(os.environ.get("LOCAL_RANK", 0))
     c = CONFIGS[args.config]
     B = c["samples"] * c["fields"]
-    t0 = time.perf_counter()
-    # --steps/--warmup scale the sample: about 0.1 s of CPU work per requested step, 10-60 s in total
-    cb = cpu_baseline(args, world, seconds=min(60.0, max(10.0, 0.1 * args.steps)))
-    steps = int(cb["sample"].split(" steps")[0])
-    return {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": world,
-            "steps": steps, "warmup": 1, "ms_per_step": world * B / cb["value"] * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": args.config + (" (size overridden)" if args.rows or args.width else ""), "rows": c["rows"], "width": c["width"],
-                       "keys_per_gpu_per_step": B},
-            "cpu_baseline": cb,
-            "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-            "total_s": time.perf_counter() - t0}
+    ref = _ref_module() if _gpu_present() else None
+    if ref is None:
+        if rank != 0:
+            return None
+        t0 = time.perf_counter()
+        # --steps scales the sample: about 0.1 s of CPU work per requested step, 10-60 s in total
+        cb = cpu_baseline(args, world, seconds=min(60.0, max(10.0, 0.1 * args.steps)))
+        steps = int(cb["sample"].split(" steps")[0])
+        return {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": UNIT, "n_gpus": world,
+                "steps": steps, "warmup": 1, "ms_per_step": world * B / cb["value"] * 1e3, "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "config": {"workload": args.config, "rows": c["rows"], "width": c["width"],
+                           "keys_per_gpu_per_step": B},
+                "cpu_baseline": cb,
+                "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+                "total_s": time.perf_counter() - t0}
+
+    c, root, storage, batches = make_workload(args.config, world, rank, args.rows, args.width)
+    W = c["width"]
+    addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
+    port = int(os.environ.get("MASTER_PORT", 29500)) + 203
+    ref.seed(0)
+    table = ref.HetuTable(rank=rank, nrank=world, device_id=local, ip=addr, port=port, length=c["rows"], width=W,
+                          pull_bound=c["pull_bound"], push_bound=c["push_bound"], root_arr=root, storage_arr=storage,
+                          init_kind=1, init_a=0.0, init_b=c["init_std"], learning_rate=c["lr"], verbose=0)
+    grad = (np.random.RandomState(1234 + rank).standard_normal((B, W)) * 0.01).astype(np.float32)
+    steps, warmup = args.steps, max(args.warmup, 3)
+    ms = table.bench_loop(batches, grad, steps, warmup, False)
+    e2e_steps = max(3, min(args.e2e_steps, steps))
+    e2e_ms = table.bench_loop(batches, grad, e2e_steps, 2, True)
+    del table
+    # max over ranks through a scratch directory (no collective library in these processes)
+    tag = os.environ.get("MASTER_PORT", "0")
+    d = os.path.join("/tmp", f"hctr_ref_bench_{tag}")
+    os.makedirs(d, exist_ok=True)
+    with open(os.path.join(d, f"r{rank}.json.tmp"), "w") as f:
+        json.dump({"ms": ms, "e2e_ms": e2e_ms}, f)
+    os.replace(os.path.join(d, f"r{rank}.json.tmp"), os.path.join(d, f"r{rank}.json"))
+    if rank != 0:
+        return None
+    times, t_wait = [], time.time()
+    for r in range(world):
+        fpath = os.path.join(d, f"r{r}.json")
+        while not os.path.exists(fpath):
+            if time.time() - t_wait > 600:
+                raise RuntimeError("a rank of the reference arm did not finish")
+            time.sleep(0.05)
+        times.append(json.load(open(fpath)))
+    for r in range(world):
+        os.remove(os.path.join(d, f"r{r}.json"))
+    ms = max(t["ms"] for t in times)
+    e2e_ms = max(t["e2e_ms"] for t in times)
+    value = world * B * steps / (ms * 1e-3)
+    return {"impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": args.config + (" (size overridden)" if args.rows or args.width else ""),
+                       "rows": c["rows"], "width": W, "keys_per_gpu_per_step": B, "partition": f"random owners x{world}",
+                       "cache_fraction": c["cache"] if world > 1 else 0.0,
+                       "what": "the reference's own CUDA/NCCL build (oracle/_ref), unmodified sources, "
+                               "preprocess()+pushPull() per step, inputs resident on the device"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": world, "kind": "reference",
+                             "sample": f"{steps} steps of {args.config} by the reference's own GPU build "
+                                       f"(one driving host thread per rank; the reference has no CPU path)"},
+            "e2e": {"value": world * B * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
+                    "h2d_bytes_per_step": B * 8 + B * W * 4, "d2h_bytes_per_step": B * W * 4,
+                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps}}
 
 
 def main():

@@ -75,6 +75,8 @@ def lib():
     L.hctr_table_dump.argtypes = [vp, c.c_char_p, i32, vp]
     L.hctr_table_set_embedding.argtypes = [vp, vp]
     L.hctr_table_stats.argtypes = [vp, vp]
+    L.hctr_table_exchange_name.restype = c.c_char_p
+    L.hctr_table_exchange_name.argtypes = [vp]
     L.hctr_table_stream.restype = vp
     L.hctr_table_stream.argtypes = [vp]
     L.hctr_rendezvous_broadcast.argtypes = [i32, i32, c.c_char_p, i32, vp, sz, c.c_double]
@@ -201,6 +203,9 @@ class Table:
         calls = (ctypes.c_longlong * len(self.PHASES))()
         self._lib.hctr_table_phase_times(self._h, ms, calls, int(reset))
         return {p: (ms[i], calls[i]) for i, p in enumerate(self.PHASES)}
+
+    def exchange_name(self):
+        return self._lib.hctr_table_exchange_name(self._h).decode()
 
     def stream(self):
         return self._lib.hctr_table_stream(self._h)

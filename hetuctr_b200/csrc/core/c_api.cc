@@ -167,6 +167,8 @@ int hctr_rendezvous_broadcast(int rank, int nrank, const char *ip, int port, voi
   });
 }
 
+const char *hctr_table_exchange_name(hctr_table *t) { return t->impl->exchangeName(); }
+
 void *hctr_table_stream(hctr_table *t) { return (void *)t->impl->stream(); }
 
 }  // extern "C"

@@ -2,9 +2,11 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <iostream>
 
+#include "core/p2p.h"
 #include "core/transport.h"
 #include "hctr_kernels.h"
 #include "utils/errors.h"
@@ -124,6 +126,23 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
 void HetuTable::initComm(const std::string &ip, int port) {
   if (nrank_ == 1) return;  // a single-rank table has nobody to talk to
   transport_ = make_transport(rank_, nrank_, ip, port, verbose_);
+  // Exchange flavour: HCTR_EXCHANGE = auto (default) | p2p | nccl.  The peer-to-peer exchange needs one
+  // process per GPU and peer access between all of them; all ranks take the same decision.
+  const char *env = std::getenv("HCTR_EXCHANGE");
+  const std::string mode = env ? env : "auto";
+  HCTR_CHECK(mode == "auto" || mode == "p2p" || mode == "nccl", "HCTR_EXCHANGE must be auto, p2p or nccl");
+  if (mode != "nccl" && transport_->multiProcess()) {
+    p2p_ = std::make_unique<P2PMailbox>(rank_, nrank_, device_id_, kEmbeddingWidth, transport_.get());
+    use_p2p_ = p2p_->usable();
+    if (!use_p2p_) p2p_.reset();
+  }
+  HCTR_CHECK(mode != "p2p" || use_p2p_, "HCTR_EXCHANGE=p2p but the ranks cannot map each other's memory");
+  info(*this, "exchange: ", exchangeName());
+}
+
+const char *HetuTable::exchangeName() const {
+  if (nrank_ == 1) return "none";
+  return use_p2p_ ? "p2p" : transport_->name();
 }
 
 // csrc/core/table_initialize.cu:66-114 — owner array, storage layout (cached rows first, stable),
@@ -227,6 +246,8 @@ void HetuTable::reserveShared(size_t batch) {
   d_need_push_.ensure((batch + 1) * sizeof(uint32_t));
   d_push_slot_.ensure((batch + 1) * sizeof(uint32_t));
   d_push_count_.ensure((size_t)nrank_ * sizeof(uint32_t));
+  d_push_base_.ensure((size_t)nrank_ * sizeof(uint32_t));
+  d_recv_idx_.ensure((batch + 1) * sizeof(uint32_t));
   if (nrank_ > 1) {
     const size_t n = nrank_;
     d_cnt_s_.ensure(2 * n * sizeof(uint32_t));
@@ -254,6 +275,7 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   BatchDesc &cur = cur_batch_, &prev = prev_batch_;
   reserveBatch(cur, std::max<size_t>(batch_size, 1));
   reserveShared(std::max<size_t>(batch_size, 1));
+  if (use_p2p_) p2p_->reserve(std::max<size_t>(batch_size, 1), stream_main_);  // collective when it grows
   cur.batch_size = batch_size;
   const int n = nrank_;
   const size_t meta_words = HCTR_META_WORDS + n + 1;
@@ -303,15 +325,17 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
     HCTR_LAUNCH(hctr_push_decide(prev.meta.as<uint32_t>(), n, rank_, prev.unique_size, prev.uniq_owner.as<uint8_t>(),
                                  prev.uniq_row.as<int32_t>(), prev.run_start.as<uint32_t>(), d_updates_.as<int64_t>(),
                                  push_bound_, d_need_push_.as<uint32_t>(), d_push_slot_.as<uint32_t>(),
-                                 d_scan_.as<uint32_t>(), d_push_count_.as<uint32_t>(), stream_main_));
+                                 d_scan_.as<uint32_t>(), d_push_count_.as<uint32_t>(), d_push_base_.as<uint32_t>(),
+                                 stream_main_));
     toc(sp);
   }
+  prev_push_valid_ = decide;
 
   uint32_t *h_meta = h_pinned_;
   uint32_t *h_cnt_s = h_pinned_ + meta_words;
   uint32_t *h_cnt_r = h_cnt_s + 2 * n;
   HCTR_CUDA(cudaMemcpyAsync(h_meta, cur.meta.p, meta_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
-  if (n > 1) {
+  if (n > 1 && !use_p2p_) {
     // One packed count exchange instead of the reference's two all2allExchangeShape rounds
     // (csrc/core/preprocess.cu:135,176): per peer {keys I will query, rows I will push}.
     HCTR_LAUNCH(hctr_pack_counts(cur.meta.as<uint32_t>(), decide ? d_push_count_.as<uint32_t>() : nullptr, n,
@@ -325,7 +349,8 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
     HCTR_CUDA(cudaMemcpyAsync(h_cnt_s, d_cnt_s_.p, 2 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
     HCTR_CUDA(cudaMemcpyAsync(h_cnt_r, d_cnt_r_.p, 2 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
   }
-  if (n == 1) {
+  if (n == 1 || use_p2p_) {
+    // (Single rank, or the device-driven exchange where counts never visit the host.)
     // Nothing on the host depends on the result before push_pull: wait only until the caller's key
     // buffer has been consumed and let the rest of the pipeline run under the next call's launches.
     // The batch's sizes (and a key-range error, if any) are picked up at the next synchronisation.
@@ -353,9 +378,10 @@ void HetuTable::finalizeBatch() {
   for (int p = 0; p <= n; p++) cur.seg[p] = h_meta[HCTR_META_SEG + p];
   for (int p = 0; p < n; p++) {
     cur.query_send[p] = cur.seg[p + 1] - cur.seg[p];
-    cur.query_recv[p] = n > 1 ? h_cnt_r[2 * p] : cur.query_send[p];
-    prev.push_send[p] = n > 1 ? h_cnt_s[2 * p + 1] : 0;
-    prev.push_recv[p] = n > 1 ? h_cnt_r[2 * p + 1] : 0;
+    const bool host_counts = n > 1 && !use_p2p_;  // the device-driven exchange keeps counts on the device
+    cur.query_recv[p] = host_counts ? h_cnt_r[2 * p] : cur.query_send[p];
+    prev.push_send[p] = host_counts ? h_cnt_s[2 * p + 1] : 0;
+    prev.push_recv[p] = host_counts ? h_cnt_r[2 * p + 1] : 0;
   }
   if (h_meta[HCTR_META_ERR] & HCTR_ERR_KEY_RANGE) {
     // leave a consistent (empty) batch behind, then report
@@ -463,6 +489,9 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     r.push_updates = d_pupd_s_.as<int64_t>();
     r.push_val = d_pval_s_.as<float>();
     r.work_counter = d_err_.as<uint32_t>() + 32;
+    r.p2p = use_p2p_ ? &p2p_->ctx() : nullptr;
+    r.uniq_owner = prev.uniq_owner.as<uint8_t>();
+    r.push_base = d_push_base_.as<uint32_t>();
     r.side_stream = stream_side_;
     r.fork_event = ev_fork_;
     r.join_event = ev_join_;
@@ -477,6 +506,8 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
                                  nullptr, d_embedding_.as<float>(), dst_dev, stream_main_));
     toc(sp);
+  } else if (use_p2p_) {
+    exchangeP2P(dst_dev);
   } else {
     const size_t U = cur.unique_size;
     // B. query = (key, local version) for every unique key (generateQuery)
@@ -645,6 +676,114 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     finalizeBatch();
     stats_.unique = cur.unique_size;
   }
+  uint32_t p2p_err = 0;
+  if (p2p_counts_pending_) {
+    p2p_counts_pending_ = false;
+    const uint32_t *h_cnt = h_pinned_ + HCTR_META_WORDS + n + 1 + 4 * n;
+    stats_.queried_keys = stats_.received_push_rows = stats_.received_rows = 0;
+    for (int p = 0; p < n; p++) {
+      cur.query_recv[p] = h_cnt[p];
+      prev.push_recv[p] = h_cnt[n + p];
+      cur.ret_recv[p] = h_cnt[2 * n + p];
+      stats_.queried_keys += h_cnt[p];
+      stats_.received_push_rows += h_cnt[n + p];
+      stats_.received_rows += h_cnt[2 * n + p];
+    }
+    p2p_err = h_cnt[3 * n];
+    if (p2p_err) HCTR_CUDA(cudaMemsetAsync(d_err_.p, 0, sizeof(uint32_t), stream_main_));
+  }
+  if (p2p_err & HCTR_ERR_TIMEOUT)
+    throw std::runtime_error("push_pull: a peer's message did not arrive in time (is every rank calling push_pull?)");
+  if (p2p_err & HCTR_ERR_NOT_OWNER)
+    throw std::runtime_error("push_pull: a peer addressed a key to a rank that does not own it (root_arr differs between ranks?)");
+  if (p2p_err & HCTR_ERR_CAPACITY)
+    throw std::runtime_error("push_pull: a peer sent more rows than the mailbox holds (ranks must use the same batch size)");
+}
+
+// ------------------------------------------------------------------------------------------------
+// Steps B-E of pushPull with the device-driven peer-to-peer exchange: no NCCL call and no host
+// synchronisation inside the step; every count stays on the device.
+// ------------------------------------------------------------------------------------------------
+void HetuTable::exchangeP2P(embed_t *dst_dev) {
+  BatchDesc &cur = cur_batch_;
+  const int n = nrank_;
+  const size_t W = kEmbeddingWidth;
+  const hctr_p2p_ctx ctx_copy = [&] {
+    hctr_p2p_ctx c = p2p_->ctx();
+    c.err = d_err_.as<uint32_t>();
+    return c;
+  }();
+  const hctr_p2p_ctx *c = &ctx_copy;
+  const uint32_t seq = p2p_->nextSeq();
+  const size_t cap = p2p_->capacity();
+  const size_t slots = (size_t)n * cap;
+  const size_t u_max = cur.batch_size;  // U is only known on the device here
+  const uint32_t *meta = cur.meta.as<uint32_t>();
+  d_flag32_.ensure((std::max(slots, u_max) + 1) * sizeof(uint32_t));
+  d_ret_slot_.ensure((slots + 1) * sizeof(uint32_t));
+  d_flag_r_.ensure(u_max + 16);
+  d_retcnt_s_.ensure((size_t)n * sizeof(uint32_t));
+
+  // B. queries straight into the owners' mailboxes, then publish counts + sequence number
+  int sp = tic(kPhQuery);
+  HCTR_LAUNCH(hctr_p2p_query_send(c, meta, u_max, cur.uniq.as<int64_t>(), cur.uniq_owner.as<uint8_t>(),
+                                  cur.uniq_row.as<int32_t>(), d_version_.as<int64_t>(), stream_main_));
+  toc(sp);
+  sp = tic(kPhExchange);
+  HCTR_LAUNCH(hctr_p2p_signal(c, 0, seq, meta, prev_push_valid_ && prev_batch_.unique_size > 0
+                                                   ? d_push_count_.as<uint32_t>() : nullptr, stream_main_));
+  HCTR_LAUNCH(hctr_p2p_wait(c, 0, seq, stream_main_));
+  toc(sp);
+
+  // C. owner applies the pushed rows of each source in rank order
+  const hctr_p2p_box mine = p2p_->mine();
+  sp = tic(kPhOwnerUpdate);
+  for (int s = 0; s < n; s++) {
+    if (s == rank_) continue;  // a rank never pushes to itself
+    HCTR_LAUNCH(hctr_owner_update_dev(cap, c->cnt_in + n + s, W, mine.pkey + (size_t)s * cap, mine.pupd + (size_t)s * cap,
+                                      mine.pval + (size_t)s * cap * W, d_row_of_.as<int32_t>(), kEmbeddingIDMax,
+                                      kNonLocalStorageMax, d_embedding_.as<float>(), d_version_.as<int64_t>(),
+                                      d_err_.as<uint32_t>(), stream_main_));
+  }
+  toc(sp);
+
+  // D. staleness, per-requester counts, rows gathered into the requesters' mailboxes
+  sp = tic(kPhStaleGather);
+  HCTR_LAUNCH(hctr_p2p_stale_check(c, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
+                                   d_version_.as<int64_t>(), pull_bound_, d_flag32_.as<uint32_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_scan_exclusive_u32(d_flag32_.as<uint32_t>(), d_ret_slot_.as<uint32_t>(), slots, nullptr,
+                                      d_scan_.as<uint32_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_p2p_return_counts(c, d_ret_slot_.as<uint32_t>(), d_retcnt_s_.as<uint32_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_p2p_gather(c, d_flag32_.as<uint32_t>(), d_ret_slot_.as<uint32_t>(), d_row_of_.as<int32_t>(),
+                              d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
+  toc(sp);
+  sp = tic(kPhExchange);
+  HCTR_LAUNCH(hctr_p2p_signal(c, 1, seq, meta, d_retcnt_s_.as<uint32_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_p2p_wait(c, 1, seq, stream_main_));
+  toc(sp);
+
+  // E. requester: flags -> row indices in its own mailbox, cache refresh, expand
+  sp = tic(kPhRefresh);
+  HCTR_LAUNCH(hctr_p2p_recv_flags(c, meta, u_max, cur.uniq_owner.as<uint8_t>(), d_flag_r_.as<uint8_t>(),
+                                  d_flag32_.as<uint32_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_scan_exclusive_u32(d_flag32_.as<uint32_t>(), d_recv_slot_.as<uint32_t>(), u_max, nullptr,
+                                      d_scan_.as<uint32_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_p2p_recv_index(c, meta, u_max, cur.uniq_owner.as<uint8_t>(), d_recv_slot_.as<uint32_t>(),
+                                  d_recv_idx_.as<uint32_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_cache_refresh(u_max, W, d_flag_r_.as<uint8_t>(), d_recv_idx_.as<uint32_t>(),
+                                 cur.uniq_row.as<int32_t>(), mine.rval, mine.rver, d_gradient_.as<float>(),
+                                 d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
+  toc(sp);
+  sp = tic(kPhExpand);
+  HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
+                               d_recv_idx_.as<uint32_t>(), mine.rval, d_embedding_.as<float>(), dst_dev, stream_main_));
+  toc(sp);
+
+  // counts and the error word come back with the step's final synchronisation
+  uint32_t *h_cnt = h_pinned_ + HCTR_META_WORDS + n + 1 + 4 * n;  // [3n] + error word
+  HCTR_CUDA(cudaMemcpyAsync(h_cnt, c->cnt_in, 3 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+  HCTR_CUDA(cudaMemcpyAsync(h_cnt + 3 * n, d_err_.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+  p2p_counts_pending_ = true;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -729,7 +868,17 @@ long long HetuTable::dump(const std::string &what, bool prev, void *out) {
   if (what == "root") return copy_widen<uint8_t>(b.uniq_owner.p, U, out, s);
   if (what == "offset") return copy_widen<int32_t>(b.uniq_row.p, U, out, s);
   if (what == "shape") return copy_sizes(b.query_send, nrank_, out);
-  if (what == "shape_exchanged") return copy_sizes(b.query_recv, nrank_, out);
+  if (what == "shape_exchanged") {
+    if (use_p2p_ && !prev) {
+      // The device-driven exchange never brings the peers' counts to the host before push_pull, so this
+      // view is assembled on demand with a host all-gather: COLLECTIVE in that mode (every rank must ask).
+      std::vector<unsigned long long> mine(nrank_), all((size_t)nrank_ * nrank_);
+      for (int p = 0; p < nrank_; p++) mine[p] = b.query_send[p];
+      transport_->allgatherHost(mine.data(), all.data(), nrank_ * sizeof(unsigned long long));
+      for (int p = 0; p < nrank_; p++) b.query_recv[p] = (size_t)all[(size_t)p * nrank_ + rank_];
+    }
+    return copy_sizes(b.query_recv, nrank_, out);
+  }
   if (what == "push_shape") return copy_sizes(b.push_send, nrank_, out);
   if (what == "push_shape_exchanged") return copy_sizes(b.push_recv, nrank_, out);
   if (what == "return_shape") return copy_sizes(b.ret_send, nrank_, out);
@@ -780,10 +929,11 @@ void HetuTable::releaseAll() {
   cudaSetDevice(device_id_);
   if (stream_side_) cudaStreamSynchronize(stream_side_);
   if (stream_main_) cudaStreamSynchronize(stream_main_);
+  p2p_.reset();
   transport_.reset();
   DevBuf *all[] = {&d_embedding_, &d_gradient_, &d_updates_, &d_version_, &d_root_, &d_row_of_, &d_stored_keys_,
                    &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_blk_base_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_cnt_,
-                   &d_need_push_, &d_push_slot_, &d_push_count_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
+                   &d_need_push_, &d_push_slot_, &d_push_count_, &d_push_base_, &d_recv_idx_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
                    &d_qkey_r_, &d_qver_r_, &d_pkey_s_, &d_pupd_s_, &d_pval_s_, &d_pkey_r_, &d_pupd_r_, &d_pval_r_,
                    &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,
                    &d_retcnt_r_, &d_rver_s_, &d_rval_s_, &d_rver_r_, &d_rval_r_, &d_stage_grad_, &d_stage_dst_};

@@ -17,6 +17,7 @@
 namespace hetuCTR {
 
 class Transport;
+class P2PMailbox;
 
 // csrc/core/types.h:12-28
 typedef float embed_t;
@@ -124,6 +125,8 @@ class HetuTable {
   // Overwrites the local rows (local row order) from host memory.
   void setEmbedding(const embed_t *host_rows);
   const StepStats &stats() const { return stats_; }
+  // "none" (single rank), "nccl", "inproc" or "p2p"
+  const char *exchangeName() const;
   // Per-phase device time.  While enabled, every phase is bracketed by two events on the table's
   // stream; times are summed when the call that recorded them has drained the stream.
   void setProfile(bool on);
@@ -139,12 +142,17 @@ class HetuTable {
   void releaseAll();
   void finalizeBatch();
   void finalizePending();
+  void exchangeP2P(embed_t *dst_dev);
   const void *stageIn(const void *ptr, size_t bytes, DevBuf &buf);
 
   cudaStream_t stream_main_ = nullptr;
   cudaStream_t stream_side_ = nullptr;  // overlaps the long-run kernels with their short-run twins
   cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr, ev_keys_ = nullptr;
   std::unique_ptr<Transport> transport_;
+  std::unique_ptr<P2PMailbox> p2p_;  // device-driven exchange (one process per GPU, peer access); else NCCL groups
+  bool use_p2p_ = false;
+  bool p2p_counts_pending_ = false;
+  bool prev_push_valid_ = false;     // d_push_count_/d_push_base_ describe prev_batch_
 
   // table state
   DevBuf d_embedding_, d_gradient_, d_updates_, d_version_, d_root_, d_row_of_, d_stored_keys_;
@@ -152,7 +160,7 @@ class HetuTable {
 
   // dedupe scratch (persistent, all-zero between calls) and per-step scratch
   DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_blk_base_, d_word_base_, d_scan_, d_sk_, d_rank_, d_cnt_;
-  DevBuf d_need_push_, d_push_slot_, d_push_count_, d_err_;
+  DevBuf d_need_push_, d_push_slot_, d_push_count_, d_push_base_, d_recv_idx_, d_err_;
   size_t shared_capacity_ = 0;
 
   // exchange buffers: *_s = send side, *_r = receive side

@@ -33,6 +33,7 @@ class NcclTransport : public Transport {
     TCPRendezvous tcp(rank, nrank, ip, port);
     tcp.broadcast(&uid, sizeof(uid));
     HCTR_NCCL(ncclCommInitRank(&comm_, nrank, uid, rank));
+    nrank_ = nrank;
   }
   ~NcclTransport() override {
     if (comm_) ncclCommDestroy(comm_);
@@ -46,9 +47,20 @@ class NcclTransport : public Transport {
     HCTR_NCCL(ncclGroupEnd());
   }
   const char *name() const override { return "nccl"; }
+  bool multiProcess() const override { return true; }
+  void allgatherHost(const void *mine, void *all, size_t bytes) override {
+    char *d = nullptr;
+    HCTR_CUDA(cudaMalloc(reinterpret_cast<void **>(&d), bytes * (nrank_ + 1)));
+    HCTR_CUDA(cudaMemcpy(d, mine, bytes, cudaMemcpyHostToDevice));
+    HCTR_NCCL(ncclAllGather(d, d + bytes, bytes, ncclChar, comm_, nullptr));
+    HCTR_CUDA(cudaStreamSynchronize(nullptr));
+    HCTR_CUDA(cudaMemcpy(all, d + bytes, bytes * nrank_, cudaMemcpyDeviceToHost));
+    cudaFree(d);
+  }
 
  private:
   ncclComm_t comm_ = nullptr;
+  int nrank_ = 1;
 };
 
 // ------------------------------------------------------------------------------------------------
@@ -122,6 +134,19 @@ class InprocTransport : public Transport {
     world_->barrier();  // nobody reuses a send range before every reader is done
   }
   const char *name() const override { return "inproc"; }
+  bool multiProcess() const override { return false; }
+  void allgatherHost(const void *mine, void *all, size_t bytes) override {
+    std::vector<XferItem> items;
+    items.push_back({rank_, mine, bytes, nullptr, 0});
+    {
+      std::lock_guard<std::mutex> g(world_->mu);
+      world_->posted[rank_] = items;
+    }
+    world_->barrier();
+    for (int p = 0; p < world_->nrank; p++)
+      std::memcpy(static_cast<char *>(all) + (size_t)p * bytes, world_->posted[p][0].send, bytes);
+    world_->barrier();
+  }
 
  private:
   int rank_;

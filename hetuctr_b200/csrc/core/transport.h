@@ -31,6 +31,10 @@ class Transport {
   // (in-process).
   virtual void exchange(const std::vector<XferItem> &items, cudaStream_t stream) = 0;
   virtual const char *name() const = 0;
+  // Host-memory all-gather of `bytes` per rank (set-up paths only); acts as a barrier.
+  virtual void allgatherHost(const void *mine, void *all, size_t bytes) = 0;
+  // True when ranks are separate processes that each drive their own GPU.
+  virtual bool multiProcess() const = 0;
 };
 
 // ip == "inproc" selects the in-process transport (all ranks of the job must use the same port value,

@@ -1,5 +1,7 @@
 // Gradient side of a step: push decision, duplicate-gradient reduction fused with the local SGD
 // apply and the packing of pushed rows, and the owner-side apply of received rows.
+#include <cstring>
+
 #include "rowops.cuh"
 
 namespace hctr {
@@ -24,11 +26,12 @@ __global__ void __launch_bounds__(kThreads) push_decide(const u32 *__restrict__ 
 }
 
 __global__ void push_counts(const u32 *__restrict__ meta, int nrank, const u32 *__restrict__ push_slot,
-                            u32 *__restrict__ push_count) {
+                            u32 *__restrict__ push_count, u32 *__restrict__ push_base) {
   const int p = threadIdx.x;
   if (p < nrank) {
     const u32 *seg = meta + HCTR_META_SEG;
     push_count[p] = push_slot[seg[p + 1]] - push_slot[seg[p]];
+    if (push_base) push_base[p] = push_slot[seg[p]];
   }
 }
 
@@ -48,8 +51,44 @@ struct RowTarget {
   int32_t row;
 };
 
+// Where a pushed row goes: the local send buffers, or (peer-to-peer routing) this rank's sub-region in
+// the owner's mailbox.
+struct PushDest {
+  long long *key, *upd;
+  float *val;
+};
+
+struct ReduceKernelArgs {
+  hctr_reduce_args a;
+  hctr_p2p_ctx p2p;  // valid when a.p2p != nullptr
+};
+
+__device__ __forceinline__ PushDest push_dest(const hctr_reduce_args &a, const hctr_p2p_ctx &c, size_t u,
+                                              size_t slot) {
+  PushDest d;
+  if (a.p2p) {
+    const unsigned p = a.uniq_owner[u];
+    size_t j = slot - a.push_base[p];
+    if (j >= c.cap) {  // cannot happen when every rank uses the same batch size; never write out of bounds
+      atomicOr(c.err, HCTR_ERR_CAPACITY);
+      j = 0;
+    }
+    const hctr_p2p_box b = c.box[p];
+    const size_t idx = (size_t)c.rank * c.cap + j;
+    d.key = reinterpret_cast<long long *>(b.pkey) + idx;
+    d.upd = reinterpret_cast<long long *>(b.pupd) + idx;
+    d.val = b.pval + idx * a.width;
+  } else {
+    d.key = reinterpret_cast<long long *>(a.push_key) + slot;
+    d.upd = reinterpret_cast<long long *>(a.push_updates) + slot;
+    d.val = a.push_val + slot * a.width;
+  }
+  return d;
+}
+
 // bookkeeping of one unique key (one thread): versions, pending counts, packed id + update count
-__device__ __forceinline__ RowTarget reduce_bookkeeping(const hctr_reduce_args &a, size_t u, u32 count, bool lead) {
+__device__ __forceinline__ RowTarget reduce_bookkeeping(const hctr_reduce_args &a, const hctr_p2p_ctx &c, size_t u,
+                                                        u32 count, bool lead, PushDest *dest) {
   RowTarget t;
   t.row = a.uniq_row[u];
   const bool need = a.need_push ? a.need_push[u] != 0 : false;
@@ -57,21 +96,23 @@ __device__ __forceinline__ RowTarget reduce_bookkeeping(const hctr_reduce_args &
   else if ((size_t)t.row >= a.n_cached) t.type = 1;
   else t.type = need ? 2 : 3;
   t.slot = need ? a.push_slot[u] : 0;
+  if (need) *dest = push_dest(a, c, u, t.slot);
+  else dest->key = nullptr, dest->upd = nullptr, dest->val = nullptr;
   if (lead) {
-    long long c = (long long)count;
-    if (t.type == 1) a.version[t.row] = (long long)((u64)a.version[t.row] + (u64)c);
+    long long cnt = (long long)count;
+    if (t.type == 1) a.version[t.row] = (long long)((u64)a.version[t.row] + (u64)cnt);
     else if (t.type >= 2) {
-      long long pc = a.pending_cnt[t.row] + c;
+      long long pc = a.pending_cnt[t.row] + cnt;
       if (t.type == 2) {
-        c = pc;
+        cnt = pc;
         pc = 0;
-        a.version[t.row] = (long long)((u64)a.version[t.row] + (u64)c);
+        a.version[t.row] = (long long)((u64)a.version[t.row] + (u64)cnt);
       }
       a.pending_cnt[t.row] = pc;
     }
     if (need) {
-      a.push_key[t.slot] = a.uniq[u];
-      a.push_updates[t.slot] = c;
+      *dest->key = a.uniq[u];
+      *dest->upd = cnt;
     }
   }
   return t;
@@ -98,7 +139,8 @@ __device__ __forceinline__ void reduce_apply(const RowTarget &t, typename R::T s
 
 // Short runs (<= HCTR_LIGHT_RUN positions): one group of LANES lanes per unique key.
 template <int LANES, bool VEC>
-__global__ void __launch_bounds__(kThreads) grad_reduce_short(hctr_reduce_args a) {
+__global__ void __launch_bounds__(kThreads) grad_reduce_short(ReduceKernelArgs ka) {
+  const hctr_reduce_args &a = ka.a;
   typedef RowT<VEC> R;
   typedef typename R::T T;
   const size_t u = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES;
@@ -106,12 +148,13 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short(hctr_reduce_args a
   if (u >= a.n_unique) return;
   const u32 l = a.run_start[u], r = a.run_start[u + 1];
   if (r - l > HCTR_LIGHT_RUN) return;  // handled by grad_reduce_long
-  const RowTarget t = reduce_bookkeeping(a, u, r - l, gl == 0);
+  PushDest dest;
+  const RowTarget t = reduce_bookkeeping(a, ka.p2p, u, r - l, gl == 0, &dest);
   const size_t E = R::elems(a.width);
   const T *grad = reinterpret_cast<const T *>(a.grad);
   T *emb = reinterpret_cast<T *>(a.embedding) + (t.row >= 0 ? (size_t)t.row * E : 0);
   T *pend = reinterpret_cast<T *>(a.pending) + (t.type >= 2 ? (size_t)t.row * E : 0);
-  T *out = reinterpret_cast<T *>(a.push_val) + t.slot * E;
+  T *out = reinterpret_cast<T *>(dest.val);
   for (size_t c = gl; c < E; c += LANES) {
     T sum = R::zero();
     u32 j = l;
@@ -152,7 +195,8 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short(hctr_reduce_args a
 // sums and applies key k the first gradient row and the table row of the next key are already in
 // flight.  The chunk is small so that a batch still yields enough warps to fill every SM.
 constexpr unsigned kWideChunk = 8;
-__global__ void __launch_bounds__(kThreads) grad_reduce_short_wide(hctr_reduce_args a) {
+__global__ void __launch_bounds__(kThreads) grad_reduce_short_wide(ReduceKernelArgs ka) {
+  const hctr_reduce_args &a = ka.a;
   typedef RowT<true> R;
   typedef float4 T;
   const unsigned lane = threadIdx.x & 31;
@@ -162,20 +206,21 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_wide(hctr_reduce_a
   const T *grad = reinterpret_cast<const T *>(a.grad);
   T *emb_base = reinterpret_cast<T *>(a.embedding);
   T *pend_base = reinterpret_cast<T *>(a.pending);
-  T *out_base = reinterpret_cast<T *>(a.push_val);
   for (size_t u0 = warp * kWideChunk; u0 < a.n_unique; u0 += n_warps * kWideChunk) {
     const size_t my_u = u0 + lane;
-    u32 l = 0, len = 0, p0 = 0, slot = 0;
-    int row = 0, type = -1;  // type -1: nothing to do for this lane's key
+    u32 l = 0, len = 0, p0 = 0;
+    unsigned long long outp = 0;  // destination of this lane's key if it is pushed
+    int row = 0, type = -1;       // type -1: nothing to do for this lane's key
     if (lane < kWideChunk && my_u < a.n_unique) {
       l = a.run_start[my_u];
       len = a.run_start[my_u + 1] - l;
       if (len > 0 && len <= HCTR_LIGHT_RUN) {
         p0 = a.sorted_pos[l];
-        const RowTarget t = reduce_bookkeeping(a, my_u, len, true);
+        PushDest dest;
+        const RowTarget t = reduce_bookkeeping(a, ka.p2p, my_u, len, true, &dest);
         row = t.row;
         type = t.type;
-        slot = (u32)t.slot;
+        outp = (unsigned long long)dest.val;
       }
     }
     unsigned todo = __ballot_sync(0xffffffffu, type >= 0);
@@ -192,7 +237,7 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_wide(hctr_reduce_a
     }
     while (k >= 0) {
       const u32 lk = __shfl_sync(0xffffffffu, l, k), lenk = __shfl_sync(0xffffffffu, len, k);
-      const u32 slotk = __shfl_sync(0xffffffffu, slot, k);
+      const unsigned long long outk = __shfl_sync(0xffffffffu, outp, k);
       const int rowk = __shfl_sync(0xffffffffu, row, k), typek = __shfl_sync(0xffffffffu, type, k);
       const T g0 = g_next, e0 = e_next;
       const int kn = todo ? __ffs(todo) - 1 : -1;
@@ -205,7 +250,7 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_wide(hctr_reduce_a
       }
       T *emb = emb_base + (typek != 0 ? (size_t)rowk * E : 0);
       T *pend = pend_base + (typek >= 2 ? (size_t)rowk * E : 0);
-      T *out = out_base + (size_t)slotk * E;
+      T *out = reinterpret_cast<T *>(outk);
       for (size_t c = lane; c < E; c += 32) {
         T sum, e_old;
         if (c == lane) {
@@ -265,7 +310,8 @@ __device__ __forceinline__ void cp_async_elem(void *smem_dst, const void *gsrc) 
 }
 
 template <bool VEC>
-__global__ void __launch_bounds__(kLongThreads) grad_reduce_long(hctr_reduce_args a, u32 n_heavy, u32 *work_counter) {
+__global__ void __launch_bounds__(kLongThreads) grad_reduce_long(ReduceKernelArgs ka, u32 n_heavy, u32 *work_counter) {
+  const hctr_reduce_args &a = ka.a;
   typedef RowT<VEC> R;
   typedef typename R::T T;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -298,7 +344,8 @@ __global__ void __launch_bounds__(kLongThreads) grad_reduce_long(hctr_reduce_arg
     const size_t u = a.heavy_list[h];
     const u32 l = a.run_start[u], len = a.run_start[u + 1] - l;
     if ((len >= kVeryLongRun) != (pass == 0)) continue;
-    const RowTarget t = reduce_bookkeeping(a, u, len, tid == 0);
+    PushDest dest;
+    const RowTarget t = reduce_bookkeeping(a, ka.p2p, u, len, tid == 0, &dest);
     // columns are processed in slabs of up to 4 per thread (width <= 1024 needs a single pass)
     for (size_t col0 = 0; col0 < W; col0 += 4 * kLongThreads) {
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
@@ -356,7 +403,7 @@ __global__ void __launch_bounds__(kLongThreads) grad_reduce_long(hctr_reduce_arg
       }
       float *emb = a.embedding + (t.row >= 0 ? (size_t)t.row * W : 0);
       float *pend = a.pending + (t.type >= 2 ? (size_t)t.row * W : 0);
-      float *out = a.push_val + t.slot * W;
+      float *out = dest.val;
 #pragma unroll
       for (int k = 0; k < 4; k++) {
         const size_t col = col0 + tid + (size_t)k * kLongThreads;
@@ -368,7 +415,8 @@ __global__ void __launch_bounds__(kLongThreads) grad_reduce_long(hctr_reduce_arg
 
 // ---- owner-side apply of one source's rows -----------------------------------------------------
 template <int LANES, bool VEC>
-__global__ void __launch_bounds__(kThreads) owner_update(size_t n_rows, size_t width, const long long *__restrict__ key,
+__global__ void __launch_bounds__(kThreads) owner_update(size_t n_rows_max, const u32 *__restrict__ n_rows_dev, size_t width,
+                                                         const long long *__restrict__ key,
                                                          const long long *__restrict__ updates,
                                                          const float *__restrict__ val,
                                                          const int32_t *__restrict__ row_of, size_t length,
@@ -376,21 +424,23 @@ __global__ void __launch_bounds__(kThreads) owner_update(size_t n_rows, size_t w
                                                          long long *__restrict__ version, u32 *err) {
   typedef RowT<VEC> R;
   typedef typename R::T T;
-  const size_t m = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES;
   const unsigned gl = threadIdx.x % LANES;
-  if (m >= n_rows) return;
-  const long long k = key[m];
-  int32_t row = -1;
-  if (k >= 0 && (size_t)k < length) row = row_of[k];
-  if (row < 0 || (size_t)row < n_cached) {  // only an owner may receive pushes for a key
-    if (gl == 0) atomicOr(err, HCTR_ERR_NOT_OWNER);
-    return;
-  }
-  if (gl == 0) version[row] = (long long)((u64)version[row] + (u64)updates[m]);
+  const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
+  const size_t n_rows = n_rows_dev ? min((size_t)*n_rows_dev, n_rows_max) : n_rows_max;
   const size_t E = R::elems(width);
-  T *emb = reinterpret_cast<T *>(embedding) + (size_t)row * E;
-  const T *v = reinterpret_cast<const T *>(val) + m * E;
-  for (size_t c = gl; c < E; c += LANES) emb[c] = R::add(emb[c], R::ld_once(v + c));
+  for (size_t m = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; m < n_rows; m += groups) {
+    const long long k = key[m];
+    int32_t row = -1;
+    if (k >= 0 && (size_t)k < length) row = row_of[k];
+    if (row < 0 || (size_t)row < n_cached) {  // only an owner may receive pushes for a key
+      if (gl == 0) atomicOr(err, HCTR_ERR_NOT_OWNER);
+      continue;
+    }
+    if (gl == 0) version[row] = (long long)((u64)version[row] + (u64)updates[m]);
+    T *emb = reinterpret_cast<T *>(embedding) + (size_t)row * E;
+    const T *v = reinterpret_cast<const T *>(val) + m * E;
+    for (size_t c = gl; c < E; c += LANES) emb[c] = R::add(emb[c], R::ld_once(v + c));
+  }
 }
 
 }  // namespace hctr
@@ -401,7 +451,7 @@ extern "C" int hctr_push_decide(const uint32_t *meta, int nrank, int rank, size_
                                 const uint8_t *uniq_owner, const int32_t *uniq_row, const uint32_t *run_start,
                                 const int64_t *pending_cnt, int64_t push_bound, uint32_t *need_push,
                                 uint32_t *push_slot, uint32_t *scan_scratch, uint32_t *push_count,
-                                void *stream) {
+                                uint32_t *push_base, void *stream) {
   cudaStream_t s = (cudaStream_t)stream;
   if (nrank > 1024) return (int)cudaErrorInvalidValue;
   push_decide<<<grid_for(u_max, kThreads), kThreads, 0, s>>>(meta, rank, uniq_owner, uniq_row, run_start,
@@ -409,7 +459,7 @@ extern "C" int hctr_push_decide(const uint32_t *meta, int nrank, int rank, size_
                                                               need_push);
   int rc = hctr_scan_exclusive_u32(need_push, push_slot, u_max, meta + HCTR_META_UNIQUE, scan_scratch, stream);
   if (rc) return rc;
-  push_counts<<<1, 1024, 0, s>>>(meta, nrank, push_slot, push_count);
+  push_counts<<<1, 1024, 0, s>>>(meta, nrank, push_slot, push_count, push_base);
   count_launches(2);
   return launch_status();
 }
@@ -418,8 +468,12 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
   cudaStream_t s = (cudaStream_t)stream;
   const hctr_reduce_args a = *ap;
   if (a.n_unique == 0) return 0;
+  ReduceKernelArgs ka;
+  ka.a = a;
+  if (a.p2p) ka.p2p = *a.p2p;
+  else memset(&ka.p2p, 0, sizeof(ka.p2p));
   const bool al = host_aligned16(a.grad) && host_aligned16(a.embedding) && host_aligned16(a.pending) &&
-                  host_aligned16(a.push_val);
+                  host_aligned16(a.push_val);  // mailbox regions are 256-byte aligned by construction
   if (a.n_heavy > 0 && a.side_stream && a.fork_event && a.join_event) {
     cudaError_t e = cudaEventRecord((cudaEvent_t)a.fork_event, s);
     if (e != cudaSuccess) return (int)e;
@@ -428,10 +482,10 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
     size_t ctas = ((a.n_unique + kWideChunk - 1) / kWideChunk * 32 + kThreads - 1) / kThreads;
     const size_t cap = (size_t)kSMs * 8;
     if (ctas > cap) ctas = cap;
-    grad_reduce_short_wide<<<(unsigned)ctas, kThreads, 0, s>>>(a);
+    grad_reduce_short_wide<<<(unsigned)ctas, kThreads, 0, s>>>(ka);
   } else {
 #define CALL(L, V) \
-  grad_reduce_short<L, V><<<grid_for(a.n_unique * L, kThreads), kThreads, 0, s>>>(a)
+  grad_reduce_short<L, V><<<grid_for(a.n_unique * L, kThreads), kThreads, 0, s>>>(ka)
     HCTR_DISPATCH_ROWS(a.width, al, CALL);
 #undef CALL
   }
@@ -460,8 +514,8 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
     cudaError_t em = cudaMemsetAsync(a.work_counter, 0, 2 * sizeof(u32), ls);
     if (em != cudaSuccess) return (int)em;
     const unsigned grid = (unsigned)min((size_t)a.n_heavy, (size_t)kSMs * (need > 100 * 1024 ? 1 : 3));
-    if (al && a.width % 4 == 0) grad_reduce_long<true><<<grid, kLongThreads, need, ls>>>(a, (u32)a.n_heavy, a.work_counter);
-    else grad_reduce_long<false><<<grid, kLongThreads, need, ls>>>(a, (u32)a.n_heavy, a.work_counter);
+    if (al && a.width % 4 == 0) grad_reduce_long<true><<<grid, kLongThreads, need, ls>>>(ka, (u32)a.n_heavy, a.work_counter);
+    else grad_reduce_long<false><<<grid, kLongThreads, need, ls>>>(ka, (u32)a.n_heavy, a.work_counter);
     count_launches(1);
     if (ls != s) {
       cudaError_t e = cudaEventRecord((cudaEvent_t)a.join_event, ls);
@@ -472,18 +526,30 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
   return launch_status();
 }
 
-extern "C" int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int64_t *updates,
-                                 const float *val, const int32_t *row_of, size_t length, size_t n_cached,
-                                 float *embedding, int64_t *version, uint32_t *err, void *stream) {
+extern "C" int hctr_owner_update_dev(size_t n_rows_max, const uint32_t *n_rows_dev, size_t width, const int64_t *key,
+                                     const int64_t *updates, const float *val, const int32_t *row_of, size_t length,
+                                     size_t n_cached, float *embedding, int64_t *version, uint32_t *err,
+                                     void *stream) {
   cudaStream_t s = (cudaStream_t)stream;
-  if (n_rows == 0) return 0;
+  if (n_rows_max == 0) return 0;
   const bool al = host_aligned16(val) && host_aligned16(embedding);
-#define CALL(L, V)                                                                                    \
-  owner_update<L, V><<<grid_for(n_rows * L, kThreads), kThreads, 0, s>>>(                             \
-      n_rows, width, (const long long *)key, (const long long *)updates, val, row_of, length, n_cached, \
-      embedding, (long long *)version, err)
+#define CALL(L, V)                                                                                          \
+  do {                                                                                                      \
+    size_t g_ = (n_rows_max * L + kThreads - 1) / kThreads;                                                 \
+    if (g_ > (size_t)kSMs * 8) g_ = (size_t)kSMs * 8;                                                       \
+    owner_update<L, V><<<(unsigned)g_, kThreads, 0, s>>>(n_rows_max, n_rows_dev, width, (const long long *)key, \
+                                                         (const long long *)updates, val, row_of, length,   \
+                                                         n_cached, embedding, (long long *)version, err);   \
+  } while (0)
   HCTR_DISPATCH_ROWS(width, al, CALL);
 #undef CALL
   count_launches(1);
   return launch_status();
+}
+
+extern "C" int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int64_t *updates,
+                                 const float *val, const int32_t *row_of, size_t length, size_t n_cached,
+                                 float *embedding, int64_t *version, uint32_t *err, void *stream) {
+  return hctr_owner_update_dev(n_rows, nullptr, width, key, updates, val, row_of, length, n_cached, embedding, version,
+                               err, stream);
 }

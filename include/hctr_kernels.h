@@ -33,6 +33,7 @@ extern "C" {
 #define HCTR_ERR_KEY_RANGE 1u    /* a batch key is <0, >= length, or its owner id is >= nrank          */
 #define HCTR_ERR_NOT_OWNER 2u    /* an owner-side kernel met a key this rank does not store as owned   */
 #define HCTR_ERR_CAPACITY 4u     /* an internal list overflowed its reserved capacity                  */
+#define HCTR_ERR_TIMEOUT 8u      /* a peer's message did not arrive within the wait limit              */
 
 /* Keys of the dedupe bitmap are sort keys  sk = key + length_pad * owner  with length_pad = length
  * rounded up to HCTR_BLOCK_KEYS, so every owner's range starts on a bitmap-block boundary. */
@@ -169,10 +170,11 @@ int hctr_dedupe_map(const hctr_dedupe_args *a, void *stream);
  * with occurrences(u) = run_start[u+1] - run_start[u].
  * Then push_slot = exclusive scan of need_push (U+1 entries) and push_count[p] = pushes to owner p.
  * U is read from meta (device). */
+/* push_base[p] (optional output, device [nrank]) = push_slot at the first unique key of owner p. */
 int hctr_push_decide(const uint32_t *meta, int nrank, int rank, size_t u_max, const uint8_t *uniq_owner,
                      const int32_t *uniq_row, const uint32_t *run_start, const int64_t *pending_cnt,
                      int64_t push_bound, uint32_t *need_push, uint32_t *push_slot,
-                     uint32_t *scan_scratch, uint32_t *push_count, void *stream);
+                     uint32_t *scan_scratch, uint32_t *push_count, uint32_t *push_base, void *stream);
 
 /* Packs the per-peer counts a rank announces after preprocess: out[2p] = unique keys of the current
  * batch owned by p (from meta's segment starts), out[2p+1] = push_count[p] (0 when push_count is null).
@@ -183,6 +185,76 @@ int hctr_pack_counts(const uint32_t *meta, const uint32_t *push_count, int nrank
  * Gradient aggregation + local SGD apply + pack of pushed rows (previous batch).
  * Replaces gradient_index_kernel and gradient_reduction_kernel, csrc/core/generate_query.cu:8-89.
  * ------------------------------------------------------------------------------------------- */
+
+/* ---------------------------------------------------------------------------------------------
+ * Peer-to-peer exchange (one process per GPU, all GPUs of one NVLink domain).
+ *
+ * Every rank owns a MAILBOX in its own device memory, mapped into every peer through CUDA IPC.  Each
+ * region of a mailbox holds nrank sub-regions of `cap` rows; sub-region s is written only by source
+ * rank s (plain peer stores from that rank's kernels) and read only by the owner of the mailbox.
+ * A 64-byte header per source carries the counts and a sequence number written last with release
+ * semantics; the receiver's wait kernel polls its own memory with acquire loads, for at most
+ * `timeout_ns`, and reports HCTR_ERR_TIMEOUT instead of hanging.  This replaces the grouped
+ * ncclSend/ncclRecv rounds of csrc/core/all2all.cu:6-130 and the host synchronisations between them
+ * (csrc/core/hetu_gpu_table.cu:33,64): counts never leave the device.
+ * ------------------------------------------------------------------------------------------- */
+typedef struct hctr_p2p_box { /* one rank's mailbox as mapped into the calling GPU's address space */
+  uint32_t *hdr;  /* [nrank][16] words: 0 query seq, 1 query count, 2 push count, 8 return seq, 9 return count */
+  int64_t *qkey;  /* [nrank*cap]   queried keys                      (requester -> owner) */
+  int64_t *qver;  /* [nrank*cap]   requester's version of each key                        */
+  int64_t *pkey;  /* [nrank*cap]   ids of pushed rows                (requester -> owner) */
+  int64_t *pupd;  /* [nrank*cap]   update counts of pushed rows                           */
+  float *pval;    /* [nrank*cap*W] pushed rows                                            */
+  uint8_t *flag;  /* [nrank*cap]   stale flag per queried key        (owner -> requester) */
+  int64_t *rver;  /* [nrank*cap]   versions of returned rows                              */
+  float *rval;    /* [nrank*cap*W] returned rows                                          */
+} hctr_p2p_box;
+
+typedef struct hctr_p2p_ctx {
+  int nrank, rank;
+  uint32_t cap;             /* rows per (mailbox, source) sub-region */
+  size_t width;
+  const hctr_p2p_box *box;  /* device array [nrank]; box[rank] is this rank's own mailbox */
+  uint32_t *cnt_in;         /* device [3*nrank]: query, push and return counts received from each peer */
+  uint32_t *err;            /* device error word */
+  unsigned long long timeout_ns;
+} hctr_p2p_ctx;
+
+/* Requester: (key, local version) of every unique key, written into its owner's mailbox.
+ * U and the per-owner segment starts are read from the batch's meta words. */
+int hctr_p2p_query_send(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const int64_t *uniq,
+                        const uint8_t *uniq_owner, const int32_t *uniq_row, const int64_t *version, void *stream);
+
+/* Publishes this rank's counts to every peer and releases sequence number `seq`.
+ * phase 0: query count (from meta's segments) + push_count (null = zeros); phase 1: ret_count. */
+int hctr_p2p_signal(const hctr_p2p_ctx *c, int phase, uint32_t seq, const uint32_t *meta,
+                    const uint32_t *counts, void *stream);
+
+/* Waits (bounded) until every peer has released `seq` for `phase`; copies the announced counts into
+ * c->cnt_in.  On timeout sets HCTR_ERR_TIMEOUT and records zero counts for the silent peers. */
+int hctr_p2p_wait(const hctr_p2p_ctx *c, int phase, uint32_t seq, void *stream);
+
+/* Owner: staleness flags for all received queries (slot q = source*cap + j), flag bytes stored into the
+ * requesters' mailboxes, flags32 = 0/1 per slot (0 for unused slots). */
+int hctr_p2p_stale_check(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
+                         const int64_t *version, int64_t pull_bound, uint32_t *flags32, void *stream);
+
+/* Owner: ret_count[s] = rows to return to requester s, from the exclusive scan ret_slot of flags32. */
+int hctr_p2p_return_counts(const hctr_p2p_ctx *c, const uint32_t *ret_slot, uint32_t *ret_count, void *stream);
+
+/* Owner: flagged rows (+ versions) gathered straight into the requesters' mailboxes. */
+int hctr_p2p_gather(const hctr_p2p_ctx *c, const uint32_t *flags32, const uint32_t *ret_slot,
+                    const int32_t *row_of, const float *embedding, const int64_t *version, void *stream);
+
+/* Requester: flags of its unique keys collected from its mailbox (flags[u], flags32[u]; zeros for
+ * u >= U up to u_max). */
+int hctr_p2p_recv_flags(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const uint8_t *uniq_owner,
+                        uint8_t *flags, uint32_t *flags32, void *stream);
+
+/* Requester: recv_index[u] = row index (in units of rows, relative to box[rank].rval / rver) of the row
+ * returned for unique key u, from the exclusive scan recv_slot of flags32. */
+int hctr_p2p_recv_index(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const uint8_t *uniq_owner,
+                        const uint32_t *recv_slot, uint32_t *recv_index, void *stream);
 
 typedef struct hctr_reduce_args {
   size_t n_unique;            /* U of the previous batch (host value) */
@@ -206,6 +278,12 @@ typedef struct hctr_reduce_args {
   int64_t *push_updates;      /* [P] update counts */
   float *push_val;            /* [P, W] */
   uint32_t *work_counter;     /* two device words of scratch (needed when n_heavy > 0) */
+  /* optional peer-to-peer routing of pushed rows: when p2p is non-null, a pushed row of a key owned by
+   * rank p goes to slot (push_slot[u] - push_base[p]) of this rank's sub-region in p's mailbox instead
+   * of push_key / push_updates / push_val */
+  const hctr_p2p_ctx *p2p;    /* host pointer, copied into the launch */
+  const uint8_t *uniq_owner;  /* [U] */
+  const uint32_t *push_base;  /* device [nrank]: push_slot at the first unique key of each owner */
   /* optional: a second stream (cudaStream_t) and two events (cudaEvent_t, timing disabled) that let
    * the long-run kernel overlap the short-run kernel; null = everything on the call's stream */
   void *side_stream;
@@ -232,6 +310,10 @@ int hctr_query_versions(size_t n_unique, const int32_t *uniq_row, const int64_t 
 int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int64_t *updates,
                       const float *val, const int32_t *row_of, size_t length, size_t n_cached,
                       float *embedding, int64_t *version, uint32_t *err, void *stream);
+/* Same, with the row count read from device memory (at most n_rows_max). */
+int hctr_owner_update_dev(size_t n_rows_max, const uint32_t *n_rows_dev, size_t width, const int64_t *key,
+                          const int64_t *updates, const float *val, const int32_t *row_of, size_t length,
+                          size_t n_cached, float *embedding, int64_t *version, uint32_t *err, void *stream);
 
 /* Staleness decision for `n_query` received (key, version) pairs, laid out as nrank consecutive
  * segments whose starts are seg_start[0..nrank] (device, 32-bit).  stale = (v == INT64_MIN or

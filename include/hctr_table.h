@@ -91,6 +91,11 @@ int hctr_table_phase_times(hctr_table *t, double ms[HCTR_N_PHASES], long long ca
 int hctr_rendezvous_broadcast(int rank, int nrank, const char *ip, int port, void *data, size_t len,
                               double timeout_s);
 
+/* How this table exchanges data with its peers: "none" (single rank), "p2p" (device-driven mailboxes
+ * in peer memory; one process per GPU with peer access, the default when possible), "nccl" (grouped
+ * send/receive; forced with HCTR_EXCHANGE=nccl) or "inproc" (thread ranks of one process, tests). */
+const char *hctr_table_exchange_name(hctr_table *t);
+
 /* The CUDA stream (cudaStream_t) the table enqueues its work on. */
 void *hctr_table_stream(hctr_table *t);
 

@@ -5,12 +5,15 @@
 // reference class are public (csrc/core/hetu_gpu_table.h:22), so nothing in the reference is modified.
 #include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
 
 #include <cuda_runtime.h>
 
 #include <memory>
 #include <string>
 #include <algorithm>
+#include <chrono>
+#include <cstring>
 #include <vector>
 
 #include "core/hetu_gpu_table.h"
@@ -115,6 +118,72 @@ PYBIND11_MODULE(hetuCTR_ref, m) {
              return out;
            },
            py::arg("grad"), py::arg("n_cur"))
+      // Timed loop for the benchmark's reference arm: `steps` x (preprocess + push_pull) over the given key
+      // batches (cycled) with real gradients, after `warmup` untimed steps.  host_buffers = false: keys,
+      // gradients and dst are resident on the device before the clock starts; true: keys are passed as a
+      // host pointer and gradients / pulled rows are copied from / to pinned host memory every step.
+      // Every reference call ends with a stream synchronisation, so wall time around the loop is device time.
+      .def("bench_loop",
+           [](HetuTable &t, std::vector<py::array_t<long long, py::array::c_style | py::array::forcecast>> batches,
+              py::array_t<float, py::array::c_style | py::array::forcecast> grad, int steps, int warmup,
+              bool host_buffers) {
+             cudaSetDevice(t.device_id_);
+             const size_t W = t.kEmbeddingWidth, nb = batches.size();
+             const size_t B = batches[0].size();
+             std::vector<index_t *> dkeys(nb), hkeys(nb);
+             for (size_t i = 0; i < nb; i++) {
+               cudaMalloc(&dkeys[i], B * sizeof(index_t));
+               cudaMemcpy(dkeys[i], batches[i].data(), B * sizeof(index_t), cudaMemcpyHostToDevice);
+               cudaMallocHost(&hkeys[i], B * sizeof(index_t));
+               memcpy(hkeys[i], batches[i].data(), B * sizeof(index_t));
+             }
+             float *dgrad[2], *ddst, *hgrad = nullptr, *hdst = nullptr;
+             for (int i = 0; i < 2; i++) {
+               cudaMalloc(&dgrad[i], B * W * sizeof(float));
+               cudaMemcpy(dgrad[i], grad.data(), B * W * sizeof(float), cudaMemcpyHostToDevice);
+             }
+             cudaMalloc(&ddst, B * W * sizeof(float));
+             if (host_buffers) {
+               cudaMallocHost(&hgrad, B * W * sizeof(float));
+               cudaMallocHost(&hdst, B * W * sizeof(float));
+               memcpy(hgrad, grad.data(), B * W * sizeof(float));
+             }
+             double ms = 0;
+             {
+               py::gil_scoped_release rel;
+               t.preprocess(dkeys[nb - 1], B);
+               t.pushPull(nullptr, ddst);
+               auto one = [&](int i) {
+                 const size_t j = (size_t)i % nb;
+                 if (host_buffers) {
+                   t.preprocess(hkeys[j], B);
+                   cudaMemcpy(dgrad[i & 1], hgrad, B * W * sizeof(float), cudaMemcpyHostToDevice);
+                   t.pushPull(dgrad[i & 1], ddst);
+                   cudaMemcpy(hdst, ddst, B * W * sizeof(float), cudaMemcpyDeviceToHost);
+                 } else {
+                   t.preprocess(dkeys[j], B);
+                   t.pushPull(dgrad[i & 1], ddst);
+                 }
+               };
+               for (int i = 0; i < warmup; i++) one(i);
+               cudaDeviceSynchronize();
+               auto t0 = std::chrono::steady_clock::now();
+               for (int i = 0; i < steps; i++) one(i);
+               cudaDeviceSynchronize();
+               ms = std::chrono::duration<double, std::milli>(std::chrono::steady_clock::now() - t0).count();
+             }
+             for (size_t i = 0; i < nb; i++) {
+               cudaFree(dkeys[i]);
+               cudaFreeHost(hkeys[i]);
+             }
+             cudaFree(dgrad[0]);
+             cudaFree(dgrad[1]);
+             cudaFree(ddst);
+             if (hgrad) cudaFreeHost(hgrad);
+             if (hdst) cudaFreeHost(hdst);
+             return ms;
+           },
+           py::arg("batches"), py::arg("grad"), py::arg("steps"), py::arg("warmup"), py::arg("host_buffers"))
       .def("set_embedding",
            [](HetuTable &t, py::array_t<float, py::array::c_style | py::array::forcecast> rows) {
              cudaSetDevice(t.device_id_);

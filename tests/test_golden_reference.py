@@ -93,18 +93,20 @@ def test_initial_values_match_reference_build(name):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("exchange", ["p2p", "nccl"])
 @pytest.mark.parametrize("name", [n for n in sorted(cases.CASES) if cases.CASES[n]["nrank"] > 1])
-def test_multi_process_nccl_matches_oracle(oracle_mod, name, tmp_path):
-    """One process per GPU through the drop-in `hetuCTR` module over NCCL (sync and async calls, host and device key
-    buffers) against the oracle.  Needs as many GPUs as the case has ranks."""
+def test_multi_process_matches_oracle(oracle_mod, name, exchange, tmp_path):
+    """One process per GPU through the drop-in `hetuCTR` module (sync and async calls, host and device key buffers)
+    against the oracle, with both exchange flavours: device-driven peer-to-peer mailboxes and NCCL groups.
+    Needs as many GPUs as the case has ranks."""
     torch = pytest.importorskip("torch")
     c, root, storage, emb, keys, grads = cases.make_inputs(name)
     n = c["nrank"]
     if not torch.cuda.is_available() or torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
-    port = 25000 + (os.getpid() % 2000) + 10 * sorted(cases.CASES).index(name)
+    port = 25000 + (os.getpid() % 2000) + 10 * sorted(cases.CASES).index(name) + (5 if exchange == "p2p" else 0)
     outs = [str(tmp_path / f"r{r}.npz") for r in range(n)]
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", HCTR_EXCHANGE=exchange)
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "mp_worker.py"), name, str(r), str(port), outs[r]],
                               env=env) for r in range(n)]
     for p in procs:
