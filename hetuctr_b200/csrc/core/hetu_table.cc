@@ -82,6 +82,16 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
     HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
     HCTR_CUDA(cudaStreamCreateWithPriority(&stream_side_, cudaStreamNonBlocking, hi));
   }
+  HCTR_CUDA(cudaStreamCreateWithFlags(&stream_reduce_, cudaStreamNonBlocking));
+  {
+    int lo = 0, hi = 0;
+    HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_reduce_side_, cudaStreamNonBlocking, hi));
+  }
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_rfork_, cudaEventDisableTiming));
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_rjoin_, cudaEventDisableTiming));
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_decide_, cudaEventDisableTiming));
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_reduce_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_keys_, cudaEventDisableTiming | cudaEventBlockingSync));
@@ -313,22 +323,25 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   a.side_stream = stream_side_;
   a.fork_event = ev_fork_;
   a.join_event = ev_join_;
-  int sp = tic(kPhDedupe);
-  HCTR_LAUNCH(hctr_dedupe_map(&a, stream_main_));
-  toc(sp);
+  // The push decision for the previous batch goes first: the gradient reduction (on its own stream, started
+  // by the next push_pull) only needs this, not the dedupe of the new batch that follows.
 
   // Push decision for the previous batch (csrc/core/preprocess.cu:167-182).  With one rank every
   // row is owned, nothing is ever pushed.
   const bool decide = n > 1 && prev.unique_size > 0;
   if (decide) {
-    sp = tic(kPhPushDecide);
+    int spd = tic(kPhPushDecide);
     HCTR_LAUNCH(hctr_push_decide(prev.meta.as<uint32_t>(), n, rank_, prev.unique_size, prev.uniq_owner.as<uint8_t>(),
                                  prev.uniq_row.as<int32_t>(), prev.run_start.as<uint32_t>(), d_updates_.as<int64_t>(),
                                  push_bound_, d_need_push_.as<uint32_t>(), d_push_slot_.as<uint32_t>(),
                                  d_scan_.as<uint32_t>(), d_push_count_.as<uint32_t>(), d_push_base_.as<uint32_t>(),
                                  stream_main_));
-    toc(sp);
+    toc(spd);
   }
+  HCTR_CUDA(cudaEventRecord(ev_decide_, stream_main_));
+  int sp = tic(kPhDedupe);
+  HCTR_LAUNCH(hctr_dedupe_map(&a, stream_main_));
+  toc(sp);
   prev_push_valid_ = decide;
 
   uint32_t *h_meta = h_pinned_;
@@ -399,7 +412,7 @@ void HetuTable::finalizePending() {
   finalizeBatch();
 }
 
-const void *HetuTable::stageIn(const void *ptr, size_t bytes, DevBuf &buf) {
+const void *HetuTable::stageIn(const void *ptr, size_t bytes, DevBuf &buf, cudaStream_t st) {
   cudaPointerAttributes attr;
   cudaError_t e = cudaPointerGetAttributes(&attr, ptr);
   if (e != cudaSuccess) {
@@ -408,7 +421,7 @@ const void *HetuTable::stageIn(const void *ptr, size_t bytes, DevBuf &buf) {
   }
   if (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged) return ptr;
   buf.ensure(bytes);
-  HCTR_CUDA(cudaMemcpyAsync(buf.p, ptr, bytes, cudaMemcpyHostToDevice, stream_main_));
+  HCTR_CUDA(cudaMemcpyAsync(buf.p, ptr, bytes, cudaMemcpyHostToDevice, st));
   return buf.p;
 }
 
@@ -448,7 +461,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   }
   const embed_t *grad_dev = grad;
   if (grad != nullptr && prev.batch_size > 0)
-    grad_dev = static_cast<const embed_t *>(stageIn(grad, prev.batch_size * W * sizeof(embed_t), d_stage_grad_));
+    grad_dev = static_cast<const embed_t *>(stageIn(grad, prev.batch_size * W * sizeof(embed_t), d_stage_grad_, stream_reduce_));
 
   size_t pushed = 0, push_recv = 0, q_recv = 0;
   for (int p = 0; p < n; p++) {
@@ -492,12 +505,18 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     r.p2p = use_p2p_ ? &p2p_->ctx() : nullptr;
     r.uniq_owner = prev.uniq_owner.as<uint8_t>();
     r.push_base = d_push_base_.as<uint32_t>();
-    r.side_stream = stream_side_;
-    r.fork_event = ev_fork_;
-    r.join_event = ev_join_;
-    int sp = tic(kPhReduce);
-    HCTR_LAUNCH(hctr_grad_reduce_apply_pack(&r, stream_main_));
-    toc(sp);
+    r.side_stream = stream_reduce_side_;
+    r.fork_event = ev_rfork_;
+    r.join_event = ev_rjoin_;
+    // Own stream: overlaps the (still running) dedupe of the current batch.  It needs the push decision of
+    // the previous batch (ev_decide_) and nothing else from stream_main_.
+    HCTR_CUDA(cudaStreamWaitEvent(stream_reduce_, ev_decide_, 0));
+    int sp = tic(kPhReduce, stream_reduce_);
+    HCTR_LAUNCH(hctr_grad_reduce_apply_pack(&r, stream_reduce_));
+    toc(sp, stream_reduce_);
+    HCTR_CUDA(cudaEventRecord(ev_reduce_, stream_reduce_));
+    // everything below reads rows / versions the reduction updates
+    HCTR_CUDA(cudaStreamWaitEvent(stream_main_, ev_reduce_, 0));
   }
 
   if (n == 1) {
@@ -791,8 +810,9 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
 // ------------------------------------------------------------------------------------------------
 void HetuTable::setProfile(bool on) { profile_ = on; }
 
-int HetuTable::tic(int phase) {
+int HetuTable::tic(int phase, cudaStream_t st) {
   if (!profile_) return -1;
+  if (!st) st = stream_main_;
   if (spans_used_ == spans_.size()) {
     Span s{phase, nullptr, nullptr};
     HCTR_CUDA(cudaEventCreate(&s.a));
@@ -801,13 +821,13 @@ int HetuTable::tic(int phase) {
   }
   Span &s = spans_[spans_used_];
   s.phase = phase;
-  HCTR_CUDA(cudaEventRecord(s.a, stream_main_));
+  HCTR_CUDA(cudaEventRecord(s.a, st));
   return (int)spans_used_++;
 }
 
-void HetuTable::toc(int span) {
+void HetuTable::toc(int span, cudaStream_t st) {
   if (span < 0) return;
-  HCTR_CUDA(cudaEventRecord(spans_[span].b, stream_main_));
+  HCTR_CUDA(cudaEventRecord(spans_[span].b, st ? st : stream_main_));
 }
 
 // call only after the stream has been synchronised
@@ -928,6 +948,8 @@ HetuTable::~HetuTable() { releaseAll(); }
 void HetuTable::releaseAll() {
   cudaSetDevice(device_id_);
   if (stream_side_) cudaStreamSynchronize(stream_side_);
+  if (stream_reduce_side_) cudaStreamSynchronize(stream_reduce_side_);
+  if (stream_reduce_) cudaStreamSynchronize(stream_reduce_);
   if (stream_main_) cudaStreamSynchronize(stream_main_);
   p2p_.reset();
   transport_.reset();
@@ -952,6 +974,15 @@ void HetuTable::releaseAll() {
   if (ev_fork_) cudaEventDestroy(ev_fork_);
   if (ev_join_) cudaEventDestroy(ev_join_);
   if (ev_keys_) cudaEventDestroy(ev_keys_);
+  if (ev_decide_) cudaEventDestroy(ev_decide_);
+  if (ev_reduce_) cudaEventDestroy(ev_reduce_);
+  if (ev_rfork_) cudaEventDestroy(ev_rfork_);
+  if (ev_rjoin_) cudaEventDestroy(ev_rjoin_);
+  ev_decide_ = ev_reduce_ = ev_rfork_ = ev_rjoin_ = nullptr;
+  if (stream_reduce_side_) cudaStreamDestroy(stream_reduce_side_);
+  stream_reduce_side_ = nullptr;
+  if (stream_reduce_) cudaStreamDestroy(stream_reduce_);
+  stream_reduce_ = nullptr;
   ev_fork_ = ev_join_ = ev_keys_ = nullptr;
   if (stream_side_) cudaStreamDestroy(stream_side_);
   stream_side_ = nullptr;

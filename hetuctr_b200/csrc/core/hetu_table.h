@@ -143,10 +143,16 @@ class HetuTable {
   void finalizeBatch();
   void finalizePending();
   void exchangeP2P(embed_t *dst_dev);
-  const void *stageIn(const void *ptr, size_t bytes, DevBuf &buf);
+  const void *stageIn(const void *ptr, size_t bytes, DevBuf &buf, cudaStream_t s);
 
   cudaStream_t stream_main_ = nullptr;
   cudaStream_t stream_side_ = nullptr;  // overlaps the long-run kernels with their short-run twins
+  // The gradient reduction of the PREVIOUS batch runs here, concurrently with the dedupe of the current
+  // batch on stream_main_ (they touch disjoint data); stream_main_ joins it before the first kernel that
+  // reads updated rows or versions.
+  cudaStream_t stream_reduce_ = nullptr;
+  cudaStream_t stream_reduce_side_ = nullptr;  // long-run reduce kernel, forked from stream_reduce_
+  cudaEvent_t ev_decide_ = nullptr, ev_reduce_ = nullptr, ev_rfork_ = nullptr, ev_rjoin_ = nullptr;
   cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr, ev_keys_ = nullptr;
   std::unique_ptr<Transport> transport_;
   std::unique_ptr<P2PMailbox> p2p_;  // device-driven exchange (one process per GPU, peer access); else NCCL groups
@@ -180,8 +186,8 @@ class HetuTable {
 
   // profiling
   struct Span { int phase; cudaEvent_t a, b; };
-  int tic(int phase);
-  void toc(int span);
+  int tic(int phase, cudaStream_t s = nullptr);
+  void toc(int span, cudaStream_t s = nullptr);
   void collectSpans();
   bool profile_ = false;
   std::vector<Span> spans_;
