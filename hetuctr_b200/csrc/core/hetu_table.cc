@@ -75,14 +75,24 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
   HCTR_CUDA(cudaGetDeviceCount(&num_gpus));
   HCTR_CHECK(device_id >= 0 && device_id < num_gpus, "InCorrect device number.");
   HCTR_CUDA(cudaSetDevice(device_id_));
-  HCTR_CUDA(cudaStreamCreateWithFlags(&stream_main_, cudaStreamNonBlocking));
+  {
+    // stream_main_ carries many short, latency-bound kernels; it gets the highest priority so that their
+    // CTAs are placed ahead of the bulk gradient-reduction CTAs that run concurrently on stream_reduce_
+    int lo = 0, hi = 0;
+    HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_main_, cudaStreamNonBlocking, hi));
+  }
   {
     // the side stream carries the few long-run CTAs that should start ahead of the bulk kernels
     int lo = 0, hi = 0;
     HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
     HCTR_CUDA(cudaStreamCreateWithPriority(&stream_side_, cudaStreamNonBlocking, hi));
   }
-  HCTR_CUDA(cudaStreamCreateWithFlags(&stream_reduce_, cudaStreamNonBlocking));
+  {
+    int lo = 0, hi = 0;
+    HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_reduce_, cudaStreamNonBlocking, lo));
+  }
   {
     int lo = 0, hi = 0;
     HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
@@ -217,8 +227,7 @@ void HetuTable::initTable(const worker_t *root, const index_t *storage) {
   const size_t blocks = (size_t)nrank_ * length_pad_ / HCTR_BLOCK_KEYS;
   d_bits_.ensure(words * sizeof(unsigned long long));
   d_word_base_.ensure(words * sizeof(uint32_t));
-  d_blk_cnt_.ensure((blocks + 1) * sizeof(uint32_t));
-  d_blk_base_.ensure((blocks + 1) * sizeof(uint32_t));
+  d_blk_cnt_.ensure((2 * (blocks / 8 + 2)) * sizeof(uint32_t));  // chain scratch of the block-rank kernel
   HCTR_CUDA(cudaMemsetAsync(d_bits_.p, 0, d_bits_.bytes, stream_main_));
   d_blk_flag_.ensure(blocks + 1);
   HCTR_CUDA(cudaMemsetAsync(d_blk_cnt_.p, 0, d_blk_cnt_.bytes, stream_main_));
@@ -249,6 +258,8 @@ void HetuTable::reserveShared(size_t batch) {
   // receive side of a step can hold up to batch keys from every rank
   const size_t scan_n = std::max(blocks, batch * (size_t)nrank_) + 2;
   d_scan_.ensure(hctr_scan_scratch_words(scan_n) * sizeof(uint32_t));
+  d_chain_.ensure(hctr_scan_chained_scratch_words(batch + 1) * sizeof(uint32_t));
+  HCTR_CUDA(cudaMemsetAsync(d_chain_.p, 0, d_chain_.bytes, stream_main_));
   d_sk_.ensure(batch * sizeof(unsigned long long));
   d_rank_.ensure(batch * sizeof(uint32_t));
   d_cnt_.ensure((batch + 1) * sizeof(uint32_t));  // all-zero between calls, like the bitmap
@@ -303,11 +314,11 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   a.owner_of = d_root_.as<uint8_t>();
   a.row_of = d_row_of_.as<int32_t>();
   a.bits = d_bits_.as<unsigned long long>();
-  a.blk_cnt = d_blk_cnt_.as<uint32_t>();
+  a.chain_scratch = d_blk_cnt_.as<uint32_t>();
+  a.epoch = ++dedupe_epoch_ ? dedupe_epoch_ : ++dedupe_epoch_;
   a.blk_flag = d_blk_flag_.as<uint8_t>();
-  a.blk_base = d_blk_base_.as<uint32_t>();
   a.word_base = d_word_base_.as<uint32_t>();
-  a.scan_scratch = d_scan_.as<uint32_t>();
+  a.scan_scratch = d_chain_.as<uint32_t>();
   a.sk = d_sk_.as<unsigned long long>();
   a.rank_in_run = d_rank_.as<uint32_t>();
   a.heavy_list = cur.heavy.as<uint32_t>();
@@ -396,6 +407,8 @@ void HetuTable::finalizeBatch() {
     prev.push_send[p] = host_counts ? h_cnt_s[2 * p + 1] : 0;
     prev.push_recv[p] = host_counts ? h_cnt_r[2 * p + 1] : 0;
   }
+  if (h_meta[HCTR_META_ERR] & HCTR_ERR_TIMEOUT)
+    throw std::runtime_error("preprocess: a chained scan gave up waiting for an earlier thread block");
   if (h_meta[HCTR_META_ERR] & HCTR_ERR_KEY_RANGE) {
     // leave a consistent (empty) batch behind, then report
     cur.batch_size = 0;
@@ -954,7 +967,7 @@ void HetuTable::releaseAll() {
   p2p_.reset();
   transport_.reset();
   DevBuf *all[] = {&d_embedding_, &d_gradient_, &d_updates_, &d_version_, &d_root_, &d_row_of_, &d_stored_keys_,
-                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_blk_base_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_cnt_,
+                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_chain_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_cnt_,
                    &d_need_push_, &d_push_slot_, &d_push_count_, &d_push_base_, &d_recv_idx_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
                    &d_qkey_r_, &d_qver_r_, &d_pkey_s_, &d_pupd_s_, &d_pval_s_, &d_pkey_r_, &d_pupd_r_, &d_pval_r_,
                    &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,

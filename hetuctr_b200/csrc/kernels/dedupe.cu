@@ -5,16 +5,15 @@
 // (owner,key,position) triples the batch is RANKED through a bitmap over the sort-key space
 //     sk = key + length_pad * owner          (length_pad = length rounded up to 4096)
 //   mark     one bit per distinct sk (atomicOr); the first setter flags its 4096-key block as touched
-//   count    one warp per touched block: popcount of its 64 words = distinct keys in the block
-//            (counting by popcount instead of an atomic per key keeps dense blocks - small
-//            vocabularies are contiguous key ranges - from serialising on one counter)
-//   scan     block counts -> block bases                         (hctr_scan_exclusive_u32)
-//   extract  one warp per non-empty block: popcount prefix inside the block gives every 64-key word
-//            the rank of its first set bit = index in the sorted unique list
+//   ranks    ONE launch: touched blocks are popcounted (distinct keys per block - counting by popcount
+//            instead of an atomic per key keeps dense blocks, i.e. small vocabularies, from serialising
+//            on one counter), block counts are scanned inside each CTA and chained across CTAs, and the
+//            popcount prefix inside each block gives every 64-key word the rank of its first set bit =
+//            index in the sorted unique list
 //   rank     per batch position: unique index = word base + popcount(bits below); an atomic counter
 //            per unique key hands out a slot inside the key's run, and the position that draws slot 0
 //            writes the unique key, its owner and its local row
-//   scan     occurrences -> run starts
+//   scan     occurrences -> run starts (single launch, chained)
 //   scatter  positions into their runs; the slot-0 position also clears the bitmap word and counter
 //   order    each run is put in ascending position order so that gradient sums are taken in batch
 //            order (runs up to 32 by one warp, longer runs through a shared-memory position bitmap)
@@ -59,33 +58,6 @@ __global__ void __launch_bounds__(kThreads) dedupe_mark(hctr_dedupe_args a) {
   if (!(old & bit)) a.blk_flag[sk >> 12] = 1;
 }
 
-// blk_cnt[b] = popcount of block b's 64 words for touched blocks (flag consumed), 0 elsewhere.
-__global__ void __launch_bounds__(kThreads) dedupe_count(hctr_dedupe_args a, size_t n_blocks, unsigned group) {
-  const unsigned lane = threadIdx.x & 31;
-  const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
-  const size_t n_warps = ((size_t)gridDim.x * kThreads) >> 5;
-  for (size_t g = warp * group; g < n_blocks; g += n_warps * group) {
-    const size_t b = g + lane;
-    bool touched = false;
-    if (lane < group && b < n_blocks) {
-      touched = a.blk_flag[b] != 0;
-      if (touched) a.blk_flag[b] = 0;
-      else a.blk_cnt[b] = 0;
-    }
-    unsigned live = __ballot_sync(0xffffffffu, touched);
-    while (live) {
-      const int src = __ffs(live) - 1;
-      live &= live - 1;
-      const size_t blk = g + src;
-      const size_t w0 = blk * HCTR_BLOCK_WORDS + lane;
-      u32 c = __popcll(a.bits[w0]) + __popcll(a.bits[w0 + 32]);
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
-      if (lane == 0) a.blk_cnt[blk] = c;
-    }
-  }
-}
-
 __device__ __forceinline__ u32 warp_excl_scan_total(u32 v, u32 *total) {
   const unsigned lane = threadIdx.x & 31;
   u32 incl = v;
@@ -98,42 +70,64 @@ __device__ __forceinline__ u32 warp_excl_scan_total(u32 v, u32 *total) {
   return incl - v;
 }
 
-// Each warp walks groups of `group` (1..32) consecutive bitmap blocks; lanes fetch the counts/bases of a
-// group at once and the warp then ranks the words of the non-empty blocks.  Small tables use group = 1
-// (one warp per block, maximum parallelism); huge, sparsely hit tables use 32 so that empty blocks
-// cost one coalesced load per 32.
-__global__ void __launch_bounds__(kThreads) dedupe_extract(hctr_dedupe_args a, size_t n_blocks,
-                                                           size_t blocks_per_owner, unsigned group) {
-  const unsigned lane = threadIdx.x & 31;
-  const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
-  const size_t n_warps = ((size_t)gridDim.x * kThreads) >> 5;
-  if (warp == 0 && lane == 0) {
-    const u32 U = a.blk_base[n_blocks];
+// count + scan + extract in one launch.  Every warp owns `group` (1..32) consecutive bitmap blocks, one
+// per lane.  (1) touched blocks are popcounted by the whole warp; (2) counts are scanned inside the CTA
+// and chained across CTAs (chained_cta_prefix), which gives every block the rank of its first key;
+// (3) the warp ranks the 64 words of each touched block.  Small tables use group = 1 (maximum
+// parallelism); huge, sparsely hit tables use 32 so that untouched blocks cost one coalesced flag load
+// per 32 and the number of CTAs in the chain stays small.
+__global__ void __launch_bounds__(kThreads) dedupe_block_ranks(hctr_dedupe_args a, size_t n_blocks,
+                                                               size_t blocks_per_owner, unsigned group, u64 *agg,
+                                                               u32 epoch) {
+  __shared__ u32 warp_tot[kThreads / 32];
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const size_t g = ((size_t)blockIdx.x * (kThreads / 32) + warp) * group;  // first block of this warp
+  const size_t b = g + lane;
+  bool touched = false;
+  if (lane < group && b < n_blocks) {
+    touched = a.blk_flag[b] != 0;
+    if (touched) a.blk_flag[b] = 0;  // consumed: all-zero again for the next batch
+  }
+  const unsigned live = __ballot_sync(0xffffffffu, touched);
+  u32 cnt = 0;
+  for (unsigned todo = live; todo;) {
+    const int src = __ffs(todo) - 1;
+    todo &= todo - 1;
+    const size_t w0 = (g + src) * HCTR_BLOCK_WORDS + lane;
+    u32 c = __popcll(a.bits[w0]) + __popcll(a.bits[w0 + 32]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) c += __shfl_xor_sync(0xffffffffu, c, d);
+    if ((int)lane == src) cnt = c;
+  }
+  u32 wtotal;
+  u32 base = warp_excl_scan_total(cnt, &wtotal);
+  if (lane == 0) warp_tot[warp] = wtotal;
+  __syncthreads();
+  u32 cta_total = 0, before = 0;
+#pragma unroll
+  for (unsigned w = 0; w < kThreads / 32; w++) {
+    if (w < warp) before += warp_tot[w];
+    cta_total += warp_tot[w];
+  }
+  const u32 prefix = chained_cta_prefix(agg, epoch, blockIdx.x, cta_total, &a.meta[HCTR_META_ERR]);
+  base += before + prefix;
+  if (lane < group && b < n_blocks && b % blocks_per_owner == 0) a.meta[HCTR_META_SEG + b / blocks_per_owner] = base;
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+    const u32 U = prefix + cta_total;
     a.meta[HCTR_META_UNIQUE] = U;
     a.meta[HCTR_META_SEG + a.nrank] = U;
   }
-  for (size_t g = warp * group; g < n_blocks; g += n_warps * group) {
-    const size_t b = g + lane;
-    u32 c = 0, base = 0;
-    if (lane < group && b < n_blocks) {
-      c = a.blk_cnt[b];
-      base = a.blk_base[b];
-      if (b % blocks_per_owner == 0) a.meta[HCTR_META_SEG + b / blocks_per_owner] = base;
-    }
-    unsigned live = __ballot_sync(0xffffffffu, c != 0);
-    while (live) {
-      const int src = __ffs(live) - 1;
-      live &= live - 1;
-      const size_t blk = g + src;
-      const u32 blk_base = __shfl_sync(0xffffffffu, base, src);
-      const size_t w0 = blk * HCTR_BLOCK_WORDS + lane, w1 = w0 + 32;
-      const u64 x0 = a.bits[w0], x1 = a.bits[w1];
-      u32 t0, t1;
-      const u32 e0 = warp_excl_scan_total(__popcll(x0), &t0);
-      const u32 e1 = warp_excl_scan_total(__popcll(x1), &t1);
-      a.word_base[w0] = blk_base + e0;
-      a.word_base[w1] = blk_base + t0 + e1;
-    }
+  for (unsigned todo = live; todo;) {
+    const int src = __ffs(todo) - 1;
+    todo &= todo - 1;
+    const u32 blk_base = __shfl_sync(0xffffffffu, base, src);
+    const size_t w0 = (g + src) * HCTR_BLOCK_WORDS + lane, w1 = w0 + 32;
+    const u64 x0 = a.bits[w0], x1 = a.bits[w1];
+    u32 t0, t1;
+    const u32 e0 = warp_excl_scan_total(__popcll(x0), &t0);
+    const u32 e1 = warp_excl_scan_total(__popcll(x1), &t1);
+    a.word_base[w0] = blk_base + e0;
+    a.word_base[w1] = blk_base + t0 + e1;
   }
 }
 
@@ -297,19 +291,16 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
   }
   const unsigned gb = grid_for(a.batch, kThreads);
   dedupe_mark<<<gb, kThreads, 0, s>>>(a);
-  // aim for one resident wave of warps (148 SMs x 64 warps); beyond that let warps take wider groups
-  const size_t target_warps = (size_t)kSMs * 64;
+  // One warp per `group` bitmap blocks; keep the chain of CTAs short (each CTA adds up its predecessors).
   unsigned group = 1;
-  while (group < 32 && (n_blocks + group - 1) / group > target_warps) group *= 2;
-  size_t blk_ctas = (((n_blocks + group - 1) / group) * 32 + kThreads - 1) / kThreads;
-  if (blk_ctas > (size_t)kSMs * 8) blk_ctas = (size_t)kSMs * 8;
-  if (blk_ctas == 0) blk_ctas = 1;
-  dedupe_count<<<(unsigned)blk_ctas, kThreads, 0, s>>>(a, n_blocks, group);
-  int rc = hctr_scan_exclusive_u32(a.blk_cnt, a.blk_base, n_blocks, nullptr, a.scan_scratch, stream);
-  if (rc) return rc;
-  dedupe_extract<<<(unsigned)blk_ctas, kThreads, 0, s>>>(a, n_blocks, blocks_per_owner, group);
+  while (group < 32 && (n_blocks + group - 1) / group > (size_t)kThreads / 32 * 2048) group *= 2;
+  const size_t warps = (n_blocks + group - 1) / group;
+  const size_t blk_ctas = (warps + kThreads / 32 - 1) / (kThreads / 32);
+  dedupe_block_ranks<<<(unsigned)(blk_ctas ? blk_ctas : 1), kThreads, 0, s>>>(
+      a, n_blocks, blocks_per_owner, group, reinterpret_cast<u64 *>(a.chain_scratch), a.epoch);
   dedupe_rank<<<gb, kThreads, 0, s>>>(a);
-  rc = hctr_scan_exclusive_u32(a.cnt, a.run_start, a.batch, a.meta + HCTR_META_UNIQUE, a.scan_scratch, stream);
+  int rc = hctr_scan_exclusive_u32_chained(a.cnt, a.run_start, a.batch, a.meta + HCTR_META_UNIQUE, a.scan_scratch,
+                                           a.epoch, a.meta + HCTR_META_ERR, stream);
   if (rc) return rc;
   dedupe_scatter<<<gb, kThreads, 0, s>>>(a);
   // short and long runs are disjoint slices of sorted_pos: with a second stream the two ordering
@@ -343,6 +334,6 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
     if (e == cudaSuccess) e = cudaStreamWaitEvent(s, (cudaEvent_t)a.join_event, 0);
     if (e != cudaSuccess) return (int)e;
   }
-  count_launches(7);
+  count_launches(6);
   return launch_status();
 }

@@ -106,6 +106,29 @@ __global__ void __launch_bounds__(kScanThreads) scan_single_cta(const u32 *__res
   }
 }
 
+// Single-launch scan for any size: tile-local scan + chained prefix over the preceding tiles.
+__global__ void __launch_bounds__(kScanThreads) scan_chained(const u32 *__restrict__ in, u32 *__restrict__ out,
+                                                             size_t n_max, const u32 *__restrict__ n_dev,
+                                                             u64 *agg, u32 epoch, u32 *err) {
+  const size_t n = n_dev ? min((size_t)*n_dev, n_max) : n_max;
+  const size_t base = (size_t)blockIdx.x * HCTR_SCAN_TILE + (size_t)threadIdx.x * kScanItems;
+  u32 v[kScanItems];
+  u32 s = 0;
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++) {
+    v[k] = (base + k < n) ? in[base + k] : 0;
+    s += v[k];
+  }
+  __shared__ u32 total;
+  u32 ex = block_excl_scan(s, &total);
+  ex += chained_cta_prefix(agg, epoch, blockIdx.x, total, err);
+#pragma unroll
+  for (int k = 0; k < kScanItems; k++) {
+    if (base + k <= n) out[base + k] = ex;  // entry n receives the grand total
+    ex += v[k];
+  }
+}
+
 }  // namespace hctr
 
 using namespace hctr;
@@ -190,5 +213,17 @@ extern "C" int hctr_scan_exclusive_u32_noalloc(const uint32_t *in, uint32_t *out
   scan_tile_sums<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, n, nullptr, scratch);
   scan_apply<<<(unsigned)tiles, kScanThreads, 0, s>>>(in, out, n, nullptr, scratch);
   count_launches(2);
+  return launch_status();
+}
+
+extern "C" size_t hctr_scan_chained_scratch_words(size_t n_max) { return 2 * ((n_max + 1) / HCTR_SCAN_TILE + 2); }
+
+extern "C" int hctr_scan_exclusive_u32_chained(const uint32_t *in, uint32_t *out, size_t n_max, const uint32_t *n_dev,
+                                               uint32_t *scratch, uint32_t epoch, uint32_t *err, void *stream) {
+  if (epoch == 0) return (int)cudaErrorInvalidValue;
+  const size_t tiles = (n_max + 1 + HCTR_SCAN_TILE - 1) / HCTR_SCAN_TILE;
+  scan_chained<<<(unsigned)tiles, kScanThreads, 0, (cudaStream_t)stream>>>(
+      in, out, n_max, n_dev, reinterpret_cast<u64 *>(scratch), epoch, err);
+  count_launches(1);
   return launch_status();
 }

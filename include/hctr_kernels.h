@@ -57,6 +57,14 @@ size_t hctr_scan_scratch_words(size_t n_max);
 int hctr_scan_exclusive_u32(const uint32_t *in, uint32_t *out, size_t n_max, const uint32_t *n_dev,
                             uint32_t *scratch, void *stream);
 
+/* Same result in ONE launch: tile-local scans chained through per-tile totals that later tiles pick up
+ * with bounded acquire-polls (HCTR_ERR_TIMEOUT in *err if a tile never publishes).  `scratch` holds
+ * hctr_scan_chained_scratch_words(n_max) words, 8-byte aligned, and needs no initialisation provided
+ * `epoch` is non-zero and differs from the epoch of the previous launch that used the same scratch. */
+size_t hctr_scan_chained_scratch_words(size_t n_max);
+int hctr_scan_exclusive_u32_chained(const uint32_t *in, uint32_t *out, size_t n_max, const uint32_t *n_dev,
+                                    uint32_t *scratch, uint32_t epoch, uint32_t *err, void *stream);
+
 /* Exclusive prefix sum for callers that cannot allocate device memory.  (No counterpart in the
  * reference: it sizes and allocates cub temp storage itself, csrc/core/table_initialize.cu:166-177.)
  *
@@ -127,10 +135,10 @@ typedef struct hctr_dedupe_args {
   uint8_t *blk_flag;        /* [nrank*length_pad/4096] block touched by this batch */
   uint32_t *cnt;            /* [B+1] occurrences per unique key (consumed by the run-start scan) */
   /* scratch that needs no initial value */
-  uint32_t *blk_cnt;        /* [nblocks + 1] distinct keys per bitmap block */
-  uint32_t *blk_base;       /* [nblocks + 1] */
+  uint32_t *chain_scratch;  /* [2 * (nblocks / 8 + 2)] words, 8-byte aligned: CTA totals of the block-rank kernel */
+  uint32_t epoch;           /* non-zero, different from the previous call's (tags chain_scratch/scan_scratch) */
   uint32_t *word_base;      /* [nrank*length_pad/64] */
-  uint32_t *scan_scratch;   /* hctr_scan_scratch_words(max(nblocks, B) + 1) */
+  uint32_t *scan_scratch;   /* hctr_scan_chained_scratch_words(B + 1) words, 8-byte aligned */
   unsigned long long *sk;   /* [B] sort keys */
   uint32_t *rank_in_run;    /* [B] */
   /* outputs */
