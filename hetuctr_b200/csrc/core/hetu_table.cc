@@ -331,9 +331,15 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   a.sorted_pos = cur.sorted_pos.as<uint32_t>();
   a.idx_map = cur.idx_map.as<int32_t>();
   a.meta = cur.meta.as<uint32_t>();
+  // run ordering happens on stream_side_, off this stream's critical path; the reduction of this batch
+  // (next step) waits on the batch's own event.  stream_side_ also stages through d_rank_, which the rank
+  // kernel below overwrites: make sure the previous batch's ordering is over first.
+  if (prev.order_recorded) HCTR_CUDA(cudaStreamWaitEvent(stream_main_, prev.ev_order, 0));
+  if (!cur.ev_order) HCTR_CUDA(cudaEventCreateWithFlags(&cur.ev_order, cudaEventDisableTiming));
   a.side_stream = stream_side_;
   a.fork_event = ev_fork_;
-  a.join_event = ev_join_;
+  a.join_event = cur.ev_order;
+  cur.order_recorded = true;
   // The push decision for the previous batch goes first: the gradient reduction (on its own stream, started
   // by the next push_pull) only needs this, not the dedupe of the new batch that follows.
 
@@ -524,6 +530,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     // Own stream: overlaps the (still running) dedupe of the current batch.  It needs the push decision of
     // the previous batch (ev_decide_) and nothing else from stream_main_.
     HCTR_CUDA(cudaStreamWaitEvent(stream_reduce_, ev_decide_, 0));
+    if (prev.order_recorded) HCTR_CUDA(cudaStreamWaitEvent(stream_reduce_, prev.ev_order, 0));
     int sp = tic(kPhReduce, stream_reduce_);
     HCTR_LAUNCH(hctr_grad_reduce_apply_pack(&r, stream_reduce_));
     toc(sp, stream_reduce_);
@@ -891,6 +898,7 @@ long long copy_sizes(const std::vector<size_t> &v, size_t n, void *out) {
 long long HetuTable::dump(const std::string &what, bool prev, void *out) {
   HCTR_CUDA(cudaSetDevice(device_id_));
   finalizePending();
+  HCTR_CUDA(cudaStreamSynchronize(stream_side_));  // run ordering may still be in flight
   BatchDesc &b = prev ? prev_batch_ : cur_batch_;
   const size_t B = b.batch_size, U = b.unique_size;
   cudaStream_t s = stream_main_;
@@ -973,6 +981,10 @@ void HetuTable::releaseAll() {
                    &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,
                    &d_retcnt_r_, &d_rver_s_, &d_rval_s_, &d_rver_r_, &d_rval_r_, &d_stage_grad_, &d_stage_dst_};
   for (DevBuf *b : all) b->release();
+  for (BatchDesc *b : {&cur_batch_, &prev_batch_}) {
+    if (b->ev_order) cudaEventDestroy(b->ev_order);
+    b->ev_order = nullptr;
+  }
   for (BatchDesc *b : {&cur_batch_, &prev_batch_})
     for (DevBuf *d : {&b->keys, &b->idx_map, &b->sorted_pos, &b->uniq, &b->uniq_owner, &b->uniq_row,
                       &b->run_start, &b->meta, &b->pos_row, &b->heavy})

@@ -57,6 +57,8 @@ struct BatchDesc {
   size_t capacity = 0;
   size_t n_heavy = 0;  // runs longer than HCTR_LIGHT_RUN
   bool pending = false;  // sizes not yet read back from the device (single-rank tables defer this)
+  cudaEvent_t ev_order = nullptr;  // completion of this batch's run ordering (on the ordering stream)
+  bool order_recorded = false;
   DevBuf keys, idx_map, sorted_pos, uniq, uniq_owner, uniq_row, run_start, meta, pos_row, heavy;
   std::vector<size_t> seg;         // [n+1] first unique of each owner
   std::vector<size_t> query_send;  // [n] unique keys addressed to each owner

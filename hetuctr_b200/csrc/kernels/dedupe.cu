@@ -303,20 +303,21 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
                                            a.epoch, a.meta + HCTR_META_ERR, stream);
   if (rc) return rc;
   dedupe_scatter<<<gb, kThreads, 0, s>>>(a);
-  // short and long runs are disjoint slices of sorted_pos: with a second stream the two ordering
-  // kernels overlap
-  cudaStream_t hs = s;
+  // Run ordering is only needed by the gradient reduction of the NEXT step, not by anything else in this
+  // one.  With a second stream the two ordering kernels leave the caller's stream: they start after the
+  // scatter (fork_event) and join_event marks their completion; whoever consumes sorted_pos waits on it.
+  cudaStream_t os = s;
   if (a.side_stream && a.fork_event && a.join_event) {
-    hs = (cudaStream_t)a.side_stream;
+    os = (cudaStream_t)a.side_stream;
     cudaError_t e = cudaEventRecord((cudaEvent_t)a.fork_event, s);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(hs, (cudaEvent_t)a.fork_event, 0);
+    if (e == cudaSuccess) e = cudaStreamWaitEvent(os, (cudaEvent_t)a.fork_event, 0);
     if (e != cudaSuccess) return (int)e;
   }
   {
     size_t ctas = ((a.batch + 31) / 32 * 32 + kThreads - 1) / kThreads;  // one warp per 32 unique keys
     if (ctas > (size_t)kSMs * 8) ctas = (size_t)kSMs * 8;
     if (ctas == 0) ctas = 1;
-    dedupe_order_light<<<(unsigned)ctas, kThreads, 0, s>>>(a);
+    dedupe_order_light<<<(unsigned)ctas, kThreads, 0, os>>>(a);
   }
   {
     // window = the batch when it fits (small windows let several CTAs share an SM)
@@ -327,11 +328,10 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
     size_t per_sm = (200 * 1024) / (smem + 1024);
     if (per_sm > 2) per_sm = 2;  // 1024-thread CTAs: at most 2 per SM
     if (per_sm < 1) per_sm = 1;
-    dedupe_order_heavy<<<(unsigned)(kSMs * per_sm), 1024, smem, hs>>>(a, (u32)wbits);
+    dedupe_order_heavy<<<(unsigned)(kSMs * per_sm), 1024, smem, os>>>(a, (u32)wbits);
   }
-  if (hs != s) {
-    cudaError_t e = cudaEventRecord((cudaEvent_t)a.join_event, hs);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(s, (cudaEvent_t)a.join_event, 0);
+  if (os != s) {
+    cudaError_t e = cudaEventRecord((cudaEvent_t)a.join_event, os);
     if (e != cudaSuccess) return (int)e;
   }
   count_launches(6);

@@ -247,7 +247,8 @@ extern "C" int hctr_expand_rows(size_t batch, size_t width, const int32_t *pos_r
 #define CALL(L, V)                                                                       \
   do {                                                                                   \
     size_t g_ = (((size_t)batch + kExpandRows - 1) / kExpandRows * L + kThreads - 1) / kThreads; \
-    const size_t cap_ = (size_t)kSMs * 8; /* persistent: one resident wave of CTAs */    \
+    /* persistent, exactly one resident wave: the kernel needs ~80 registers, i.e. 3 CTAs per SM */ \
+    const size_t cap_ = (size_t)kSMs * 3;                                                \
     if (g_ > cap_) g_ = cap_;                                                            \
     expand_rows<L, V><<<(unsigned)g_, kThreads, 0, s>>>(batch, width, pos_row, idx_map,  \
                                                         recv_slot, recv_val, embedding, dst); \

@@ -151,8 +151,11 @@ typedef struct hctr_dedupe_args {
   int32_t *pos_row;         /* [B] batch position -> local row or HCTR_INVALID_ROW */
   uint32_t *heavy_list;     /* [B/32 + 2] unique indices whose run is longer than HCTR_LIGHT_RUN */
   uint32_t *meta;           /* [HCTR_META_WORDS + nrank + 1]: see HCTR_META_* */
-  /* optional: a second stream (cudaStream_t) and two events (cudaEvent_t) that let the two run-ordering
-   * kernels overlap; null = everything on the call's stream */
+  /* optional: a second stream (cudaStream_t) and two events (cudaEvent_t).  When given, the two
+   * run-ordering kernels (the only consumers/producers of the final order inside sorted_pos) run on
+   * side_stream after the rest of the pipeline, and join_event is recorded there when they are done:
+   * the call's stream does NOT wait for them, whoever reads sorted_pos must wait on join_event.
+   * null = everything on the call's stream */
   void *side_stream;
   void *fork_event;
   void *join_event;
@@ -285,7 +288,7 @@ typedef struct hctr_reduce_args {
   int64_t *push_key;          /* [P] packed ids of pushed rows */
   int64_t *push_updates;      /* [P] update counts */
   float *push_val;            /* [P, W] */
-  uint32_t *work_counter;     /* two device words of scratch (needed when n_heavy > 0) */
+  uint32_t *work_counter;     /* three device words of scratch (work queues of the kernels) */
   /* optional peer-to-peer routing of pushed rows: when p2p is non-null, a pushed row of a key owned by
    * rank p goes to slot (push_slot[u] - push_base[p]) of this rank's sub-region in p's mailbox instead
    * of push_key / push_updates / push_val */
