@@ -167,10 +167,11 @@ class HetuTable {
   size_t length_pad_ = 0;
 
   // dedupe scratch (persistent, all-zero between calls) and per-step scratch
-  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_word_base_, d_scan_, d_sk_, d_rank_, d_cnt_;
+  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_word_base_, d_scan_, d_sk_, d_rank_, d_cnt_;
   DevBuf d_need_push_, d_push_slot_, d_push_count_, d_push_base_, d_recv_idx_, d_err_;
   size_t shared_capacity_ = 0;
   uint32_t dedupe_epoch_ = 0;
+  uint32_t nextEpoch() { return ++dedupe_epoch_ ? dedupe_epoch_ : ++dedupe_epoch_; }  // never 0
 
   // exchange buffers: *_s = send side, *_r = receive side
   DevBuf d_cnt_s_, d_cnt_r_;                      // packed per-peer counts

@@ -67,8 +67,7 @@ __global__ void p2p_signal(hctr_p2p_ctx c, int phase, u32 seq, const u32 *__rest
 
 // One thread per source.  Polls this rank's own memory; gives up after timeout_ns.
 __global__ void p2p_wait(hctr_p2p_ctx c, int phase, u32 seq) {
-  const int s = threadIdx.x;
-  if (s >= c.nrank) return;
+  const int s = threadIdx.x;  // launched with exactly nrank threads
   const u32 *hdr = c.box[c.rank].hdr + (size_t)s * kHdrWords;
   const u32 *flag = hdr + (phase == 0 ? 0 : 8);
   const u64 t0 = now_ns();
@@ -91,6 +90,18 @@ __global__ void p2p_wait(hctr_p2p_ctx c, int phase, u32 seq) {
     }
     c.cnt_in[s] = q;
     c.cnt_in[c.nrank + s] = g;
+    // exclusive prefix of the query counts: flat index space [0, Q) over all received queries
+    __shared__ u32 s_q[1024];
+    s_q[s] = q;
+    __syncthreads();
+    if (s == 0) {
+      u32 acc = 0;
+      for (int i = 0; i < c.nrank; i++) {
+        c.cnt_in[3 * c.nrank + i] = acc;
+        acc += s_q[i];
+      }
+      c.cnt_in[4 * c.nrank] = acc;
+    }
   } else {
     u32 r = ok ? hdr[9] : 0u;
     if (r > c.cap) {
@@ -101,71 +112,93 @@ __global__ void p2p_wait(hctr_p2p_ctx c, int phase, u32 seq) {
   }
 }
 
+// Flat index q in [0, Q) over all received queries -> (source s, index j inside s's sub-region).
+__device__ __forceinline__ unsigned source_of(const u32 *qstart, int nrank, u32 q) {
+  int lo = 0, hi = nrank;  // qstart[lo] <= q < qstart[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (qstart[mid] <= q) lo = mid;
+    else hi = mid;
+  }
+  return (unsigned)lo;
+}
+
 __global__ void __launch_bounds__(kThreads) p2p_stale_check(hctr_p2p_ctx c, const int32_t *__restrict__ row_of,
                                                             size_t length, size_t n_cached,
                                                             const long long *__restrict__ version,
                                                             long long pull_bound, u32 *__restrict__ flags32) {
-  const size_t total = (size_t)c.nrank * c.cap;
+  __shared__ u32 qstart[1025];
+  for (int i = threadIdx.x; i <= c.nrank; i += kThreads) qstart[i] = c.cnt_in[3 * c.nrank + i];
+  __syncthreads();
+  const u32 Q = qstart[c.nrank];
   const hctr_p2p_box me = c.box[c.rank];
-  for (size_t q = (size_t)blockIdx.x * kThreads + threadIdx.x; q < total; q += (size_t)gridDim.x * kThreads) {
-    const unsigned s = (unsigned)(q / c.cap);
-    const u32 j = (u32)(q % c.cap);
+  for (size_t q = (size_t)blockIdx.x * kThreads + threadIdx.x; q < Q; q += (size_t)gridDim.x * kThreads) {
+    const unsigned s = source_of(qstart, c.nrank, (u32)q);
+    const u32 j = (u32)q - qstart[s];
+    const size_t slot = (size_t)s * c.cap + j;
+    const long long k = me.qkey[slot];
+    int32_t row = -1;
+    if (k >= 0 && (size_t)k < length) row = row_of[k];
     u32 f = 0;
-    if (j < c.cnt_in[s]) {
-      const long long k = me.qkey[q];
-      int32_t row = -1;
-      if (k >= 0 && (size_t)k < length) row = row_of[k];
-      if (row < 0 || (size_t)row < n_cached) {
-        atomicOr(c.err, HCTR_ERR_NOT_OWNER);
-      } else {
-        const long long lv = me.qver[q], gv = version[row];
-        const bool stale = lv == kInvalidVersion || (long long)((u64)lv + (u64)pull_bound) < gv;
-        f = (stale && s != (unsigned)c.rank) ? 1u : 0u;
-      }
-      c.box[s].flag[(size_t)c.rank * c.cap + j] = (uint8_t)f;
+    if (row < 0 || (size_t)row < n_cached) {
+      atomicOr(c.err, HCTR_ERR_NOT_OWNER);
+    } else {
+      const long long lv = me.qver[slot], gv = version[row];
+      const bool stale = lv == kInvalidVersion || (long long)((u64)lv + (u64)pull_bound) < gv;
+      f = (stale && s != (unsigned)c.rank) ? 1u : 0u;
     }
+    c.box[s].flag[(size_t)c.rank * c.cap + j] = (uint8_t)f;
     flags32[q] = f;
   }
 }
 
 __global__ void p2p_return_counts(hctr_p2p_ctx c, const u32 *__restrict__ ret_slot, u32 *__restrict__ ret_count) {
   const int s = threadIdx.x;
-  if (s < c.nrank) ret_count[s] = ret_slot[(size_t)(s + 1) * c.cap] - ret_slot[(size_t)s * c.cap];
+  if (s < c.nrank) {
+    const u32 *qstart = c.cnt_in + 3 * c.nrank;
+    ret_count[s] = ret_slot[qstart[s + 1]] - ret_slot[qstart[s]];
+  }
 }
 
-// A warp scans 32 consecutive slots, then copies the flagged rows one after the other with all lanes.
-template <bool VEC>
-__global__ void __launch_bounds__(kThreads) p2p_gather(hctr_p2p_ctx c, const u32 *__restrict__ flags32,
+// ret_q[r] = flat query index of the r-th returned row (inverse of the scan), so that the gather can
+// give every returned row its own group of lanes.
+__global__ void __launch_bounds__(kThreads) p2p_return_list(hctr_p2p_ctx c, const u32 *__restrict__ flags32,
+                                                            const u32 *__restrict__ ret_slot, u32 *__restrict__ ret_q) {
+  const u32 Q = c.cnt_in[4 * c.nrank];
+  for (size_t q = (size_t)blockIdx.x * kThreads + threadIdx.x; q < Q; q += (size_t)gridDim.x * kThreads)
+    if (flags32[q]) ret_q[ret_slot[q]] = (u32)q;
+}
+
+// One group of LANES lanes per returned row, rows written straight into the requester's mailbox.
+template <int LANES, bool VEC>
+__global__ void __launch_bounds__(kThreads) p2p_gather(hctr_p2p_ctx c, const u32 *__restrict__ ret_q,
                                                        const u32 *__restrict__ ret_slot,
                                                        const int32_t *__restrict__ row_of,
                                                        const float *__restrict__ embedding,
                                                        const long long *__restrict__ version) {
   typedef RowT<VEC> R;
   typedef typename R::T T;
-  const unsigned lane = threadIdx.x & 31;
-  const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
-  const size_t n_warps = ((size_t)gridDim.x * kThreads) >> 5;
-  const size_t total = (size_t)c.nrank * c.cap;
+  __shared__ u32 qstart[1025];
+  for (int i = threadIdx.x; i <= c.nrank; i += kThreads) qstart[i] = c.cnt_in[3 * c.nrank + i];
+  __syncthreads();
+  const u32 Q = qstart[c.nrank];
+  const u32 n_ret = ret_slot[Q];
+  const unsigned gl = threadIdx.x % LANES;
+  const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
   const size_t E = R::elems(c.width);
   const hctr_p2p_box me = c.box[c.rank];
-  for (size_t q0 = warp * 32; q0 < total; q0 += n_warps * 32) {
-    const size_t q = q0 + lane;
-    const bool f = q < total && flags32[q] != 0;
-    unsigned live = __ballot_sync(0xffffffffu, f);
-    while (live) {
-      const int src = __ffs(live) - 1;
-      live &= live - 1;
-      const size_t qq = q0 + src;
-      const unsigned s = (unsigned)(qq / c.cap);
-      const u32 slot = ret_slot[qq] - ret_slot[(size_t)s * c.cap];
-      const int32_t row = row_of[me.qkey[qq]];
-      const hctr_p2p_box b = c.box[s];
-      const size_t dst = (size_t)c.rank * c.cap + slot;
-      if (lane == 0) b.rver[dst] = version[row];
-      const T *from = reinterpret_cast<const T *>(embedding) + (size_t)row * E;
-      T *to = reinterpret_cast<T *>(b.rval) + dst * E;
-      for (size_t e = lane; e < E; e += 32) to[e] = from[e];
-    }
+  for (size_t r = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; r < n_ret; r += groups) {
+    const u32 qq = ret_q[r];
+    const unsigned s = source_of(qstart, c.nrank, qq);
+    const u32 j = qq - qstart[s];
+    const u32 slot = (u32)r - ret_slot[qstart[s]];
+    const int32_t row = row_of[me.qkey[(size_t)s * c.cap + j]];
+    const hctr_p2p_box b = c.box[s];
+    const size_t dst = (size_t)c.rank * c.cap + slot;
+    if (gl == 0) b.rver[dst] = version[row];
+    const T *from = reinterpret_cast<const T *>(embedding) + (size_t)row * E;
+    T *to = reinterpret_cast<T *>(b.rval) + dst * E;
+    for (size_t e = gl; e < E; e += LANES) to[e] = from[e];
   }
 }
 
@@ -233,7 +266,7 @@ extern "C" int hctr_p2p_signal(const hctr_p2p_ctx *c, int phase, uint32_t seq, c
 
 extern "C" int hctr_p2p_wait(const hctr_p2p_ctx *c, int phase, uint32_t seq, void *stream) {
   if (c->nrank > 1024) return (int)cudaErrorInvalidValue;
-  p2p_wait<<<1, 1024, 0, (cudaStream_t)stream>>>(*c, phase, seq);
+  p2p_wait<<<1, c->nrank, 0, (cudaStream_t)stream>>>(*c, phase, seq);
   count_launches(1);
   return launch_status();
 }
@@ -255,16 +288,19 @@ extern "C" int hctr_p2p_return_counts(const hctr_p2p_ctx *c, const uint32_t *ret
 }
 
 extern "C" int hctr_p2p_gather(const hctr_p2p_ctx *c, const uint32_t *flags32, const uint32_t *ret_slot,
-                               const int32_t *row_of, const float *embedding, const int64_t *version, void *stream) {
-  const unsigned g = persistent_grid((size_t)c->nrank * c->cap);
-  const bool vec = c->width % 4 == 0 && host_aligned16(embedding);
-  if (vec)
-    p2p_gather<true><<<g, kThreads, 0, (cudaStream_t)stream>>>(*c, flags32, ret_slot, row_of, embedding,
-                                                               (const long long *)version);
-  else
-    p2p_gather<false><<<g, kThreads, 0, (cudaStream_t)stream>>>(*c, flags32, ret_slot, row_of, embedding,
-                                                                (const long long *)version);
-  count_launches(1);
+                               uint32_t *ret_q, const int32_t *row_of, const float *embedding, const int64_t *version,
+                               void *stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t slots = (size_t)c->nrank * c->cap;
+  p2p_return_list<<<persistent_grid(slots), kThreads, 0, st>>>(*c, flags32, ret_slot, ret_q);
+  const bool al = host_aligned16(embedding);
+  const size_t width = c->width;
+#define CALL(L, V)                                                                                         \
+  p2p_gather<L, V><<<(unsigned)((size_t)kSMs * 8), kThreads, 0, st>>>(*c, ret_q, ret_slot, row_of, embedding, \
+                                                                      (const long long *)version)
+  HCTR_DISPATCH_ROWS(width, al, CALL);
+#undef CALL
+  count_launches(2);
   return launch_status();
 }
 

@@ -1,5 +1,7 @@
 // Gradient side of a step: push decision, duplicate-gradient reduction fused with the local SGD
 // apply and the packing of pushed rows, and the owner-side apply of received rows.
+#include <cooperative_groups.h>
+
 #include <cstring>
 
 #include "rowops.cuh"
@@ -23,6 +25,71 @@ __global__ void __launch_bounds__(kThreads) push_decide(const u32 *__restrict__ 
   else if (row < 0) need = 1;
   else need = (pending_cnt[row] + (long long)(run_start[u + 1] - run_start[u]) <= push_bound) ? 0u : 1u;
   need_push[u] = need;
+}
+
+// Decision + slot assignment in one launch: every CTA decides a tile of 4096 unique keys, scans the flags
+// locally and chains the tile totals (chained_cta_prefix), so need_push[] and push_slot[] (U+1 entries)
+// come out of a single kernel.
+constexpr int kDecideThreads = 1024;
+constexpr int kDecideItems = 4;
+
+__global__ void __launch_bounds__(kDecideThreads) push_decide_scan(const u32 *__restrict__ meta, int rank,
+                                                                   const uint8_t *__restrict__ uniq_owner,
+                                                                   const int32_t *__restrict__ uniq_row,
+                                                                   const u32 *__restrict__ run_start,
+                                                                   const long long *__restrict__ pending_cnt,
+                                                                   long long push_bound, u32 *__restrict__ need_push,
+                                                                   u32 *__restrict__ push_slot, u64 *agg, u32 epoch,
+                                                                   u32 *err) {
+  __shared__ u32 warp_sums[32];
+  const size_t U = meta[HCTR_META_UNIQUE];
+  const size_t base = ((size_t)blockIdx.x * kDecideThreads + threadIdx.x) * kDecideItems;
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  u32 v[kDecideItems];
+  u32 s = 0;
+#pragma unroll
+  for (int k = 0; k < kDecideItems; k++) {
+    const size_t u = base + k;
+    u32 need = 0;
+    if (u < U) {
+      const int32_t row = uniq_row[u];
+      if (uniq_owner[u] == rank) need = 0;
+      else if (row < 0) need = 1;
+      else need = (pending_cnt[row] + (long long)(run_start[u + 1] - run_start[u]) <= push_bound) ? 0u : 1u;
+      need_push[u] = need;
+    }
+    v[k] = need;
+    s += need;
+  }
+  // block-wide exclusive scan of s
+  u32 incl = s;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    u32 t = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= (unsigned)d) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    u32 w = warp_sums[lane], wi = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      u32 t = __shfl_up_sync(0xffffffffu, wi, d);
+      if (lane >= (unsigned)d) wi += t;
+    }
+    warp_sums[lane] = wi - w;
+  }
+  __syncthreads();
+  u32 ex = incl - s + warp_sums[warp];
+  __shared__ u32 cta_total;
+  if (threadIdx.x == kDecideThreads - 1) cta_total = ex + s;
+  __syncthreads();
+  ex += chained_cta_prefix(agg, epoch, blockIdx.x, cta_total, err);
+#pragma unroll
+  for (int k = 0; k < kDecideItems; k++) {
+    if (base + k <= U) push_slot[base + k] = ex;  // entry U receives the total
+    ex += v[k];
+  }
 }
 
 __global__ void push_counts(const u32 *__restrict__ meta, int nrank, const u32 *__restrict__ push_slot,
@@ -446,9 +513,65 @@ __global__ void __launch_bounds__(kThreads) owner_update(size_t n_rows_max, cons
   }
 }
 
+// All sources in ONE launch (peer-to-peer exchange): the pushed rows of source s sit in sub-region s of this
+// rank's mailbox.  Sources are applied one after the other with a grid-wide barrier in between, which keeps
+// the reference's deterministic per-row apply order (two sources may push the same row) without one launch
+// per source.  Launched cooperatively, so all CTAs are co-resident and the barrier cannot deadlock.
+template <int LANES, bool VEC>
+__global__ void __launch_bounds__(kThreads) owner_update_all(hctr_p2p_ctx c, const int32_t *__restrict__ row_of,
+                                                             size_t length, size_t n_cached,
+                                                             float *__restrict__ embedding,
+                                                             long long *__restrict__ version) {
+  typedef RowT<VEC> R;
+  typedef typename R::T T;
+  cooperative_groups::grid_group grid = cooperative_groups::this_grid();
+  const hctr_p2p_box me = c.box[c.rank];
+  const unsigned gl = threadIdx.x % LANES;
+  const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
+  const size_t E = R::elems(c.width);
+  for (int s = 0; s < c.nrank; s++) {
+    if (s == c.rank) continue;  // a rank never pushes to itself
+    const size_t n_rows = min((size_t)c.cnt_in[c.nrank + s], (size_t)c.cap);
+    if (n_rows == 0) continue;  // uniform across the grid
+    const long long *key = reinterpret_cast<const long long *>(me.pkey) + (size_t)s * c.cap;
+    const long long *updates = reinterpret_cast<const long long *>(me.pupd) + (size_t)s * c.cap;
+    const T *val = reinterpret_cast<const T *>(me.pval + (size_t)s * c.cap * c.width);
+    for (size_t m = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; m < n_rows; m += groups) {
+      const long long k = key[m];
+      int32_t row = -1;
+      if (k >= 0 && (size_t)k < length) row = row_of[k];
+      if (row < 0 || (size_t)row < n_cached) {
+        if (gl == 0) atomicOr(c.err, HCTR_ERR_NOT_OWNER);
+        continue;
+      }
+      if (gl == 0) version[row] = (long long)((u64)version[row] + (u64)updates[m]);
+      T *emb = reinterpret_cast<T *>(embedding) + (size_t)row * E;
+      const T *v = val + m * E;
+      for (size_t e = gl; e < E; e += LANES) emb[e] = R::add(emb[e], R::ld_once(v + e));
+    }
+    grid.sync();
+  }
+}
+
 }  // namespace hctr
 
 using namespace hctr;
+
+extern "C" int hctr_p2p_owner_update(const hctr_p2p_ctx *cp, const int32_t *row_of, size_t length, size_t n_cached,
+                                     float *embedding, int64_t *version, void *stream) {
+  hctr_p2p_ctx c = *cp;
+  long long *ver = (long long *)version;
+  void *args[] = {&c, &row_of, &length, &n_cached, &embedding, &ver};
+  const bool al = host_aligned16(embedding);
+  cudaError_t e = cudaSuccess;
+#define CALL(L, V)                                                                                              \
+  e = cudaLaunchCooperativeKernel((const void *)owner_update_all<L, V>, dim3(kSMs * 2), dim3(kThreads), args, 0, \
+                                  (cudaStream_t)stream)
+  HCTR_DISPATCH_ROWS(c.width, al, CALL);
+#undef CALL
+  count_launches(1);
+  return (int)e;
+}
 
 extern "C" int hctr_push_decide(const uint32_t *meta, int nrank, int rank, size_t u_max,
                                 const uint8_t *uniq_owner, const int32_t *uniq_row, const uint32_t *run_start,
@@ -462,6 +585,24 @@ extern "C" int hctr_push_decide(const uint32_t *meta, int nrank, int rank, size_
                                                               need_push);
   int rc = hctr_scan_exclusive_u32(need_push, push_slot, u_max, meta + HCTR_META_UNIQUE, scan_scratch, stream);
   if (rc) return rc;
+  push_counts<<<1, 1024, 0, s>>>(meta, nrank, push_slot, push_count, push_base);
+  count_launches(2);
+  return launch_status();
+}
+
+extern "C" int hctr_push_decide_fused(const uint32_t *meta, int nrank, int rank, size_t u_max,
+                                      const uint8_t *uniq_owner, const int32_t *uniq_row, const uint32_t *run_start,
+                                      const int64_t *pending_cnt, int64_t push_bound, uint32_t *need_push,
+                                      uint32_t *push_slot, uint32_t *chain_scratch, uint32_t epoch,
+                                      uint32_t *push_count, uint32_t *push_base, uint32_t *err, void *stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (nrank > 1024 || epoch == 0) return (int)cudaErrorInvalidValue;
+  const size_t per = (size_t)kDecideThreads * kDecideItems;
+  const size_t tiles = (u_max + 1 + per - 1) / per;
+  push_decide_scan<<<(unsigned)tiles, kDecideThreads, 0, s>>>(meta, rank, uniq_owner, uniq_row, run_start,
+                                                             (const long long *)pending_cnt, push_bound, need_push,
+                                                             push_slot, reinterpret_cast<u64 *>(chain_scratch), epoch,
+                                                             err);
   push_counts<<<1, 1024, 0, s>>>(meta, nrank, push_slot, push_count, push_base);
   count_launches(2);
   return launch_status();

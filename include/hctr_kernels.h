@@ -197,6 +197,14 @@ int hctr_pack_counts(const uint32_t *meta, const uint32_t *push_count, int nrank
  * Replaces gradient_index_kernel and gradient_reduction_kernel, csrc/core/generate_query.cu:8-89.
  * ------------------------------------------------------------------------------------------- */
 
+/* Same result in two launches instead of four (decision, scan and slot assignment fused; tile totals
+ * chained with bounded waits, HCTR_ERR_TIMEOUT in *err).  chain_scratch: hctr_scan_chained_scratch_words(u_max)
+ * words, 8-byte aligned, zero-initialised once; epoch: non-zero, different from the previous call's. */
+int hctr_push_decide_fused(const uint32_t *meta, int nrank, int rank, size_t u_max, const uint8_t *uniq_owner,
+                           const int32_t *uniq_row, const uint32_t *run_start, const int64_t *pending_cnt,
+                           int64_t push_bound, uint32_t *need_push, uint32_t *push_slot, uint32_t *chain_scratch,
+                           uint32_t epoch, uint32_t *push_count, uint32_t *push_base, uint32_t *err, void *stream);
+
 /* ---------------------------------------------------------------------------------------------
  * Peer-to-peer exchange (one process per GPU, all GPUs of one NVLink domain).
  *
@@ -226,7 +234,8 @@ typedef struct hctr_p2p_ctx {
   uint32_t cap;             /* rows per (mailbox, source) sub-region */
   size_t width;
   const hctr_p2p_box *box;  /* device array [nrank]; box[rank] is this rank's own mailbox */
-  uint32_t *cnt_in;         /* device [3*nrank]: query, push and return counts received from each peer */
+  uint32_t *cnt_in;         /* device [4*nrank+1]: query, push and return counts received from each peer,
+                               then the exclusive prefix of the query counts (nrank+1 entries) */
   uint32_t *err;            /* device error word */
   unsigned long long timeout_ns;
 } hctr_p2p_ctx;
@@ -245,16 +254,23 @@ int hctr_p2p_signal(const hctr_p2p_ctx *c, int phase, uint32_t seq, const uint32
  * c->cnt_in.  On timeout sets HCTR_ERR_TIMEOUT and records zero counts for the silent peers. */
 int hctr_p2p_wait(const hctr_p2p_ctx *c, int phase, uint32_t seq, void *stream);
 
-/* Owner: staleness flags for all received queries (slot q = source*cap + j), flag bytes stored into the
- * requesters' mailboxes, flags32 = 0/1 per slot (0 for unused slots). */
+/* Owner: applies the pushed rows of every source, source after source in rank order, in one cooperative
+ * launch (grid-wide barrier between sources).  Same arithmetic as hctr_owner_update. */
+int hctr_p2p_owner_update(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
+                          float *embedding, int64_t *version, void *stream);
+
+/* Owner: staleness flags for all received queries, indexed FLAT: q in [0, Q) runs over the queries of
+ * source 0, then source 1, ... (Q and the per-source starts are in c->cnt_in).  Flag bytes are stored
+ * into the requesters' mailboxes, flags32[q] = 0/1. */
 int hctr_p2p_stale_check(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
                          const int64_t *version, int64_t pull_bound, uint32_t *flags32, void *stream);
 
 /* Owner: ret_count[s] = rows to return to requester s, from the exclusive scan ret_slot of flags32. */
 int hctr_p2p_return_counts(const hctr_p2p_ctx *c, const uint32_t *ret_slot, uint32_t *ret_count, void *stream);
 
-/* Owner: flagged rows (+ versions) gathered straight into the requesters' mailboxes. */
-int hctr_p2p_gather(const hctr_p2p_ctx *c, const uint32_t *flags32, const uint32_t *ret_slot,
+/* Owner: flagged rows (+ versions) gathered straight into the requesters' mailboxes.  ret_q is scratch
+ * for one word per returned row (at most nrank*cap). */
+int hctr_p2p_gather(const hctr_p2p_ctx *c, const uint32_t *flags32, const uint32_t *ret_slot, uint32_t *ret_q,
                     const int32_t *row_of, const float *embedding, const int64_t *version, void *stream);
 
 /* Requester: flags of its unique keys collected from its mailbox (flags[u], flags32[u]; zeros for
