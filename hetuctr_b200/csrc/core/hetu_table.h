@@ -167,7 +167,7 @@ class HetuTable {
   size_t length_pad_ = 0;
 
   // dedupe scratch (persistent, all-zero between calls) and per-step scratch
-  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_word_base_, d_scan_, d_sk_, d_rank_, d_cnt_;
+  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_row_mask_, d_src_off_, d_src_cnt_, d_word_base_, d_scan_, d_sk_, d_rank_, d_cnt_;
   DevBuf d_need_push_, d_push_slot_, d_push_count_, d_push_base_, d_recv_idx_, d_err_;
   size_t shared_capacity_ = 0;
   uint32_t dedupe_epoch_ = 0;
@@ -182,6 +182,8 @@ class HetuTable {
   DevBuf d_rver_s_, d_rval_s_, d_rver_r_, d_rval_r_;  // returned rows
   DevBuf d_stage_grad_, d_stage_dst_;
 
+  void *h_src_ = nullptr;         // pinned staging of the per-source list descriptors
+  size_t p2p_off_cap_ = 0;        // mailbox capacity d_src_off_ was filled for
   uint32_t *h_pinned_ = nullptr;  // pinned mirror for counts read back from the device
   size_t h_pinned_words_ = 0;
 

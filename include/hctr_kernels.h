@@ -337,6 +337,19 @@ int hctr_query_versions(size_t n_unique, const int32_t *uniq_row, const int64_t 
 int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int64_t *updates,
                       const float *val, const int32_t *row_of, size_t length, size_t n_cached,
                       float *embedding, int64_t *version, uint32_t *err, void *stream);
+/* All sources at once, in two launches, with the same per-row apply order (ascending source rank) and
+ * therefore the same bits as calling hctr_owner_update once per source.  Source s's rows start at entry
+ * src_off[s] of key/updates/val and number min(src_cnt[s], cap) (both arrays in device memory; counts may
+ * only exist on the device); every source's list must be sorted by key, as the slices of a unique list
+ * are.  row_mask: one 64-bit word per OWNED row (row - n_cached), zero-initialised once; `epoch` must be
+ * non-zero and differ from every earlier call's on the same row_mask (no clearing between calls).
+ * rows_hint sizes the grids (an upper bound of the total number of rows is fine).  nsrc <= 32. */
+int hctr_owner_update_merged(int nsrc, int self, size_t cap, size_t rows_hint, size_t width, const int64_t *key,
+                             const int64_t *updates, const float *val, const unsigned long long *src_off,
+                             const uint32_t *src_cnt, const int32_t *row_of, size_t length, size_t n_cached,
+                             unsigned long long *row_mask, uint32_t epoch, float *embedding, int64_t *version,
+                             uint32_t *err, void *stream);
+
 /* Same, with the row count read from device memory (at most n_rows_max). */
 int hctr_owner_update_dev(size_t n_rows_max, const uint32_t *n_rows_dev, size_t width, const int64_t *key,
                           const int64_t *updates, const float *val, const int32_t *row_of, size_t length,
