@@ -137,7 +137,7 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
     reserveShared(1);
     h_pinned_words_ = HCTR_META_WORDS + (size_t)nrank_ + 1 + 8 * (size_t)nrank_ + 8;
     HCTR_CUDA(cudaMallocHost(&h_pinned_, h_pinned_words_ * sizeof(uint32_t)));
-    HCTR_CUDA(cudaMallocHost(&h_src_, (size_t)nrank_ * 16 + 16));
+    HCTR_CUDA(cudaMallocHost(&h_src_, (size_t)nrank_ * 16 + 32));
   } catch (...) {
     releaseAll();
     throw;
@@ -228,7 +228,7 @@ void HetuTable::initTable(const worker_t *root, const index_t *storage) {
     d_row_mask_.ensure(std::max<size_t>(S - kNonLocalStorageMax, 1) * sizeof(unsigned long long));
     HCTR_CUDA(cudaMemsetAsync(d_row_mask_.p, 0, d_row_mask_.bytes, stream_main_));
     d_src_off_.ensure((size_t)nrank_ * sizeof(unsigned long long));
-    d_src_cnt_.ensure((size_t)nrank_ * sizeof(uint32_t));
+    d_src_cnt_.ensure(((size_t)nrank_ + 1) * sizeof(uint32_t));
   }
 
   // dedupe scratch over the (owner, key) space: all-zero at rest
@@ -607,16 +607,17 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
         // all sources in two launches, same per-row order as source-by-source (with fewer than three remote
         // sources a launch per source is cheaper)
         unsigned long long *h_off = reinterpret_cast<unsigned long long *>(h_src_);
-        uint32_t *h_cnt = reinterpret_cast<uint32_t *>(h_off + n);
+        uint32_t *h_start = reinterpret_cast<uint32_t *>(h_off + n);
         size_t off = 0;
         for (int p = 0; p < n; p++) {
           h_off[p] = off;
-          h_cnt[p] = (uint32_t)prev.push_recv[p];
+          h_start[p] = (uint32_t)off;
           off += prev.push_recv[p];
         }
+        h_start[n] = (uint32_t)off;
         HCTR_CUDA(cudaMemcpyAsync(d_src_off_.p, h_off, n * sizeof(unsigned long long), cudaMemcpyHostToDevice, stream_main_));
-        HCTR_CUDA(cudaMemcpyAsync(d_src_cnt_.p, h_cnt, n * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_main_));
-        HCTR_LAUNCH(hctr_owner_update_merged(n, rank_, std::max<size_t>(push_recv, 1), push_recv, W, d_pkey_r_.as<int64_t>(),
+        HCTR_CUDA(cudaMemcpyAsync(d_src_cnt_.p, h_start, (n + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_main_));
+        HCTR_LAUNCH(hctr_owner_update_merged(n, push_recv, W, d_pkey_r_.as<int64_t>(),
                                              d_pupd_r_.as<int64_t>(), d_pval_r_.as<float>(),
                                              d_src_off_.as<unsigned long long>(), d_src_cnt_.as<uint32_t>(),
                                              d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
@@ -824,8 +825,8 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
       HCTR_CUDA(cudaStreamSynchronize(stream_main_));
       p2p_off_cap_ = cap;
     }
-    HCTR_LAUNCH(hctr_owner_update_merged(n, rank_, cap, cap, W, mine.pkey, mine.pupd, mine.pval,
-                                         d_src_off_.as<unsigned long long>(), c->cnt_in + n, d_row_of_.as<int32_t>(),
+    HCTR_LAUNCH(hctr_owner_update_merged(n, cap, W, mine.pkey, mine.pupd, mine.pval,
+                                         d_src_off_.as<unsigned long long>(), c->cnt_in + 4 * n + 1, d_row_of_.as<int32_t>(),
                                          kEmbeddingIDMax, kNonLocalStorageMax, d_row_mask_.as<unsigned long long>(),
                                          nextEpoch(), d_embedding_.as<float>(), d_version_.as<int64_t>(),
                                          d_err_.as<uint32_t>(), stream_main_));

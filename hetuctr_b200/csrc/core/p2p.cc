@@ -114,8 +114,8 @@ void P2PMailbox::reserve(size_t cap, cudaStream_t stream) {
   }
   if (!d_boxes_) HCTR_CUDA(cudaMalloc(reinterpret_cast<void **>(&d_boxes_), nrank_ * sizeof(hctr_p2p_box)));
   if (!d_cnt_in_) {
-    HCTR_CUDA(cudaMalloc(reinterpret_cast<void **>(&d_cnt_in_), (4 * nrank_ + 1) * sizeof(uint32_t)));
-    HCTR_CUDA(cudaMemset(d_cnt_in_, 0, (4 * nrank_ + 1) * sizeof(uint32_t)));
+    HCTR_CUDA(cudaMalloc(reinterpret_cast<void **>(&d_cnt_in_), (5 * nrank_ + 2) * sizeof(uint32_t)));
+    HCTR_CUDA(cudaMemset(d_cnt_in_, 0, (5 * nrank_ + 2) * sizeof(uint32_t)));
   }
   HCTR_CUDA(cudaMemcpy(d_boxes_, boxes.data(), nrank_ * sizeof(hctr_p2p_box), cudaMemcpyHostToDevice));
   mine_box_ = boxes[rank_];

@@ -91,16 +91,20 @@ __global__ void p2p_wait(hctr_p2p_ctx c, int phase, u32 seq) {
     c.cnt_in[s] = q;
     c.cnt_in[c.nrank + s] = g;
     // exclusive prefix of the query counts: flat index space [0, Q) over all received queries
-    __shared__ u32 s_q[1024];
+    __shared__ u32 s_q[1024], s_g[1024];
     s_q[s] = q;
+    s_g[s] = g;
     __syncthreads();
     if (s == 0) {
-      u32 acc = 0;
+      u32 acc = 0, accg = 0;
       for (int i = 0; i < c.nrank; i++) {
         c.cnt_in[3 * c.nrank + i] = acc;
+        c.cnt_in[4 * c.nrank + 1 + i] = accg;
         acc += s_q[i];
+        accg += s_g[i];
       }
       c.cnt_in[4 * c.nrank] = acc;
+      c.cnt_in[5 * c.nrank + 1] = accg;  // flat index space over all pushed rows
     }
   } else {
     u32 r = ok ? hdr[9] : 0u;

@@ -526,10 +526,9 @@ struct PushLists {  // where every source's pushed rows are, as seen by the owne
   const long long *key;
   const long long *upd;
   const float *val;
-  const unsigned long long *src_off;  // device [nsrc]: first entry of source s
-  const u32 *src_cnt;                 // device [nsrc]: number of entries of source s
+  const unsigned long long *src_off;  // device [nsrc]: first entry of source s in key/upd/val
+  const u32 *flat_start;              // device [nsrc+1]: exclusive prefix of the per-source row counts
   int nsrc;
-  int self;                           // this rank (never pushes to itself)
 };
 
 __device__ __forceinline__ int32_t owned_row(const int32_t *row_of, size_t length, size_t n_cached, long long k) {
@@ -538,74 +537,87 @@ __device__ __forceinline__ int32_t owned_row(const int32_t *row_of, size_t lengt
   return (row < 0 || (size_t)row < n_cached) ? -1 : row;
 }
 
-__global__ void __launch_bounds__(kThreads) owner_mark_sources(PushLists p, size_t cap, const int32_t *__restrict__ row_of,
+// flat row index f in [0, total) -> source
+__device__ __forceinline__ int push_source(const u32 *start, int nsrc, u32 f) {
+  int lo = 0, hi = nsrc;  // start[lo] <= f < start[hi]
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (start[mid] <= f) lo = mid;
+    else hi = mid;
+  }
+  return lo;
+}
+
+__global__ void __launch_bounds__(kThreads) owner_mark_sources(PushLists p, const int32_t *__restrict__ row_of,
                                                                size_t length, size_t n_cached, u64 *__restrict__ mask,
                                                                u32 epoch, u32 *err) {
-  for (int s = 0; s < p.nsrc; s++) {
-    if (s == p.self) continue;
-    const size_t n = min((size_t)p.src_cnt[s], cap);
-    const long long *key = p.key + p.src_off[s];
-    for (size_t m = (size_t)blockIdx.x * kThreads + threadIdx.x; m < n; m += (size_t)gridDim.x * kThreads) {
-      const int32_t row = owned_row(row_of, length, n_cached, key[m]);
-      if (row < 0) {
-        atomicOr(err, HCTR_ERR_NOT_OWNER);
-        continue;
-      }
-      u64 *w = &mask[(size_t)row - n_cached];
-      u64 old = *w;
-      for (;;) {  // terminates: at most nsrc writers per word, each CAS failure means another one got through
-        const u64 want = ((u32)(old >> 32) == epoch ? old : ((u64)epoch << 32)) | (1ull << s);
-        const u64 seen = atomicCAS(w, old, want);
-        if (seen == old) break;
-        old = seen;
-      }
+  __shared__ u32 start[33];
+  if (threadIdx.x <= (unsigned)p.nsrc) start[threadIdx.x] = p.flat_start[threadIdx.x];
+  __syncthreads();
+  const u32 total = start[p.nsrc];
+  for (size_t f = (size_t)blockIdx.x * kThreads + threadIdx.x; f < total; f += (size_t)gridDim.x * kThreads) {
+    const int s = push_source(start, p.nsrc, (u32)f);
+    const long long k = p.key[p.src_off[s] + (f - start[s])];
+    const int32_t row = owned_row(row_of, length, n_cached, k);
+    if (row < 0) {
+      atomicOr(err, HCTR_ERR_NOT_OWNER);
+      continue;
+    }
+    u64 *w = &mask[(size_t)row - n_cached];
+    u64 old = *w;
+    for (;;) {  // terminates: at most nsrc writers per word, each CAS failure means another one got through
+      const u64 want = ((u32)(old >> 32) == epoch ? old : ((u64)epoch << 32)) | (1ull << s);
+      const u64 seen = atomicCAS(w, old, want);
+      if (seen == old) break;
+      old = seen;
     }
   }
 }
 
 template <int LANES, bool VEC>
-__global__ void __launch_bounds__(kThreads) owner_apply_sources(PushLists p, size_t cap, size_t width,
+__global__ void __launch_bounds__(kThreads) owner_apply_sources(PushLists p, size_t width,
                                                                 const int32_t *__restrict__ row_of, size_t length,
                                                                 size_t n_cached, const u64 *__restrict__ mask,
                                                                 float *__restrict__ embedding,
                                                                 long long *__restrict__ version) {
   typedef RowT<VEC> R;
   typedef typename R::T T;
+  __shared__ u32 start[33];
+  if (threadIdx.x <= (unsigned)p.nsrc) start[threadIdx.x] = p.flat_start[threadIdx.x];
+  __syncthreads();
+  const u32 total = start[p.nsrc];
   const unsigned gl = threadIdx.x % LANES;
   const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
   const size_t E = R::elems(width);
-  for (int s = 0; s < p.nsrc; s++) {
-    if (s == p.self) continue;
-    const size_t n = min((size_t)p.src_cnt[s], cap);
-    const size_t off = p.src_off[s];
-    for (size_t m = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; m < n; m += groups) {
-      const long long k = p.key[off + m];
-      const int32_t row = owned_row(row_of, length, n_cached, k);
-      if (row < 0) continue;  // reported by the marking pass
-      const u64 mk = mask[(size_t)row - n_cached] & 0xffffffffull;  // this step's epoch, set by the marking pass
-      if (mk & ((1ull << s) - 1)) continue;  // a lower source pushes this row too: it applies everything
-      T *emb = reinterpret_cast<T *>(embedding) + (size_t)row * E;
-      long long ver_add = p.upd[off + m];
-      const T *v = reinterpret_cast<const T *>(p.val) + (off + m) * E;
-      for (size_t e = gl; e < E; e += LANES) emb[e] = R::add(emb[e], R::ld_once(v + e));
-      u64 rest = (mk >> (s + 1)) << (s + 1);  // higher sources that also push it
-      while (rest) {
-        const int s2 = __ffsll((long long)rest) - 1;
-        rest &= rest - 1;
-        // entry of key k in source s2's key-sorted list
-        const size_t off2 = p.src_off[s2];
-        size_t lo = 0, hi = min((size_t)p.src_cnt[s2], cap);
-        while (lo < hi) {
-          const size_t mid = (lo + hi) >> 1;
-          if (p.key[off2 + mid] < k) lo = mid + 1;
-          else hi = mid;
-        }
-        ver_add += p.upd[off2 + lo];
-        const T *v2 = reinterpret_cast<const T *>(p.val) + (off2 + lo) * E;
-        for (size_t e = gl; e < E; e += LANES) emb[e] = R::add(emb[e], R::ld_once(v2 + e));
+  for (size_t f = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; f < total; f += groups) {
+    const int s = push_source(start, p.nsrc, (u32)f);
+    const size_t ent = p.src_off[s] + (f - start[s]);
+    const long long k = p.key[ent];
+    const int32_t row = owned_row(row_of, length, n_cached, k);
+    if (row < 0) continue;  // reported by the marking pass
+    const u64 mk = mask[(size_t)row - n_cached] & 0xffffffffull;  // this step's epoch, set by the marking pass
+    if (mk & ((1ull << s) - 1)) continue;  // a lower source pushes this row too: it applies everything
+    T *emb = reinterpret_cast<T *>(embedding) + (size_t)row * E;
+    long long ver_add = p.upd[ent];
+    const T *v = reinterpret_cast<const T *>(p.val) + ent * E;
+    for (size_t e = gl; e < E; e += LANES) emb[e] = R::add(emb[e], R::ld_once(v + e));
+    u64 rest = (mk >> (s + 1)) << (s + 1);  // higher sources that also push it
+    while (rest) {
+      const int s2 = __ffsll((long long)rest) - 1;
+      rest &= rest - 1;
+      // entry of key k in source s2's key-sorted list
+      const size_t off2 = p.src_off[s2];
+      size_t lo = 0, hi = start[s2 + 1] - start[s2];
+      while (lo < hi) {
+        const size_t mid = (lo + hi) >> 1;
+        if (p.key[off2 + mid] < k) lo = mid + 1;
+        else hi = mid;
       }
-      if (gl == 0) version[row] = (long long)((u64)version[row] + (u64)ver_add);
+      ver_add += p.upd[off2 + lo];
+      const T *v2 = reinterpret_cast<const T *>(p.val) + (off2 + lo) * E;
+      for (size_t e = gl; e < E; e += LANES) emb[e] = R::add(emb[e], R::ld_once(v2 + e));
     }
+    if (gl == 0) version[row] = (long long)((u64)version[row] + (u64)ver_add);
   }
 }
 
@@ -653,12 +665,11 @@ __global__ void __launch_bounds__(kThreads) owner_update_all(hctr_p2p_ctx c, con
 
 using namespace hctr;
 
-extern "C" int hctr_owner_update_merged(int nsrc, int self, size_t cap, size_t rows_hint, size_t width,
-                                        const int64_t *key, const int64_t *updates, const float *val,
-                                        const unsigned long long *src_off, const uint32_t *src_cnt,
-                                        const int32_t *row_of, size_t length, size_t n_cached,
-                                        unsigned long long *row_mask, uint32_t epoch, float *embedding,
-                                        int64_t *version, uint32_t *err, void *stream) {
+extern "C" int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width, const int64_t *key,
+                                        const int64_t *updates, const float *val, const unsigned long long *src_off,
+                                        const uint32_t *flat_start, const int32_t *row_of, size_t length,
+                                        size_t n_cached, unsigned long long *row_mask, uint32_t epoch,
+                                        float *embedding, int64_t *version, uint32_t *err, void *stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (nsrc > 32 || epoch == 0) return (int)cudaErrorInvalidValue;
   if (rows_hint == 0) return 0;
@@ -667,18 +678,17 @@ extern "C" int hctr_owner_update_merged(int nsrc, int self, size_t cap, size_t r
   p.upd = (const long long *)updates;
   p.val = val;
   p.src_off = src_off;
-  p.src_cnt = src_cnt;
+  p.flat_start = flat_start;
   p.nsrc = nsrc;
-  p.self = self;
   size_t g = (rows_hint + kThreads - 1) / kThreads;
   if (g > (size_t)kSMs * 8) g = (size_t)kSMs * 8;
-  owner_mark_sources<<<(unsigned)g, kThreads, 0, st>>>(p, cap, row_of, length, n_cached, row_mask, epoch, err);
+  owner_mark_sources<<<(unsigned)g, kThreads, 0, st>>>(p, row_of, length, n_cached, row_mask, epoch, err);
   const bool al = host_aligned16(val) && host_aligned16(embedding);
-#define CALL(L, V)                                                                                        \
-  do {                                                                                                    \
-    size_t g_ = (rows_hint * L + kThreads - 1) / kThreads;                                                \
-    if (g_ > (size_t)kSMs * 8) g_ = (size_t)kSMs * 8;                                                     \
-    owner_apply_sources<L, V><<<(unsigned)g_, kThreads, 0, st>>>(p, cap, width, row_of, length, n_cached, \
+#define CALL(L, V)                                                                                    \
+  do {                                                                                                \
+    size_t g_ = (rows_hint * L + kThreads - 1) / kThreads;                                            \
+    if (g_ > (size_t)kSMs * 8) g_ = (size_t)kSMs * 8;                                                 \
+    owner_apply_sources<L, V><<<(unsigned)g_, kThreads, 0, st>>>(p, width, row_of, length, n_cached,  \
                                                                  row_mask, embedding, (long long *)version); \
   } while (0)
   HCTR_DISPATCH_ROWS(width, al, CALL);

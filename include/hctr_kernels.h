@@ -234,8 +234,9 @@ typedef struct hctr_p2p_ctx {
   uint32_t cap;             /* rows per (mailbox, source) sub-region */
   size_t width;
   const hctr_p2p_box *box;  /* device array [nrank]; box[rank] is this rank's own mailbox */
-  uint32_t *cnt_in;         /* device [4*nrank+1]: query, push and return counts received from each peer,
-                               then the exclusive prefix of the query counts (nrank+1 entries) */
+  uint32_t *cnt_in;         /* device [5*nrank+2]: query, push and return counts received from each peer,
+                               then the exclusive prefixes of the query counts and of the push counts
+                               (nrank+1 entries each) */
   uint32_t *err;            /* device error word */
   unsigned long long timeout_ns;
 } hctr_p2p_ctx;
@@ -339,14 +340,14 @@ int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int
                       float *embedding, int64_t *version, uint32_t *err, void *stream);
 /* All sources at once, in two launches, with the same per-row apply order (ascending source rank) and
  * therefore the same bits as calling hctr_owner_update once per source.  Source s's rows start at entry
- * src_off[s] of key/updates/val and number min(src_cnt[s], cap) (both arrays in device memory; counts may
- * only exist on the device); every source's list must be sorted by key, as the slices of a unique list
- * are.  row_mask: one 64-bit word per OWNED row (row - n_cached), zero-initialised once; `epoch` must be
+ * src_off[s] of key/updates/val and number flat_start[s+1] - flat_start[s] (device arrays of nsrc and nsrc+1
+ * entries; the counts may only exist on the device); every source's list must be sorted by key, as the
+ * slices of a unique list are.  row_mask: one 64-bit word per OWNED row (row - n_cached), zero-initialised once; `epoch` must be
  * non-zero and differ from every earlier call's on the same row_mask (no clearing between calls).
  * rows_hint sizes the grids (an upper bound of the total number of rows is fine).  nsrc <= 32. */
-int hctr_owner_update_merged(int nsrc, int self, size_t cap, size_t rows_hint, size_t width, const int64_t *key,
+int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width, const int64_t *key,
                              const int64_t *updates, const float *val, const unsigned long long *src_off,
-                             const uint32_t *src_cnt, const int32_t *row_of, size_t length, size_t n_cached,
+                             const uint32_t *flat_start, const int32_t *row_of, size_t length, size_t n_cached,
                              unsigned long long *row_mask, uint32_t epoch, float *embedding, int64_t *version,
                              uint32_t *err, void *stream);
 
