@@ -806,9 +806,9 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
                                   cur.uniq_row.as<int32_t>(), d_version_.as<int64_t>(), stream_main_));
   toc(sp);
   sp = tic(kPhExchange);
-  HCTR_LAUNCH(hctr_p2p_signal(c, 0, seq, meta, prev_push_valid_ && prev_batch_.unique_size > 0
-                                                   ? d_push_count_.as<uint32_t>() : nullptr, stream_main_));
-  HCTR_LAUNCH(hctr_p2p_wait(c, 0, seq, stream_main_));
+  HCTR_LAUNCH(hctr_p2p_signal_wait(c, 0, seq, meta, prev_push_valid_ && prev_batch_.unique_size > 0
+                                                        ? d_push_count_.as<uint32_t>() : nullptr, nullptr,
+                                   stream_main_));
   toc(sp);
 
   // C. owner applies the pushed rows of each source in rank order
@@ -860,15 +860,13 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
   HCTR_LAUNCH(hctr_scan_exclusive_u32_chained(d_flag32_.as<uint32_t>(), d_ret_slot_.as<uint32_t>(), slots,
                                               c->cnt_in + 4 * n, d_chain2_.as<uint32_t>(), nextEpoch(),
                                               d_err_.as<uint32_t>(), stream_main_));
-  HCTR_LAUNCH(hctr_p2p_return_counts(c, d_ret_slot_.as<uint32_t>(), d_retcnt_s_.as<uint32_t>(), stream_main_));
   d_ret_q_.ensure((slots + 1) * sizeof(uint32_t));
   HCTR_LAUNCH(hctr_p2p_gather(c, d_flag32_.as<uint32_t>(), d_ret_slot_.as<uint32_t>(), d_ret_q_.as<uint32_t>(),
                               d_row_of_.as<int32_t>(),
                               d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
   toc(sp);
   sp = tic(kPhExchange);
-  HCTR_LAUNCH(hctr_p2p_signal(c, 1, seq, meta, d_retcnt_s_.as<uint32_t>(), stream_main_));
-  HCTR_LAUNCH(hctr_p2p_wait(c, 1, seq, stream_main_));
+  HCTR_LAUNCH(hctr_p2p_signal_wait(c, 1, seq, meta, nullptr, d_ret_slot_.as<uint32_t>(), stream_main_));
   toc(sp);
 
   // E. requester: flags -> row indices in its own mailbox, cache refresh, expand

@@ -65,9 +65,19 @@ __global__ void p2p_signal(hctr_p2p_ctx c, int phase, u32 seq, const u32 *__rest
   }
 }
 
+// Signal and wait in one launch: thread p publishes this rank's counts to peer p, then waits for peer p's.
+// Phase 1 derives the per-requester return counts from the scan itself (ret_slot at the segment bounds).
+__global__ void p2p_signal_wait(hctr_p2p_ctx c, int phase, u32 seq, const u32 *__restrict__ meta,
+                                const u32 *__restrict__ counts, const u32 *__restrict__ ret_slot);
+
 // One thread per source.  Polls this rank's own memory; gives up after timeout_ns.
+__device__ __forceinline__ void p2p_wait_body(const hctr_p2p_ctx &c, int phase, u32 seq, int s);
+
 __global__ void p2p_wait(hctr_p2p_ctx c, int phase, u32 seq) {
-  const int s = threadIdx.x;  // launched with exactly nrank threads
+  p2p_wait_body(c, phase, seq, threadIdx.x);  // launched with exactly nrank threads
+}
+
+__device__ __forceinline__ void p2p_wait_body(const hctr_p2p_ctx &c, int phase, u32 seq, int s) {
   const u32 *hdr = c.box[c.rank].hdr + (size_t)s * kHdrWords;
   const u32 *flag = hdr + (phase == 0 ? 0 : 8);
   const u64 t0 = now_ns();
@@ -125,6 +135,24 @@ __device__ __forceinline__ unsigned source_of(const u32 *qstart, int nrank, u32 
     else hi = mid;
   }
   return (unsigned)lo;
+}
+
+__global__ void p2p_signal_wait(hctr_p2p_ctx c, int phase, u32 seq, const u32 *__restrict__ meta,
+                                const u32 *__restrict__ counts, const u32 *__restrict__ ret_slot) {
+  const int p = threadIdx.x;  // launched with exactly nrank threads
+  __threadfence_system();
+  u32 *hdr = c.box[p].hdr + (size_t)c.rank * kHdrWords;
+  if (phase == 0) {
+    const u32 *seg = meta + HCTR_META_SEG;
+    hdr[1] = seg[p + 1] - seg[p];
+    hdr[2] = counts ? counts[p] : 0u;
+    st_release_sys(hdr + 0, seq);
+  } else {
+    const u32 *qstart = c.cnt_in + 3 * c.nrank;
+    hdr[9] = ret_slot[qstart[p + 1]] - ret_slot[qstart[p]];
+    st_release_sys(hdr + 8, seq);
+  }
+  p2p_wait_body(c, phase, seq, p);
 }
 
 __global__ void __launch_bounds__(kThreads) p2p_stale_check(hctr_p2p_ctx c, const int32_t *__restrict__ row_of,
@@ -264,6 +292,14 @@ extern "C" int hctr_p2p_signal(const hctr_p2p_ctx *c, int phase, uint32_t seq, c
                                const uint32_t *counts, void *stream) {
   if (c->nrank > 1024) return (int)cudaErrorInvalidValue;
   p2p_signal<<<1, 1024, 0, (cudaStream_t)stream>>>(*c, phase, seq, meta, counts);
+  count_launches(1);
+  return launch_status();
+}
+
+extern "C" int hctr_p2p_signal_wait(const hctr_p2p_ctx *c, int phase, uint32_t seq, const uint32_t *meta,
+                                    const uint32_t *counts, const uint32_t *ret_slot, void *stream) {
+  if (c->nrank > 1024) return (int)cudaErrorInvalidValue;
+  p2p_signal_wait<<<1, c->nrank, 0, (cudaStream_t)stream>>>(*c, phase, seq, meta, counts, ret_slot);
   count_launches(1);
   return launch_status();
 }

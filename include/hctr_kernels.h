@@ -134,13 +134,14 @@ typedef struct hctr_dedupe_args {
   unsigned long long *bits; /* [nrank*length_pad/64] */
   uint8_t *blk_flag;        /* [nrank*length_pad/4096] block touched by this batch */
   uint32_t *cnt;            /* [B+1] occurrences per unique key (consumed by the run-start scan) */
-  /* scratch that needs no initial value */
+  /* epoch-tagged scratch: zero-initialised ONCE, never cleared afterwards */
   uint32_t *chain_scratch;  /* [2 * (nblocks / 8 + 2)] words, 8-byte aligned: CTA totals of the block-rank kernel */
-  uint32_t epoch;           /* non-zero, different from the previous call's (tags chain_scratch/scan_scratch) */
-  uint32_t *word_base;      /* [nrank*length_pad/64] */
   uint32_t *scan_scratch;   /* hctr_scan_chained_scratch_words(B + 1) words, 8-byte aligned */
+  uint32_t epoch;           /* non-zero, different from every earlier call's on the same scratch */
+  /* scratch that needs no initial value */
+  uint32_t *word_base;      /* [nrank*length_pad/64] */
   unsigned long long *sk;   /* [B] sort keys */
-  uint32_t *rank_in_run;    /* [B] */
+  uint32_t *rank_in_run;    /* [B] (also staging of the long-run ordering kernel) */
   /* outputs */
   int64_t *uniq;            /* [B] unique keys, owner-major, key ascending */
   uint8_t *uniq_owner;      /* [B] */
@@ -254,6 +255,11 @@ int hctr_p2p_signal(const hctr_p2p_ctx *c, int phase, uint32_t seq, const uint32
 /* Waits (bounded) until every peer has released `seq` for `phase`; copies the announced counts into
  * c->cnt_in.  On timeout sets HCTR_ERR_TIMEOUT and records zero counts for the silent peers. */
 int hctr_p2p_wait(const hctr_p2p_ctx *c, int phase, uint32_t seq, void *stream);
+
+/* hctr_p2p_signal followed by hctr_p2p_wait in one launch.  Phase 0 as hctr_p2p_signal; phase 1 computes
+ * the return counts itself from the exclusive scan ret_slot of the stale flags (counts is ignored). */
+int hctr_p2p_signal_wait(const hctr_p2p_ctx *c, int phase, uint32_t seq, const uint32_t *meta,
+                         const uint32_t *counts, const uint32_t *ret_slot, void *stream);
 
 /* Owner: applies the pushed rows of every source, source after source in rank order, in one cooperative
  * launch (grid-wide barrier between sources).  Same arithmetic as hctr_owner_update. */
