@@ -104,9 +104,26 @@ def _load_module():
     return _mod
 
 
+_part = None
+
+
+def _load_partition():
+    global _part
+    if _part is None:
+        path = os.path.join(LIB_DIR, "hetuCTR_partition" + sysconfig.get_config_var("EXT_SUFFIX"))
+        if not os.path.exists(path):
+            raise ImportError(f"{path} is missing: build it with `python -m hetuctr_b200.build`")
+        spec = importlib.util.spec_from_file_location("hetuCTR_partition", path)
+        _part = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(_part)
+    return _part
+
+
 def __getattr__(name):
     if name == "hetuCTR":
         return _load_module()
+    if name == "hetuCTR_partition":
+        return _load_partition()
     raise AttributeError(name)
 
 

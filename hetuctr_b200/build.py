@@ -32,6 +32,7 @@ CXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-I", INCLUDE, "-I", CSRC,
 
 LIB_NAME = "libhetuctr_b200.so"
 MOD_NAME = "hetuCTR" + sysconfig.get_config_var("EXT_SUFFIX")
+PART_NAME = "hetuCTR_partition" + sysconfig.get_config_var("EXT_SUFFIX")
 
 
 def _headers():
@@ -84,6 +85,13 @@ def build(force=False, verbose=False):
         _run(["g++", *CXX_FLAGS, "-fvisibility=hidden", "-shared", "-I", pybind11.get_include(),
               "-I", sysconfig.get_paths()["include"], mod_src, "-o", mod,
               "-L", LIB, "-lhetuctr_b200", "-Wl,-rpath,$ORIGIN"], verbose)
+    # the offline partitioner (CPU only): its own small module, `hetuCTR_partition`
+    pmod = os.path.join(LIB, PART_NAME)
+    psrc = [os.path.join(CSRC, "partition/partition.cc"), os.path.join(CSRC, "partition/module.cc")]
+    if force or _stale(pmod, psrc + hdrs):
+        import pybind11
+        _run(["g++", *CXX_FLAGS, "-fvisibility=hidden", "-shared", "-I", pybind11.get_include(),
+              "-I", sysconfig.get_paths()["include"], *psrc, "-o", pmod], verbose)
     return lib, mod
 
 

@@ -72,6 +72,33 @@ def build(reference="/root/reference", force=False, verbose=False):
     return MODULE
 
 
+PARTITION_MODULE = os.path.join(OUT, "partition", "hetuCTR_partition" + sysconfig.get_config_var("EXT_SUFFIX"))
+
+
+def build_partition(reference="/root/reference", force=False, verbose=False):
+    """The reference's offline partitioner (csrc/partition/), compiled WITHOUT OpenMP: its `omp parallel for`
+    pragmas are then ignored, the sweeps run sequentially and the result is reproducible (its rand() starts from
+    the C library's default seed in a fresh process)."""
+    csrc = os.path.join(reference, "csrc")
+    if not os.path.isdir(csrc):
+        raise RuntimeError(f"reference sources not found at {csrc}")
+    if os.path.exists(PARTITION_MODULE) and not force:
+        return PARTITION_MODULE
+    import pybind11
+    os.makedirs(os.path.dirname(PARTITION_MODULE), exist_ok=True)
+    cmd = ["g++", "-O2", "-std=c++17", "-w", "-fPIC", "-shared", "-fvisibility=hidden", "-I", csrc,
+           "-I", pybind11.get_include(), "-I", sysconfig.get_paths()["include"],
+           os.path.join(csrc, "partition", "partition.cc"), os.path.join(csrc, "partition", "pybind.cc"),
+           "-o", PARTITION_MODULE]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("reference partitioner build failed:\n" + r.stdout[-4000:])
+    return PARTITION_MODULE
+
+
 if __name__ == "__main__":
     ref = sys.argv[sys.argv.index("--reference") + 1] if "--reference" in sys.argv else "/root/reference"
     print(build(ref, force="--force" in sys.argv, verbose=True))
+    print(build_partition(ref, force="--force" in sys.argv, verbose=True))
