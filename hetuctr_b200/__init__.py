@@ -74,6 +74,8 @@ def lib():
     L.hctr_table_dump.restype = c.c_longlong
     L.hctr_table_dump.argtypes = [vp, c.c_char_p, i32, vp]
     L.hctr_table_set_embedding.argtypes = [vp, vp]
+    L.hctr_table_export.argtypes = [vp, ctypes.c_char_p]
+    L.hctr_table_import.argtypes = [vp, ctypes.c_char_p]
     L.hctr_table_stats.argtypes = [vp, vp]
     L.hctr_table_exchange_name.restype = c.c_char_p
     L.hctr_table_exchange_name.argtypes = [vp]
@@ -202,6 +204,14 @@ class Table:
         if rows.size != self.stats()["stored_rows"] * self.width:
             raise RuntimeError("set_embedding: expected stored_rows * width values")
         self._check(self._lib.hctr_table_set_embedding(self._h, rows.ctypes.data))
+
+    def export_state(self, path):
+        """Writes this rank's rows, versions and pending cached-row updates to `path`."""
+        self._check(self._lib.hctr_table_export(self._h, str(path).encode()))
+
+    def import_state(self, path):
+        """Loads a file written by export_state() of a table built from the same arguments."""
+        self._check(self._lib.hctr_table_import(self._h, str(path).encode()))
 
     def stats(self):
         out = (ctypes.c_longlong * 11)()

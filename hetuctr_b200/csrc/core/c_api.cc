@@ -132,6 +132,14 @@ int hctr_table_set_embedding(hctr_table *t, const float *rows) {
   return guarded([&] { t->impl->setEmbedding(rows); });
 }
 
+int hctr_table_export(hctr_table *t, const char *path) {
+  return guarded([&] { t->impl->exportState(path); });
+}
+
+int hctr_table_import(hctr_table *t, const char *path) {
+  return guarded([&] { t->impl->importState(path); });
+}
+
 int hctr_table_stats(hctr_table *t, long long out[11]) {
   const hetuCTR::StepStats &s = t->impl->stats();
   out[0] = (long long)s.batch;

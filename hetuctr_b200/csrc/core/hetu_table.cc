@@ -304,6 +304,7 @@ void HetuTable::reserveShared(size_t batch) {
 void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   HCTR_CUDA(cudaSetDevice(device_id_));
   finalizePending();
+  batch_open_ = true;
   std::swap(cur_batch_, prev_batch_);
   BatchDesc &cur = cur_batch_, &prev = prev_batch_;
   reserveBatch(cur, std::max<size_t>(batch_size, 1));
@@ -464,6 +465,7 @@ const void *HetuTable::stageIn(const void *ptr, size_t bytes, DevBuf &buf, cudaS
 // ------------------------------------------------------------------------------------------------
 void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   HCTR_CUDA(cudaSetDevice(device_id_));
+  batch_open_ = false;
   BatchDesc &cur = cur_batch_, &prev = prev_batch_;
   const int n = nrank_;
   const size_t W = kEmbeddingWidth;

@@ -126,6 +126,12 @@ class HetuTable {
   long long dump(const std::string &what, bool prev, void *out);
   // Overwrites the local rows (local row order) from host memory.
   void setEmbedding(const embed_t *host_rows);
+  // Writes / reads the learned state (rows, versions, pending gradients and counts of cached rows) to a file.
+  // The importing table must have been constructed with the same rank, nrank, length, width and storage_arr.
+  // Import is only legal between steps (not between preprocess and push_pull); batches preprocessed before
+  // it are dropped, so the next push_pull behaves like the first one of a fresh table.
+  void exportState(const std::string &path);
+  void importState(const std::string &path);
   const StepStats &stats() const { return stats_; }
   // "none" (single rank), "nccl", "inproc" or "p2p"
   const char *exchangeName() const;
@@ -144,6 +150,7 @@ class HetuTable {
   void releaseAll();
   void finalizeBatch();
   void finalizePending();
+  void quiesce();  // every stream drained, pending batch sizes read back
   void exchangeP2P(embed_t *dst_dev);
   const void *stageIn(const void *ptr, size_t bytes, DevBuf &buf, cudaStream_t s);
 
@@ -160,6 +167,7 @@ class HetuTable {
   std::unique_ptr<P2PMailbox> p2p_;  // device-driven exchange (one process per GPU, peer access); else NCCL groups
   bool use_p2p_ = false;
   bool p2p_counts_pending_ = false;
+  bool batch_open_ = false;          // preprocess done, push_pull not yet
   bool prev_push_valid_ = false;     // d_push_count_/d_push_base_ describe prev_batch_
 
   // table state

@@ -360,6 +360,203 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_wide(ReduceKernelA
   }
 }
 
+// Work-balanced streaming variant of the kernel above (rows of 128..512 floats).
+// Balance: a key costs (its gradient rows + 2) row transfers - the rows it sums plus the read and write of
+// its table row - and cost(k) = run_start[k] + 2k, the cost of all keys before k, grows strictly with k.
+// Warp w of n_warps takes the keys whose cost(k) falls into [w*T, (w+1)*T), T = ceil(cost(U) / n_warps): every
+// warp moves about the same number of rows however the run lengths are distributed over the key space
+// (small-vocabulary fields sit at the end of the unique list and have runs tens of times longer than the
+// rest).  The two range ends are found with a 32-way search (one probe per lane).
+
+// first k in [0, n_unique] with run_start[k] + 2k >= target; the caller guarantees cost(n_unique) >= target
+__device__ __forceinline__ u32 first_key_at_cost(const u32 *__restrict__ run_start, u32 n_unique, u64 target,
+                                                 unsigned lane) {
+  u32 lo = 0, hi = n_unique;
+  while (hi > lo) {
+    const u32 span = hi - lo;
+    const u32 step = (span + 30) / 31;  // 31 steps cover the span: the last lane always probes hi
+    const u64 off = (u64)lane * step;
+    const u32 probe = off >= span ? hi : lo + (u32)off;
+    const bool ge = (u64)run_start[probe] + 2ull * probe >= target;
+    const unsigned m = __ballot_sync(0xffffffffu, ge);  // monotone: true from some lane upwards (lane 31 is true)
+    const int f = __ffs(m) - 1;
+    const u32 new_hi = __shfl_sync(0xffffffffu, probe, f);
+    const u32 below = __shfl_sync(0xffffffffu, probe, f > 0 ? f - 1 : 0);
+    lo = f > 0 ? below + 1 : lo;
+    hi = f > 0 ? new_hi : lo;
+  }
+  return lo;
+}
+
+// Streaming: the rows travel through shared memory.  Every warp owns a
+// ring of D row slots; each lane copies its own 16-byte pieces of a row with cp.async (one commit group per
+// row) and later reads back exactly those pieces, so no barrier is needed, and D-1 row transfers stay in
+// flight per warp without holding them in registers.  The rows of a warp form one stream: for every key its
+// table row (if it is stored here), then its gradient rows in batch order; the consumer adds them in that
+// order, so the sums are the ones a sequential loop produces.
+__device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
+  const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+struct RowCursor {  // warp-uniform position in the row stream of one 32-key chunk
+  unsigned mask;    // keys not yet started
+  int k;            // lane that holds the current key, -1 = stream exhausted
+  int j;            // -1 = the key's table row, 0..len-1 = its gradient rows
+  u32 l, len;
+  int type, row;
+};
+
+__device__ __forceinline__ void cursor_next_key(RowCursor &c, u32 l, u32 len, int type, int row) {
+  c.k = c.mask ? __ffs(c.mask) - 1 : -1;
+  c.mask &= c.mask - 1;
+  if (c.k >= 0) {
+    c.l = __shfl_sync(0xffffffffu, l, c.k);
+    c.len = __shfl_sync(0xffffffffu, len, c.k);
+    c.type = __shfl_sync(0xffffffffu, type, c.k);
+    c.row = __shfl_sync(0xffffffffu, row, c.k);
+    c.j = c.type != 0 ? -1 : 0;
+  }
+}
+
+template <int D, int EPL>
+__global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKernelArgs ka) {
+  extern __shared__ float4 ring_all[];
+  const hctr_reduce_args &a = ka.a;
+  typedef RowT<true> R;
+  typedef float4 T;
+  const unsigned lane = threadIdx.x & 31;
+  const u64 warp = ((u64)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const u64 n_warps = ((u64)gridDim.x * kThreads) >> 5;
+  const size_t E = a.width / 4;
+  const u32 U = (u32)a.n_unique;
+  const T *grad = reinterpret_cast<const T *>(a.grad);
+  T *emb_base = reinterpret_cast<T *>(a.embedding);
+  T *pend_base = reinterpret_cast<T *>(a.pending);
+  T *ring = ring_all + (size_t)(threadIdx.x >> 5) * D * E;
+  const u32 n_pos = a.run_start[U];
+  const u64 total = (u64)n_pos + 2ull * U;
+  const u64 per_warp = (total + n_warps - 1) / n_warps;
+  if (warp * per_warp >= total) return;
+  const u32 k_lo = first_key_at_cost(a.run_start, U, warp * per_warp, lane);
+  const u32 k_hi = (warp + 1) * per_warp >= total ? U : first_key_at_cost(a.run_start, U, (warp + 1) * per_warp, lane);
+  for (u32 u0 = k_lo; u0 < k_hi; u0 += 32) {
+    const u32 my_u = u0 + lane;
+    u32 l = 0, len = 0;
+    unsigned long long outp = 0;  // destination of this lane's key if it is pushed
+    int row = 0, type = -1;       // type -1: nothing to do for this lane's key
+    if (my_u < k_hi) {
+      l = a.run_start[my_u];
+      len = a.run_start[my_u + 1] - l;
+      if (len > 0 && len <= HCTR_LIGHT_RUN) {
+        PushDest dest;
+        const RowTarget t = reduce_bookkeeping(a, ka.p2p, my_u, len, true, &dest);
+        row = t.row;
+        type = t.type;
+        outp = (unsigned long long)dest.val;
+      }
+    }
+    const unsigned todo = __ballot_sync(0xffffffffu, type >= 0);
+    if (!todo) continue;
+    RowCursor P, C;
+    P.mask = C.mask = todo;
+    cursor_next_key(P, l, len, type, row);
+    cursor_next_key(C, l, len, type, row);
+    // window of 32 batch positions, one per lane (the positions of consecutive keys are consecutive)
+    u32 q_base = 0, sp = 0;
+    bool have_window = false;
+    int slot_p = 0, slot_c = 0;
+    T sum[EPL], e_old[EPL];
+#pragma unroll
+    for (int i = 0; i < EPL; i++) sum[i] = R::zero(), e_old[i] = R::zero();
+
+    auto issue = [&]() {  // copy the producer's current row into slot_p, then move the producer on
+      if (P.k >= 0) {
+        const T *src;
+        if (P.j < 0) {
+          src = emb_base + (size_t)P.row * E;
+        } else {
+          const u32 q = P.l + (u32)P.j;
+          if (!have_window || q - q_base >= 32u) {
+            q_base = q;
+            have_window = true;
+            sp = q_base + lane < n_pos ? a.sorted_pos[q_base + lane] : 0u;
+          }
+          const u32 pos = __shfl_sync(0xffffffffu, sp, (int)(q - q_base));
+          src = grad + (size_t)pos * E;
+        }
+        T *dst = ring + (size_t)slot_p * E;
+#pragma unroll
+        for (int i = 0; i < EPL; i++) {
+          const size_t c = lane + 32u * i;
+          if (c < E) cp_async16(dst + c, src + c);
+        }
+        if (++P.j == (int)P.len) cursor_next_key(P, l, len, type, row);
+      }
+      cp_async_commit();
+      slot_p = slot_p + 1 == D ? 0 : slot_p + 1;
+    };
+
+#pragma unroll
+    for (int i = 0; i < D - 1; i++) issue();
+    while (C.k >= 0) {
+      issue();
+      cp_async_wait<D - 1>();
+      const T *src = ring + (size_t)slot_c * E;
+      slot_c = slot_c + 1 == D ? 0 : slot_c + 1;
+      if (C.j < 0) {
+#pragma unroll
+        for (int i = 0; i < EPL; i++) {
+          const size_t c = lane + 32u * i;
+          if (c < E) e_old[i] = src[c];
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < EPL; i++) {
+          const size_t c = lane + 32u * i;
+          if (c < E) sum[i] = R::add(sum[i], src[c]);
+        }
+      }
+      if (++C.j == (int)C.len) {
+        // the key is complete: scale once, then the update its storage class asks for
+        const unsigned long long outk = __shfl_sync(0xffffffffu, outp, C.k);
+        T *emb = emb_base + (C.type != 0 ? (size_t)C.row * E : 0);
+        T *pend = pend_base + (C.type >= 2 ? (size_t)C.row * E : 0);
+        T *out = reinterpret_cast<T *>(outk);
+#pragma unroll
+        for (int i = 0; i < EPL; i++) {
+          const size_t c = lane + 32u * i;
+          if (c < E) {
+            const T sc = R::scale(sum[i], a.neg_lr);
+            if (C.type == 0) {
+              out[c] = sc;
+            } else {
+              emb[c] = R::add(e_old[i], sc);
+              if (C.type >= 2) {
+                const T p = R::add(pend[c], sc);
+                if (C.type == 2) {
+                  out[c] = p;
+                  pend[c] = R::zero();
+                } else {
+                  pend[c] = p;
+                }
+              }
+            }
+          }
+          sum[i] = R::zero();
+        }
+        cursor_next_key(C, l, len, type, row);
+      }
+    }
+    cp_async_wait<0>();
+  }
+}
+
 // Long runs (hot keys, up to the whole batch): one CTA per key.  All threads stream the key's
 // gradient rows into a ring of shared-memory stages with cp.async (16-byte copies, several stages in
 // flight), and one thread per row element adds the staged rows in order.  The sequential sum of a
@@ -762,7 +959,28 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
     cudaError_t e = cudaEventRecord((cudaEvent_t)a.fork_event, s);
     if (e != cudaSuccess) return (int)e;
   }
-  if (al && a.width % 4 == 0 && a.width >= 128) {
+  if (al && a.width % 4 == 0 && a.width >= 128 && a.width <= 512 && a.n_unique < 0x7fffffffu) {
+    const size_t E = a.width / 4;
+    const int variant = E <= 32 ? 0 : E <= 64 ? 1 : 2;
+    void (*kernel)(ReduceKernelArgs) = variant == 0   ? grad_reduce_short_stream<8, 1>
+                                       : variant == 1 ? grad_reduce_short_stream<4, 2>
+                                                      : grad_reduce_short_stream<2, 4>;
+    const int depth = variant == 0 ? 8 : variant == 1 ? 4 : 2;
+    const size_t smem = (size_t)(kThreads / 32) * depth * E * sizeof(float4);  // at most 32 KB
+    static int per_sm_of[3][3] = {};  // resident thread blocks per SM, by kernel variant and ring size class
+    int &per_sm = per_sm_of[variant][smem <= 16384 ? 0 : smem <= 24576 ? 1 : 2];
+    if (per_sm == 0) {
+      cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, kThreads, smem);
+      if (e != cudaSuccess) return (int)e;
+      if (per_sm < 1) per_sm = 1;
+    }
+    // two rounds of equal-cost thread blocks (one, two and four rounds measured the same); small batches get
+    // fewer, not thinner, warps
+    size_t ctas = (size_t)kSMs * per_sm * 2;
+    const size_t enough = (3 * a.n_unique / 48 * 32 + kThreads - 1) / kThreads + 1;
+    if (ctas > enough) ctas = enough;
+    kernel<<<(unsigned)ctas, kThreads, smem, s>>>(ka);
+  } else if (al && a.width % 4 == 0 && a.width >= 128) {
     size_t ctas = ((a.n_unique + kWideChunk - 1) / kWideChunk * 32 + kThreads - 1) / kThreads;
     const size_t cap = (size_t)kSMs * 8;
     if (ctas > cap) ctas = cap;

@@ -112,7 +112,12 @@ PYBIND11_MODULE(hetuCTR, m) {
         if ((size_t)rows.size() != t.kStorageMax * t.kEmbeddingWidth)
           throw std::runtime_error("set_embedding: expected stored_rows * width values");
         t.setEmbedding(rows.data());
-      });
+      })
+      // checkpoint of this rank's learned state (the reference has none)
+      .def("export_state", [](TableContainer &t, const std::string &path) { t.exportState(path); },
+           py::arg("path"), py::call_guard<py::gil_scoped_release>())
+      .def("import_state", [](TableContainer &t, const std::string &path) { t.importState(path); },
+           py::arg("path"), py::call_guard<py::gil_scoped_release>());
 
   m.def("seed", [](unsigned long seed) { set_seed(seed); });
 }

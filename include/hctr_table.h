@@ -72,6 +72,14 @@ long long hctr_table_dump(hctr_table *t, const char *what, int prev, void *out);
 /* Overwrites all local rows from host memory ([stored rows, width], local row order). */
 int hctr_table_set_embedding(hctr_table *t, const float *rows);
 
+/* Checkpoint (no counterpart in the reference, which cannot save a table at all): writes / reads the rows,
+ * versions and, for cached rows, pending gradients and pending-update counts of this rank to `path`.  The
+ * importing table must have been created with the same rank, nrank, length, width and storage_arr; a file of
+ * another shape, with other keys, truncated or with a wrong checksum is refused before anything is changed.
+ * Import is legal between steps only; batches preprocessed earlier are dropped. */
+int hctr_table_export(hctr_table *t, const char *path);
+int hctr_table_import(hctr_table *t, const char *path);
+
 /* Sizes of the last push_pull: {batch, unique, prev_batch, prev_unique, pushed_rows,
  * received_push_rows, queried_keys, returned_rows, received_rows, stored_rows, cached_rows}. */
 int hctr_table_stats(hctr_table *t, long long out[11]);
