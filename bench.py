@@ -254,7 +254,8 @@ def run_ours(args):
             "wall_ms_per_step": wall * 1e3 / args.steps,
             "clocks": clk,
         }
-        if not args.no_cpu_baseline:
+        # the CPU baseline is a single-GPU-run item (a multi-rank launcher also pins OpenMP to one thread)
+        if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(args, world)
     table.close()
     if world > 1:

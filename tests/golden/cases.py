@@ -11,6 +11,12 @@ CASES = {
     "r2_hybrid_bsp": dict(nrank=2, length=1500, width=8, batch=400, steps=6, pull=0, push=0, lr=0.05, cache=0.4, seed=22),
     "r2_hybrid_stale": dict(nrank=2, length=800, width=4, batch=400, steps=8, pull=2, push=3, lr=0.05, cache=0.5, seed=23),
     "r4_hybrid_stale": dict(nrank=4, length=1200, width=4, batch=256, steps=6, pull=1, push=2, lr=0.1, cache=0.3, seed=41),
+    # rows of 128 / 256 floats (the shapes the benchmark configurations use); float arrays are recorded as
+    # digests (see digest() below) to keep the fixtures small
+    "r1_rows128": dict(nrank=1, length=1500, width=128, batch=1200, steps=4, pull=0, push=0, lr=0.1, cache=0.0,
+                       seed=51, digest=True),
+    "r2_rows256_stale": dict(nrank=2, length=1000, width=256, batch=700, steps=5, pull=2, push=3, lr=0.05,
+                             cache=0.4, seed=52, digest=True),
 }
 
 # arrays recorded after every preprocess (per rank) and after the last step
@@ -24,6 +30,15 @@ INIT_CASES = {
     "init_uniform": (2, -0.25, 0.75, 3, 4096),
     "init_truncated": (3, 0.0, 1.0, 5, 4096),
 }
+
+
+def digest(rows, width):
+    """Compact stand-in for a [n, width] float array: per-row sum and sum of magnitudes (float64) plus six
+    sampled columns.  Every row is still checked, at a fraction of the size."""
+    rows = np.asarray(rows, dtype=np.float32).reshape(-1, width)
+    cols = sorted({0, 1, width // 2 - 1, width // 2, width - 2, width - 1} & set(range(width)))
+    r64 = rows.astype(np.float64)
+    return {"rowsum": r64.sum(1), "rowabs": np.abs(r64).sum(1), "cols": rows[:, cols].copy()}
 
 
 def make_inputs(name):

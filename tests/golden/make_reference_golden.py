@@ -29,15 +29,26 @@ def worker(name, rank, port, q):
                       pull_bound=c["pull"], push_bound=c["push"], root_arr=root, storage_arr=storage[rank],
                       init_kind=0, init_a=0.0, init_b=0.0, learning_rate=c["lr"], verbose=0)
     out = {}
+
+    def put(key, rows):  # float rows: whole, or as a digest for the wide-row cases
+        if c.get("digest"):
+            for part, v in cases.digest(rows, W).items():
+                out[f"{key}.{part}"] = v
+        else:
+            out[key] = rows
+
     t.set_embedding(cases.layout_rows(root, storage[rank], rank, emb[rank]))
     for s in range(c["steps"]):
         k = keys[s][rank]
         t.preprocess(k.ctypes.data, k.size)
         for a in cases.INDEX_ARRAYS:
             out[f"s{s}_r{rank}_{a}"] = t.dump(a)
-        out[f"s{s}_r{rank}_dst"] = t.push_pull_np(None if grads[s] is None else grads[s][rank], k.size)
+        put(f"s{s}_r{rank}_dst", t.push_pull_np(None if grads[s] is None else grads[s][rank], k.size))
     for a in cases.STATE_ARRAYS:
-        out[f"final_r{rank}_{a}"] = t.dump(a)
+        if a in ("embedding", "gradient"):
+            put(f"final_r{rank}_{a}", t.dump(a))
+        else:
+            out[f"final_r{rank}_{a}"] = t.dump(a)
     q.put(out)
 
 

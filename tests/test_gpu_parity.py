@@ -61,7 +61,7 @@ def test_config1_plumbing(oracle_mod):
     gw.close()
 
 
-@pytest.mark.parametrize("width", [1, 3, 4, 8, 20, 32, 64, 100, 128, 256])
+@pytest.mark.parametrize("width", [1, 3, 4, 8, 20, 32, 64, 100, 128, 132, 256, 512, 516, 1024])
 def test_single_rank_widths(oracle_mod, width):
     N, B = 5000, 3000
     root = np.zeros(N, dtype=np.uint8)
@@ -175,6 +175,22 @@ def test_multi_rank_parity(oracle_mod, nrank, pull, push, frac):
     grads = [None] + [[rng.normal(0, 1, size=(len(k), W)).astype(np.float32) for k in batches[s - 1]]
                       for s in range(1, 8)]
     grads[6] = None  # an inference step in the middle
+    run_steps(gw, ow, batches, grads)
+    gw.close()
+
+
+@pytest.mark.parametrize("width", [128, 132, 256, 260, 512, 640])
+def test_multi_rank_wide_rows(oracle_mod, width):
+    # rows of 128..512 floats take the streaming reduction, wider ones the register kernel; with caches and
+    # bounds every storage class (not stored / owned / cached push / cached hold) occurs
+    nrank, N, B = 3, 2500, 900
+    rng = np.random.RandomState(width)
+    root = rng.randint(nrank, size=N).astype(np.uint8)
+    storage = _hybrid_storage(root, nrank, rng, 0.4)
+    gw, ow = make_worlds(oracle_mod, nrank, N, width, 2, 3, 0.1, root, storage)
+    batches = [[(rng.zipf(1.15, size=B) - 1) % N for _ in range(nrank)] for _ in range(5)]
+    grads = [None] + [[rng.normal(0, 1, size=(len(k), width)).astype(np.float32) for k in batches[s - 1]]
+                      for s in range(1, 5)]
     run_steps(gw, ow, batches, grads)
     gw.close()
 
