@@ -74,6 +74,7 @@ def lib():
     L.hctr_table_dump.restype = c.c_longlong
     L.hctr_table_dump.argtypes = [vp, c.c_char_p, i32, vp]
     L.hctr_table_set_embedding.argtypes = [vp, vp]
+    L.hctr_table_timeline.argtypes = [vp, vp, ctypes.c_int]
     L.hctr_table_export.argtypes = [vp, ctypes.c_char_p]
     L.hctr_table_import.argtypes = [vp, ctypes.c_char_p]
     L.hctr_table_stats.argtypes = [vp, vp]
@@ -222,6 +223,7 @@ class Table:
               "expand")
 
     def profile(self, enable=True):
+        """False/0: off; True/1: time every step; k > 1: time every k-th step."""
         self._lib.hctr_table_profile(self._h, int(enable))
 
     def phase_times(self, reset=True):
@@ -230,6 +232,12 @@ class Table:
         calls = (ctypes.c_longlong * len(self.PHASES))()
         self._lib.hctr_table_phase_times(self._h, ms, calls, int(reset))
         return {p: (ms[i], calls[i]) for i, p in enumerate(self.PHASES)}
+
+    def timeline(self, max_spans=256):
+        """[(phase, start_ms, end_ms)] of the most recent timed phases, oldest first."""
+        out = (ctypes.c_double * (3 * max_spans))()
+        n = self._lib.hctr_table_timeline(self._h, out, max_spans)
+        return [(self.PHASES[int(out[3 * i])], out[3 * i + 1], out[3 * i + 2]) for i in range(n)]
 
     def exchange_name(self):
         return self._lib.hctr_table_exchange_name(self._h).decode()

@@ -157,7 +157,7 @@ int hctr_table_stats(hctr_table *t, long long out[11]) {
 }
 
 int hctr_table_profile(hctr_table *t, int enable) {
-  t->impl->setProfile(enable != 0);
+  t->impl->setProfile(enable);
   return 0;
 }
 
@@ -165,6 +165,10 @@ int hctr_table_phase_times(hctr_table *t, double ms[HCTR_N_PHASES], long long ca
   static_assert(HCTR_N_PHASES == hetuCTR::kPhCount, "phase list out of sync");
   t->impl->phaseTimes(ms, calls, reset != 0);
   return 0;
+}
+
+int hctr_table_timeline(hctr_table *t, double *out, int max_spans) {
+  return (int)t->impl->timeline(out, max_spans > 0 ? (size_t)max_spans : 0);
 }
 
 int hctr_rendezvous_broadcast(int rank, int nrank, const char *ip, int port, void *data, size_t len,

@@ -305,6 +305,8 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   HCTR_CUDA(cudaSetDevice(device_id_));
   finalizePending();
   batch_open_ = true;
+  profile_ = profile_every_ > 0 && (profile_step_++ % (size_t)profile_every_) == 0;
+  flushOrdering(cur_batch_);  // normally done by push_pull already; two preprocess calls in a row get here
   std::swap(cur_batch_, prev_batch_);
   BatchDesc &cur = cur_batch_, &prev = prev_batch_;
   reserveBatch(cur, std::max<size_t>(batch_size, 1));
@@ -351,8 +353,12 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   if (!cur.ev_order) HCTR_CUDA(cudaEventCreateWithFlags(&cur.ev_order, cudaEventDisableTiming));
   a.side_stream = stream_side_;
   a.fork_event = ev_fork_;
-  a.join_event = cur.ev_order;
-  cur.order_recorded = true;
+  // The ordering kernels are not even enqueued here: push_pull enqueues them after the gradient reduction,
+  // which brings the reduction (it only starts once push_pull is called) several launches forward.
+  a.join_event = nullptr;
+  cur.order_recorded = false;
+  cur.order_pending = true;
+  cur.order_args = a;
   // The push decision for the previous batch goes first: the gradient reduction (on its own stream, started
   // by the next push_pull) only needs this, not the dedupe of the new batch that follows.
 
@@ -407,6 +413,15 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   HCTR_CUDA(cudaStreamSynchronize(stream_main_));
   collectSpans();
   finalizeBatch();
+}
+
+void HetuTable::flushOrdering(BatchDesc &b) {
+  if (!b.order_pending) return;
+  b.order_pending = false;
+  HCTR_CUDA(cudaStreamWaitEvent(stream_side_, ev_fork_, 0));  // recorded after this batch's scatter
+  HCTR_LAUNCH(hctr_dedupe_order(&b.order_args, stream_side_));
+  HCTR_CUDA(cudaEventRecord(b.ev_order, stream_side_));
+  b.order_recorded = true;
 }
 
 // Reads the counts the preprocess pipeline copied to pinned memory into the batch descriptors.
@@ -555,6 +570,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     // everything below reads rows / versions the reduction updates
     HCTR_CUDA(cudaStreamWaitEvent(stream_main_, ev_reduce_, 0));
   }
+  flushOrdering(cur);  // the current batch's run ordering, deferred by preprocess
 
   if (n == 1) {
     // Single rank: every key is owned and stored here; the pull is a local gather.
@@ -899,7 +915,32 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
 // ------------------------------------------------------------------------------------------------
 // Profiling spans
 // ------------------------------------------------------------------------------------------------
-void HetuTable::setProfile(bool on) { profile_ = on; }
+void HetuTable::setProfile(int every) {
+  if (every < 0) every = 0;
+  if (every > 0 && profile_every_ == 0) {
+    HCTR_CUDA(cudaSetDevice(device_id_));
+    if (!ev_epoch_) HCTR_CUDA(cudaEventCreate(&ev_epoch_));
+    HCTR_CUDA(cudaEventRecord(ev_epoch_, stream_main_));
+    timeline_.assign(3 * kTimelineSpans, 0.0);
+    timeline_next_ = timeline_count_ = 0;
+  }
+  profile_every_ = every;
+  profile_step_ = 0;
+  profile_ = every > 0;
+}
+
+size_t HetuTable::timeline(double *out, size_t max_spans) {
+  if (spans_used_) {
+    quiesce();
+    resolveSpans();
+  }
+  const size_t n = std::min(max_spans, timeline_count_);
+  for (size_t i = 0; i < n; i++) {
+    const size_t slot = (timeline_next_ + kTimelineSpans - n + i) % kTimelineSpans;
+    for (int j = 0; j < 3; j++) out[3 * i + j] = timeline_[3 * slot + j];
+  }
+  return n;
+}
 
 int HetuTable::tic(int phase, cudaStream_t st) {
   if (!profile_) return -1;
@@ -921,13 +962,29 @@ void HetuTable::toc(int span, cudaStream_t st) {
   HCTR_CUDA(cudaEventRecord(spans_[span].b, st ? st : stream_main_));
 }
 
-// call only after the stream has been synchronised
+// Called at the synchronisation points of a step.  Reading the event times costs several microseconds of
+// host time per span, so the spans of many steps are left to pile up and are only read when somebody
+// asks for the result (phaseTimes / timeline) or when the pile is large.
 void HetuTable::collectSpans() {
+  if (spans_used_ >= kMaxDeferredSpans) resolveSpans();
+}
+
+// Every recorded span must have completed: call after the streams have drained.
+void HetuTable::resolveSpans() {
   for (size_t i = 0; i < spans_used_; i++) {
     float ms = 0.f;
     if (cudaEventElapsedTime(&ms, spans_[i].a, spans_[i].b) == cudaSuccess) {
       phase_ms_[spans_[i].phase] += ms;
       phase_calls_[spans_[i].phase]++;
+      float t0 = 0.f;
+      if (ev_epoch_ && cudaEventElapsedTime(&t0, ev_epoch_, spans_[i].a) == cudaSuccess) {
+        double *slot = &timeline_[3 * timeline_next_];
+        slot[0] = spans_[i].phase, slot[1] = t0, slot[2] = t0 + ms;
+        timeline_next_ = (timeline_next_ + 1) % kTimelineSpans;
+        if (timeline_count_ < kTimelineSpans) timeline_count_++;
+      } else {
+        cudaGetLastError();
+      }
     } else {
       cudaGetLastError();
     }
@@ -936,6 +993,10 @@ void HetuTable::collectSpans() {
 }
 
 void HetuTable::phaseTimes(double ms[kPhCount], long long calls[kPhCount], bool reset) {
+  if (spans_used_) {
+    quiesce();
+    resolveSpans();
+  }
   for (int i = 0; i < kPhCount; i++) {
     ms[i] = phase_ms_[i];
     calls[i] = phase_calls_[i];
@@ -967,9 +1028,7 @@ long long copy_sizes(const std::vector<size_t> &v, size_t n, void *out) {
 }  // namespace
 
 long long HetuTable::dump(const std::string &what, bool prev, void *out) {
-  HCTR_CUDA(cudaSetDevice(device_id_));
-  finalizePending();
-  HCTR_CUDA(cudaStreamSynchronize(stream_side_));  // run ordering may still be in flight
+  quiesce();  // also enqueues and completes a deferred run ordering
   BatchDesc &b = prev ? prev_batch_ : cur_batch_;
   const size_t B = b.batch_size, U = b.unique_size;
   cudaStream_t s = stream_main_;
@@ -1069,6 +1128,8 @@ void HetuTable::releaseAll() {
   h_pinned_ = nullptr;
   if (h_src_) cudaFreeHost(h_src_);
   h_src_ = nullptr;
+  if (ev_epoch_) cudaEventDestroy(ev_epoch_);
+  ev_epoch_ = nullptr;
   if (ev_fork_) cudaEventDestroy(ev_fork_);
   if (ev_join_) cudaEventDestroy(ev_join_);
   if (ev_keys_) cudaEventDestroy(ev_keys_);

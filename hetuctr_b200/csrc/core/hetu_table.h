@@ -14,6 +14,8 @@
 #include <utility>
 #include <vector>
 
+#include "hctr_kernels.h"
+
 namespace hetuCTR {
 
 class Transport;
@@ -59,6 +61,8 @@ struct BatchDesc {
   bool pending = false;  // sizes not yet read back from the device (single-rank tables defer this)
   cudaEvent_t ev_order = nullptr;  // completion of this batch's run ordering (on the ordering stream)
   bool order_recorded = false;
+  bool order_pending = false;      // the run-ordering kernels of this batch are not enqueued yet
+  hctr_dedupe_args order_args;     // what they will be launched with
   DevBuf keys, idx_map, sorted_pos, uniq, uniq_owner, uniq_row, run_start, meta, pos_row, heavy;
   std::vector<size_t> seg;         // [n+1] first unique of each owner
   std::vector<size_t> query_send;  // [n] unique keys addressed to each owner
@@ -137,8 +141,12 @@ class HetuTable {
   const char *exchangeName() const;
   // Per-phase device time.  While enabled, every phase is bracketed by two events on the table's
   // stream; times are summed when the call that recorded them has drained the stream.
-  void setProfile(bool on);
+  // every = 0: off; 1: every step; k: every k-th step (the timing events cost a few microseconds per phase)
+  void setProfile(int every);
   void phaseTimes(double ms[kPhCount], long long calls[kPhCount], bool reset);
+  // The most recent spans as (phase, start ms, end ms) triples, oldest first; times count from the moment
+  // profiling was enabled.  Returns the number of triples written (at most max_spans).
+  size_t timeline(double *out, size_t max_spans);
   cudaStream_t stream() const { return stream_main_; }
 
  private:
@@ -150,6 +158,7 @@ class HetuTable {
   void releaseAll();
   void finalizeBatch();
   void finalizePending();
+  void flushOrdering(BatchDesc &b);  // enqueues a batch's deferred run ordering
   void quiesce();  // every stream drained, pending batch sizes read back
   void exchangeP2P(embed_t *dst_dev);
   const void *stageIn(const void *ptr, size_t bytes, DevBuf &buf, cudaStream_t s);
@@ -203,9 +212,17 @@ class HetuTable {
   int tic(int phase, cudaStream_t s = nullptr);
   void toc(int span, cudaStream_t s = nullptr);
   void collectSpans();
-  bool profile_ = false;
+  void resolveSpans();
+  static constexpr size_t kMaxDeferredSpans = 1 << 15;
+  bool profile_ = false;   // this step is being timed
+  int profile_every_ = 0;
+  size_t profile_step_ = 0;
   std::vector<Span> spans_;
   size_t spans_used_ = 0;
+  cudaEvent_t ev_epoch_ = nullptr;          // recorded on stream_main_ when profiling is enabled
+  std::vector<double> timeline_;            // ring of (phase, start, end), kTimelineSpans entries
+  size_t timeline_next_ = 0, timeline_count_ = 0;
+  static constexpr size_t kTimelineSpans = 256;
   double phase_ms_[kPhCount] = {};
   long long phase_calls_[kPhCount] = {};
 };

@@ -68,6 +68,7 @@ struct Pinned {
 void HetuTable::quiesce() {
   HCTR_CUDA(cudaSetDevice(device_id_));
   finalizePending();
+  flushOrdering(cur_batch_);
   for (cudaStream_t s : {stream_main_, stream_side_, stream_reduce_, stream_reduce_side_})
     if (s) HCTR_CUDA(cudaStreamSynchronize(s));
 }

@@ -282,13 +282,6 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
   const hctr_dedupe_args a = *ap;
   const size_t n_blocks = (size_t)a.nrank * a.length_pad / HCTR_BLOCK_KEYS;
   const size_t blocks_per_owner = a.length_pad / HCTR_BLOCK_KEYS;
-  static bool attr_set = false;
-  if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(dedupe_order_heavy, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         kHeavyWindowBits / 8);
-    if (e != cudaSuccess) return (int)e;
-    attr_set = true;
-  }
   const unsigned gb = grid_for(a.batch, kThreads);
   dedupe_mark<<<gb, kThreads, 0, s>>>(a);
   // One warp per `group` bitmap blocks; keep the chain of CTAs short (each CTA adds up its predecessors).
@@ -306,12 +299,33 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
   // Run ordering is only needed by the gradient reduction of the NEXT step, not by anything else in this
   // one.  With a second stream the two ordering kernels leave the caller's stream: they start after the
   // scatter (fork_event) and join_event marks their completion; whoever consumes sorted_pos waits on it.
-  cudaStream_t os = s;
-  if (a.side_stream && a.fork_event && a.join_event) {
-    os = (cudaStream_t)a.side_stream;
+  // Without a join_event the caller enqueues them itself, later, with hctr_dedupe_order.
+  if (a.side_stream && a.fork_event) {
     cudaError_t e = cudaEventRecord((cudaEvent_t)a.fork_event, s);
-    if (e == cudaSuccess) e = cudaStreamWaitEvent(os, (cudaEvent_t)a.fork_event, 0);
     if (e != cudaSuccess) return (int)e;
+    count_launches(4);
+    if (!a.join_event) return launch_status();
+    cudaStream_t os = (cudaStream_t)a.side_stream;
+    e = cudaStreamWaitEvent(os, (cudaEvent_t)a.fork_event, 0);
+    if (e != cudaSuccess) return (int)e;
+    const int rc2 = hctr_dedupe_order(ap, a.side_stream);
+    if (rc2) return rc2;
+    e = cudaEventRecord((cudaEvent_t)a.join_event, os);
+    return e != cudaSuccess ? (int)e : launch_status();
+  }
+  count_launches(4);
+  return hctr_dedupe_order(ap, stream);
+}
+
+extern "C" int hctr_dedupe_order(const hctr_dedupe_args *ap, void *stream) {
+  cudaStream_t os = (cudaStream_t)stream;
+  const hctr_dedupe_args a = *ap;
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(dedupe_order_heavy, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         kHeavyWindowBits / 8);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
   }
   {
     size_t ctas = ((a.batch + 31) / 32 * 32 + kThreads - 1) / kThreads;  // one warp per 32 unique keys
@@ -330,10 +344,6 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
     if (per_sm < 1) per_sm = 1;
     dedupe_order_heavy<<<(unsigned)(kSMs * per_sm), 1024, smem, os>>>(a, (u32)wbits);
   }
-  if (os != s) {
-    cudaError_t e = cudaEventRecord((cudaEvent_t)a.join_event, os);
-    if (e != cudaSuccess) return (int)e;
-  }
-  count_launches(6);
+  count_launches(2);
   return launch_status();
 }

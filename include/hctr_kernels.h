@@ -156,7 +156,9 @@ typedef struct hctr_dedupe_args {
    * run-ordering kernels (the only consumers/producers of the final order inside sorted_pos) run on
    * side_stream after the rest of the pipeline, and join_event is recorded there when they are done:
    * the call's stream does NOT wait for them, whoever reads sorted_pos must wait on join_event.
-   * null = everything on the call's stream */
+   * side_stream and fork_event given but join_event null: the ordering kernels are NOT enqueued; fork_event
+   * is recorded when their inputs are ready and the caller enqueues them later with hctr_dedupe_order.
+   * All null = everything on the call's stream */
   void *side_stream;
   void *fork_event;
   void *join_event;
@@ -172,6 +174,12 @@ typedef struct hctr_dedupe_args {
  * = index of the first unique key owned by p (entry nrank = U), and the bitmap scratch is all-zero
  * again.  Keys out of range set HCTR_ERR_KEY_RANGE in meta[HCTR_META_ERR] and get idx_map = -1. */
 int hctr_dedupe_map(const hctr_dedupe_args *a, void *stream);
+
+/* The run-ordering half of the pipeline alone (positions of every unique key's run in ascending batch order
+ * inside sorted_pos), for callers that deferred it: same args as the hctr_dedupe_map call it completes, on a
+ * stream that has waited for that call's fork_event.  Nothing but the next gradient reduction (and a reader
+ * of sorted_pos) needs it. */
+int hctr_dedupe_order(const hctr_dedupe_args *a, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Gradient push decision (previous batch).  Replaces decide_update_kernel + scan,

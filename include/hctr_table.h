@@ -84,13 +84,18 @@ int hctr_table_import(hctr_table *t, const char *path);
  * received_push_rows, queried_keys, returned_rows, received_rows, stored_rows, cached_rows}. */
 int hctr_table_stats(hctr_table *t, long long out[11]);
 
-/* Per-phase device time.  While profiling is enabled each phase of preprocess/push_pull is bracketed by
- * two CUDA events on the table's stream; hctr_table_phase_times returns the accumulated milliseconds and
+/* Per-phase device time.  hctr_table_profile(t, k): k = 0 off, 1 every step, k > 1 every k-th step (the
+ * timing events cost the step a few microseconds per phase, sampling keeps that out of a benchmark).  In a
+ * timed step each phase of preprocess/push_pull is bracketed by two CUDA events on the stream it runs on; hctr_table_phase_times returns the accumulated milliseconds and
  * call counts per phase (and clears them when reset != 0).  Phase order: dedupe, push_decide, reduce,
  * query, exchange, owner_update, stale_gather, refresh, expand. */
 #define HCTR_N_PHASES 9
 int hctr_table_profile(hctr_table *t, int enable);
 int hctr_table_phase_times(hctr_table *t, double ms[HCTR_N_PHASES], long long calls[HCTR_N_PHASES], int reset);
+/* The most recent timed phases (up to 256 are kept) as triples {phase index, start ms, end ms}, oldest first,
+ * in milliseconds since profiling was enabled: shows which phases overlap and where the device idles.
+ * Writes at most max_spans triples to out and returns how many. */
+int hctr_table_timeline(hctr_table *t, double *out, int max_spans);
 
 /* The bootstrap broadcast used when a multi-rank table is constructed, exposed for tests and tools: copies
  * `len` bytes at `data` from rank 0 to every rank over TCP (rank 0 listens on ip:port).  Returns -1 with a
