@@ -90,7 +90,7 @@ def build(force=False, verbose=False):
     psrc = [os.path.join(CSRC, "partition/partition.cc"), os.path.join(CSRC, "partition/module.cc")]
     if force or _stale(pmod, psrc + hdrs):
         import pybind11
-        _run(["g++", *CXX_FLAGS, "-fvisibility=hidden", "-shared", "-I", pybind11.get_include(),
+        _run(["g++", *CXX_FLAGS, "-fopenmp", "-fvisibility=hidden", "-shared", "-I", pybind11.get_include(),
               "-I", sysconfig.get_paths()["include"], *psrc, "-o", pmod], verbose)
     return lib, mod
 

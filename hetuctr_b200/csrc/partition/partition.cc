@@ -28,8 +28,10 @@ int first_argmax(const std::vector<float> &v) {
 }
 
 // splitmix64: the assignment only needs to be uniform and reproducible
-uint64_t next_u64(uint64_t &s) {
-  uint64_t z = (s += 0x9e3779b97f4a7c15ull);
+// i-th value (i = 1, 2, ...) of the splitmix64 stream started at `seed`: the stream's state is seed + i * gamma, so
+// any element can be computed on its own
+uint64_t splitmix_at(uint64_t seed, uint64_t i) {
+  uint64_t z = seed + i * 0x9e3779b97f4a7c15ull;
   z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
   z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
   return z ^ (z >> 31);
@@ -43,20 +45,25 @@ Partitioner::Partitioner(const int *data, int n_data, int n_slot, const float *c
   if (n_part < 1 || n_data < n_part || n_slot < 1 || batch_size < 1)
     throw std::runtime_error("partition: need n_part >= 1, n_data >= n_part, n_slot >= 1, batch_size >= 1");
   const size_t n_edge = (size_t)n_data * n_slot;
-  n_embed_ = 0;
-  for (size_t i = 0; i < n_edge; i++) {
-    if (data[i] < 0) throw std::runtime_error("partition: negative embedding id");
-    n_embed_ = std::max(n_embed_, data[i]);
+  int lowest = 0, highest = 0;
+#pragma omp parallel for reduction(min : lowest) reduction(max : highest) schedule(static)
+  for (long long i = 0; i < (long long)n_edge; i++) {
+    lowest = std::min(lowest, data[i]);
+    highest = std::max(highest, data[i]);
   }
-  n_embed_++;
+  if (lowest < 0) throw std::runtime_error("partition: negative embedding id");
+  n_embed_ = highest + 1;
   data_indices_.assign(data, data + n_edge);
-  // CSR of embedding -> samples (sample ids ascending inside a row)
-  embed_indptr_.assign(n_embed_ + 1, 0);
-  for (size_t i = 0; i < n_edge; i++) embed_indptr_[data[i] + 1]++;
-  for (int e = 0; e < n_embed_; e++) embed_indptr_[e + 1] += embed_indptr_[e];
-  embed_indices_.resize(n_edge);
-  std::vector<int> fill(embed_indptr_.begin(), embed_indptr_.end() - 1);
-  for (size_t i = 0; i < n_edge; i++) embed_indices_[fill[data[i]]++] = (int)(i / n_slot);
+  // occurrences of every embedding over all samples (the reference keeps a CSR of embedding -> samples,
+  // csrc/partition/partition.cc:35-56; only its row lengths and per-part counts are ever needed, and the
+  // latter are maintained incrementally in cnt_part_embed_)
+  degree_.assign(n_embed_, 0);
+  // (integer counts: the parallel loops below give the same result in any order)
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < (long long)n_edge; i++) {
+#pragma omp atomic
+    degree_[data[i]]++;
+  }
 
   // soft_cnt[k]: expected number of batches (scaled) in which a row with k occurrences among a part's
   // samples is needed: 1 - (1 - k/max)^batch, times max/batch; 1 beyond max (partition.cc:58-64)
@@ -74,9 +81,11 @@ Partitioner::Partitioner(const int *data, int n_data, int n_slot, const float *c
 
   res_data_.resize(n_data_);
   res_embed_.resize(n_embed_);
-  uint64_t s = seed;
-  for (int i = 0; i < n_data_; i++) res_data_[i] = (int)(next_u64(s) % (uint64_t)n_part_);
-  for (int i = 0; i < n_embed_; i++) res_embed_[i] = (int)(next_u64(s) % (uint64_t)n_part_);
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < n_data_; i++) res_data_[i] = (int)(splitmix_at(seed, (uint64_t)i + 1) % (uint64_t)n_part_);
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < n_embed_; i++)
+    res_embed_[i] = (int)(splitmix_at(seed, (uint64_t)n_data_ + (uint64_t)i + 1) % (uint64_t)n_part_);
   rebuildCounts();
 }
 
@@ -84,12 +93,16 @@ void Partitioner::rebuildCounts() {
   cnt_data_.assign(n_part_, 0);
   cnt_embed_.assign(n_part_, 0);
   cnt_part_embed_.assign((size_t)n_part_ * n_embed_, 0);
-  for (int i = 0; i < n_data_; i++) {
-    const int p = res_data_[i];
-    cnt_data_[p]++;
-    for (int j = 0; j < n_slot_; j++) cnt_part_embed_[(size_t)p * n_embed_ + data_indices_[(size_t)i * n_slot_ + j]]++;
-  }
+  for (int i = 0; i < n_data_; i++) cnt_data_[res_data_[i]]++;
   for (int e = 0; e < n_embed_; e++) cnt_embed_[res_embed_[e]]++;
+#pragma omp parallel for schedule(static)
+  for (long long i = 0; i < n_data_; i++) {
+    const int p = res_data_[i];
+    for (int j = 0; j < n_slot_; j++) {
+#pragma omp atomic
+      cnt_part_embed_[(size_t)data_indices_[(size_t)i * n_slot_ + j] * n_part_ + p]++;
+    }
+  }
 }
 
 void Partitioner::setResult(const int *data_part, const int *embed_part) {
@@ -106,6 +119,7 @@ void Partitioner::setResult(const int *data_part, const int *embed_part) {
 // part k: every row it uses costs (soft[c+1] - soft[c]) * comm[k][owner] where c is the row's occurrence
 // count in part k without this sample.
 void Partitioner::refineData() {
+  constexpr int kAhead = 6;
   std::vector<float> score(n_part_);
   for (int i = 0; i < n_data_; i++) {
     const int old = res_data_[i];
@@ -114,11 +128,19 @@ void Partitioner::refineData() {
       score[j] = alpha_ * c;
     }
     const int *row = &data_indices_[(size_t)i * n_slot_];
+    // the sweep is a chain of cache misses (two per slot); ask for the lines of a later sample now
+    if (i + kAhead < n_data_) {
+      const int *later = &data_indices_[(size_t)(i + kAhead) * n_slot_];
+      for (int j = 0; j < n_slot_; j++) {
+        __builtin_prefetch(&res_embed_[later[j]], 0, 1);
+        __builtin_prefetch(&cnt_part_embed_[(size_t)later[j] * n_part_], 1, 1);
+      }
+    }
     for (int j = 0; j < n_slot_; j++) {
       const int e = row[j];
       const int owner = res_embed_[e];
       for (int k = 0; k < n_part_; k++) {
-        int use = cnt_part_embed_[(size_t)k * n_embed_ + e];
+        int use = cnt_part_embed_[(size_t)e * n_part_ + k];
         if (k == old) use--;
         score[k] -= (soft_cnt_[use + 1] - soft_cnt_[use]) * comm_[(size_t)k * n_part_ + owner];
       }
@@ -128,8 +150,8 @@ void Partitioner::refineData() {
       cnt_data_[old]--;
       cnt_data_[s]++;
       for (int j = 0; j < n_slot_; j++) {
-        cnt_part_embed_[(size_t)s * n_embed_ + row[j]]++;
-        cnt_part_embed_[(size_t)old * n_embed_ + row[j]]--;
+        cnt_part_embed_[(size_t)row[j] * n_part_ + s]++;
+        cnt_part_embed_[(size_t)row[j] * n_part_ + old]--;
       }
       res_data_[i] = s;
     }
@@ -142,20 +164,21 @@ void Partitioner::refineEmbed() {
   embed_weight_.assign(n_part_, 0.f);
   for (int i = 0; i < n_part_; i++)
     for (int j = 0; j < n_embed_; j++)
-      if (res_embed_[j] != i) embed_weight_[res_embed_[j]] += soft_cnt_[cnt_part_embed_[(size_t)i * n_embed_ + j]];
+      if (res_embed_[j] != i) embed_weight_[res_embed_[j]] += soft_cnt_[cnt_part_embed_[(size_t)j * n_part_ + i]];
   const float scale = float(batch_size_ * n_part_) / n_data_;
   for (int i = 0; i < n_part_; i++) embed_weight_[i] *= scale;
 
   std::vector<float> score(n_part_), cnt(n_part_);
   for (int i = 0; i < n_embed_; i++) {
     const int old = res_embed_[i];
-    std::fill(cnt.begin(), cnt.end(), 0.f);
-    for (int j = embed_indptr_[i]; j < embed_indptr_[i + 1]; j++) cnt[res_data_[embed_indices_[j]]]++;
+    // samples of every part that use row i (the reference recounts them from its CSR; the running counts
+    // hold the same numbers because refine_embed moves no sample)
+    for (int j = 0; j < n_part_; j++) cnt[j] = (float)cnt_part_embed_[(size_t)i * n_part_ + j];
     for (int j = 0; j < n_part_; j++) {
       const int c = old == j ? cnt_embed_[j] - 1 : cnt_embed_[j];
       score[j] = beta_ * c;
     }
-    const int deg = embed_indptr_[i + 1] - embed_indptr_[i];
+    const int deg = degree_[i];
     for (int j = 0; j < n_part_; j++) {
       const float need = soft_cnt_[(size_t)cnt[j]];
       for (int k = 0; k < n_part_; k++) score[k] -= comm_[(size_t)j * n_part_ + k] * need;
@@ -168,7 +191,7 @@ void Partitioner::refineEmbed() {
       cnt_embed_[s]++;
       res_embed_[i] = s;
       for (int j = 0; j < n_part_; j++) {
-        const float w = soft_cnt_[cnt_part_embed_[(size_t)j * n_embed_ + i]] * (batch_size_ * n_part_) / n_data_;
+        const float w = soft_cnt_[cnt_part_embed_[(size_t)i * n_part_ + j]] * (batch_size_ * n_part_) / n_data_;
         if (j != s) embed_weight_[s] += w;
         if (j != old) embed_weight_[old] -= w;
       }
@@ -180,7 +203,7 @@ std::vector<float> Partitioner::communication() const {
   std::vector<float> cost((size_t)n_part_ * n_part_, 0.f);
   for (int i = 0; i < n_part_; i++)
     for (int j = 0; j < n_embed_; j++)
-      cost[(size_t)i * n_part_ + res_embed_[j]] += soft_cnt_[cnt_part_embed_[(size_t)i * n_embed_ + j]];
+      cost[(size_t)i * n_part_ + res_embed_[j]] += soft_cnt_[cnt_part_embed_[(size_t)j * n_part_ + i]];
   const float scale = float(batch_size_ * n_part_) / n_data_;
   for (float &c : cost) c *= scale;
   return cost;
@@ -190,10 +213,10 @@ std::vector<float> Partitioner::priority() const {
   std::vector<float> pr((size_t)n_part_ * n_embed_, 0.f);
   for (int i = 0; i < n_part_; i++)
     for (int j = 0; j < n_embed_; j++) {
-      const int c = cnt_part_embed_[(size_t)i * n_embed_ + j];
+      const int c = cnt_part_embed_[(size_t)j * n_part_ + i];
       if (c == 0) continue;
       const double soft = soft_cnt_[c];
-      const int deg = embed_indptr_[j + 1] - embed_indptr_[j];
+      const int deg = degree_[j];
       pr[(size_t)i * n_embed_ + j] =
           (float)(comm_[(size_t)i * n_part_ + res_embed_[j]] * (soft * soft) * ((1.0 / deg) + (1.0 / c)));
     }

@@ -39,10 +39,10 @@ class Partitioner {
   int n_part_, n_data_, n_slot_, n_embed_, batch_size_;
   float alpha_, beta_;
   std::vector<int> data_indices_;                 // [n_data * n_slot]
-  std::vector<int> embed_indptr_, embed_indices_; // CSR: samples of every embedding
+  std::vector<int> degree_;                       // occurrences of every embedding over all samples
   std::vector<float> soft_cnt_;                   // expected distinct-batch hits for k occurrences
   std::vector<float> comm_;                       // [n_part * n_part]
-  std::vector<int> cnt_part_embed_;               // [n_part * n_embed] occurrences of row j in part i's samples
+  std::vector<int> cnt_part_embed_;               // [n_embed * n_part] occurrences of row j in part i's samples, part-minor
   std::vector<float> embed_weight_;
 };
 
