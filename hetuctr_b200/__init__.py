@@ -158,6 +158,7 @@ class Table:
         if root.shape != (length,):
             raise RuntimeError("root_arr must have `length` entries")
         self.width, self.length, self.nrank, self.rank = width, length, nrank, rank
+        self.device_id = device_id
         self._h = self._lib.hctr_table_create(rank, nrank, device_id, ip.encode(), port, length, width, pull_bound,
                                               push_bound, root.ctypes.data, storage.ctypes.data, storage.size,
                                               init[0], init[1], init[2], learning_rate, verbose)
