@@ -37,6 +37,8 @@ def parse_args():
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-seconds", type=float, default=12.0, help="CPU work in the cpu_baseline sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--timeline", action="store_true",
+                    help="after the run, time three more steps phase by phase and print where they ran (stderr)")
     ap.add_argument("--width", type=int, default=0, help="override the row width (small ncu captures only)")
     ap.add_argument("--rows", type=int, default=0,
                     help="override the table length (small ncu captures only; the line is then not a bench value)")
@@ -206,6 +208,19 @@ def run_ours(args):
     f1.record(stream)
     barrier()
     e2e_ms = f0.elapsed_time(f1)
+
+    if args.timeline:
+        table.profile(1)
+        for i in range(3):
+            step(i)
+        barrier()
+        spans = table.timeline()
+        table.profile(0)
+        if rank == 0 and spans:
+            t_first = spans[0][1]
+            for ph, a, b in spans:
+                print(f"timeline {ph:13s} {1e3 * (a - t_first):8.1f} -> {1e3 * (b - t_first):8.1f} us ({1e3 * (b - a):6.1f})",
+                      file=sys.stderr)
 
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:

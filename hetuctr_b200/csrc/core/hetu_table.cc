@@ -866,22 +866,21 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
 
   // D. staleness, per-requester counts, rows gathered into the requesters' mailboxes
   sp = tic(kPhStaleGather);
-  HCTR_LAUNCH(hctr_p2p_stale_check(c, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
-                                   d_version_.as<int64_t>(), pull_bound_, d_flag32_.as<uint32_t>(), stream_main_));
-  // flat index space: Q = all received queries (device value), at most `slots`
+  // flat index space: Q = all received queries (device value), at most `slots`; flags, slots and the list of
+  // returned queries come out of one launch
   {
     const size_t before = d_chain2_.bytes;
-    d_chain2_.ensure(hctr_scan_chained_scratch_words(slots + 1) * sizeof(uint32_t));
+    d_chain2_.ensure(std::max(hctr_scan_chained_scratch_words(slots + 1), hctr_p2p_scan_scratch_words(slots)) *
+                     sizeof(uint32_t));
     if (d_chain2_.bytes != before)  // epoch tags must not match leftovers of an earlier allocation
       HCTR_CUDA(cudaMemsetAsync(d_chain2_.p, 0, d_chain2_.bytes, stream_main_));
   }
-  HCTR_LAUNCH(hctr_scan_exclusive_u32_chained(d_flag32_.as<uint32_t>(), d_ret_slot_.as<uint32_t>(), slots,
-                                              c->cnt_in + 4 * n, d_chain2_.as<uint32_t>(), nextEpoch(),
-                                              d_err_.as<uint32_t>(), stream_main_));
   d_ret_q_.ensure((slots + 1) * sizeof(uint32_t));
-  HCTR_LAUNCH(hctr_p2p_gather(c, d_flag32_.as<uint32_t>(), d_ret_slot_.as<uint32_t>(), d_ret_q_.as<uint32_t>(),
-                              d_row_of_.as<int32_t>(),
-                              d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_p2p_stale_scan(c, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
+                                  d_version_.as<int64_t>(), pull_bound_, d_ret_slot_.as<uint32_t>(),
+                                  d_ret_q_.as<uint32_t>(), d_chain2_.as<uint32_t>(), nextEpoch(), stream_main_));
+  HCTR_LAUNCH(hctr_p2p_gather_listed(c, d_ret_q_.as<uint32_t>(), d_ret_slot_.as<uint32_t>(), d_row_of_.as<int32_t>(),
+                                     d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
   toc(sp);
   sp = tic(kPhExchange);
   HCTR_LAUNCH(hctr_p2p_signal_wait(c, 1, seq, meta, nullptr, d_ret_slot_.as<uint32_t>(), stream_main_));
@@ -889,13 +888,8 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
 
   // E. requester: flags -> row indices in its own mailbox, cache refresh, expand
   sp = tic(kPhRefresh);
-  HCTR_LAUNCH(hctr_p2p_recv_flags(c, meta, u_max, cur.uniq_owner.as<uint8_t>(), d_flag_r_.as<uint8_t>(),
-                                  d_flag32_.as<uint32_t>(), stream_main_));
-  HCTR_LAUNCH(hctr_scan_exclusive_u32_chained(d_flag32_.as<uint32_t>(), d_recv_slot_.as<uint32_t>(), u_max, nullptr,
-                                              d_chain_.as<uint32_t>(), nextEpoch(), d_err_.as<uint32_t>(),
-                                              stream_main_));
-  HCTR_LAUNCH(hctr_p2p_recv_index(c, meta, u_max, cur.uniq_owner.as<uint8_t>(), d_recv_slot_.as<uint32_t>(),
-                                  d_recv_idx_.as<uint32_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_p2p_recv_scan(c, meta, u_max, cur.uniq_owner.as<uint8_t>(), d_flag_r_.as<uint8_t>(),
+                                 d_recv_idx_.as<uint32_t>(), d_chain_.as<uint32_t>(), nextEpoch(), stream_main_));
   HCTR_LAUNCH(hctr_cache_refresh(u_max, W, d_flag_r_.as<uint8_t>(), d_recv_idx_.as<uint32_t>(),
                                  cur.uniq_row.as<int32_t>(), mine.rval, mine.rver, d_gradient_.as<float>(),
                                  d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));

@@ -268,6 +268,153 @@ __global__ void __launch_bounds__(kThreads) p2p_recv_index(hctr_p2p_ctx c, const
   }
 }
 
+// ---- fused flag + scan kernels ---------------------------------------------------------------------
+// A tile of kTileThreads * kTileItems entries per thread block: every thread computes the flags of its
+// kTileItems consecutive entries, the block scans them and the tile totals are chained across blocks
+// (chained_cta_prefix), so flags, slots and the lists derived from them come out of one launch.
+constexpr int kTileThreads = 1024;
+constexpr int kTileItems = 4;
+constexpr size_t kTile = (size_t)kTileThreads * kTileItems;
+
+// exclusive prefix of `s` over the thread block (kTileThreads threads); *total = sum over the block
+__device__ __forceinline__ u32 tile_exclusive_scan(u32 s, u32 *total) {
+  __shared__ u32 warp_sums[32];
+  __shared__ u32 s_total;
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  u32 incl = s;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const u32 t = __shfl_up_sync(0xffffffffu, incl, d);
+    if (lane >= (unsigned)d) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    const u32 w = warp_sums[lane];
+    u32 wi = w;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const u32 t = __shfl_up_sync(0xffffffffu, wi, d);
+      if (lane >= (unsigned)d) wi += t;
+    }
+    warp_sums[lane] = wi - w;
+    if (lane == 31) s_total = wi;
+  }
+  __syncthreads();
+  *total = s_total;
+  return incl - s + warp_sums[warp];
+}
+
+// Owner: staleness flag of every received query (stored into the requester's mailbox), slot of every
+// returned row (ret_slot, Q + 1 entries, entry Q = number of returned rows) and the list of returned
+// queries (ret_q[slot] = flat query index) in one launch.  Same decisions as p2p_stale_check.
+__global__ void __launch_bounds__(kTileThreads) p2p_stale_scan(hctr_p2p_ctx c, const int32_t *__restrict__ row_of,
+                                                               size_t length, size_t n_cached,
+                                                               const long long *__restrict__ version,
+                                                               long long pull_bound, u32 *__restrict__ ret_slot,
+                                                               u32 *__restrict__ ret_q, u64 *agg, u32 epoch) {
+  __shared__ u32 qstart[1025];
+  for (int i = threadIdx.x; i <= c.nrank; i += kTileThreads) qstart[i] = c.cnt_in[3 * c.nrank + i];
+  __syncthreads();
+  const u32 Q = qstart[c.nrank];
+  const size_t tile_base = (size_t)blockIdx.x * kTile;
+  if (tile_base > Q) return;  // the tile that holds entry Q still runs: it writes the total
+  const hctr_p2p_box me = c.box[c.rank];
+  const size_t base = tile_base + (size_t)threadIdx.x * kTileItems;
+  u32 v[kTileItems];
+  u32 sum = 0;
+#pragma unroll
+  for (int k = 0; k < kTileItems; k++) {
+    const size_t q = base + k;
+    u32 f = 0;
+    if (q < Q) {
+      const unsigned s = source_of(qstart, c.nrank, (u32)q);
+      const u32 j = (u32)q - qstart[s];
+      const size_t slot = (size_t)s * c.cap + j;
+      const long long key = me.qkey[slot];
+      int32_t row = -1;
+      if (key >= 0 && (size_t)key < length) row = row_of[key];
+      if (row < 0 || (size_t)row < n_cached) {
+        atomicOr(c.err, HCTR_ERR_NOT_OWNER);
+      } else {
+        const long long lv = me.qver[slot], gv = version[row];
+        const bool stale = lv == kInvalidVersion || (long long)((u64)lv + (u64)pull_bound) < gv;
+        f = (stale && s != (unsigned)c.rank) ? 1u : 0u;
+      }
+      c.box[s].flag[(size_t)c.rank * c.cap + j] = (uint8_t)f;
+    }
+    v[k] = f;
+    sum += f;
+  }
+  u32 total;
+  u32 ex = tile_exclusive_scan(sum, &total);
+  ex += chained_cta_prefix(agg, epoch, blockIdx.x, total, c.err);
+#pragma unroll
+  for (int k = 0; k < kTileItems; k++) {
+    const size_t q = base + k;
+    if (q <= Q) ret_slot[q] = ex;
+    if (q < Q && v[k]) ret_q[ex] = (u32)q;
+    ex += v[k];
+  }
+}
+
+// Requester: flag of every unique key collected from its mailbox (flags[u], zero for u >= U) and the
+// index of the row returned for it (recv_index[u], in rows relative to box[rank].rval / rver) in one launch.
+// Rows returned by owner p sit in sub-region p in the order of the flagged keys, so the index is
+// p * cap + (flagged keys before u) - (flagged keys of earlier owners); the latter are the per-owner
+// returned-row counts the second exchange delivered (cnt_in[2n + p]).
+__global__ void __launch_bounds__(kTileThreads) p2p_recv_scan(hctr_p2p_ctx c, const u32 *__restrict__ meta, size_t u_max,
+                                                              const uint8_t *__restrict__ uniq_owner,
+                                                              uint8_t *__restrict__ flags,
+                                                              u32 *__restrict__ recv_index, u64 *agg, u32 epoch) {
+  __shared__ u32 owner_base[1025];
+  const size_t U = meta[HCTR_META_UNIQUE];
+  const u32 *seg = meta + HCTR_META_SEG;
+  const size_t tile_base = (size_t)blockIdx.x * kTile;
+  const size_t base = tile_base + (size_t)threadIdx.x * kTileItems;
+  if (tile_base >= U) {  // nothing to rank here (and nobody waits for this block): clear and leave
+#pragma unroll
+    for (int k = 0; k < kTileItems; k++)
+      if (base + k < u_max) flags[base + k] = 0, recv_index[base + k] = 0;
+    return;
+  }
+  if (threadIdx.x == 0) {
+    u32 acc = 0;
+    for (int p = 0; p < c.nrank; p++) {
+      owner_base[p] = acc;
+      acc += c.cnt_in[2 * c.nrank + p];
+    }
+  }
+  __syncthreads();
+  const hctr_p2p_box me = c.box[c.rank];
+  u32 v[kTileItems];
+  unsigned owner[kTileItems];
+  u32 sum = 0;
+#pragma unroll
+  for (int k = 0; k < kTileItems; k++) {
+    const size_t u = base + k;
+    u32 f = 0;
+    owner[k] = 0;
+    if (u < U) {
+      owner[k] = uniq_owner[u];
+      const u32 j = (u32)u - seg[owner[k]];
+      if (j < c.cap) f = me.flag[(size_t)owner[k] * c.cap + j] ? 1u : 0u;
+    }
+    if (u < u_max) flags[u] = (uint8_t)f;
+    v[k] = f;
+    sum += f;
+  }
+  u32 total;
+  u32 ex = tile_exclusive_scan(sum, &total);
+  ex += chained_cta_prefix(agg, epoch, blockIdx.x, total, c.err);
+#pragma unroll
+  for (int k = 0; k < kTileItems; k++) {
+    const size_t u = base + k;
+    if (u < u_max) recv_index[u] = u < U ? owner[k] * (u32)c.cap + (ex - owner_base[owner[k]]) : 0u;
+    ex += v[k];
+  }
+}
+
 static unsigned persistent_grid(size_t items) {
   size_t g = (items + kThreads - 1) / kThreads;
   const size_t cap = (size_t)kSMs * 8;
@@ -357,6 +504,48 @@ extern "C" int hctr_p2p_recv_index(const hctr_p2p_ctx *c, const uint32_t *meta, 
                                    void *stream) {
   p2p_recv_index<<<persistent_grid(u_max), kThreads, 0, (cudaStream_t)stream>>>(*c, meta, u_max, uniq_owner,
                                                                                 recv_slot, recv_index);
+  count_launches(1);
+  return launch_status();
+}
+
+extern "C" size_t hctr_p2p_scan_scratch_words(size_t entries) { return 2 * ((entries + 1 + kTile - 1) / kTile + 1); }
+
+extern "C" int hctr_p2p_stale_scan(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
+                                   const int64_t *version, int64_t pull_bound, uint32_t *ret_slot, uint32_t *ret_q,
+                                   uint32_t *scratch, uint32_t epoch, void *stream) {
+  if (c->nrank > 1024 || epoch == 0) return (int)cudaErrorInvalidValue;
+  const size_t slots = (size_t)c->nrank * c->cap;
+  const unsigned grid = (unsigned)((slots + 1 + kTile - 1) / kTile);
+  p2p_stale_scan<<<grid, kTileThreads, 0, (cudaStream_t)stream>>>(*c, row_of, length, n_cached,
+                                                                  (const long long *)version, pull_bound, ret_slot,
+                                                                  ret_q, reinterpret_cast<u64 *>(scratch), epoch);
+  count_launches(1);
+  return launch_status();
+}
+
+extern "C" int hctr_p2p_gather_listed(const hctr_p2p_ctx *c, const uint32_t *ret_q, const uint32_t *ret_slot,
+                                      const int32_t *row_of, const float *embedding, const int64_t *version,
+                                      void *stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool al = host_aligned16(embedding);
+  const size_t width = c->width;
+#define CALL(L, V)                                                                                         \
+  p2p_gather<L, V><<<(unsigned)((size_t)kSMs * 8), kThreads, 0, st>>>(*c, ret_q, ret_slot, row_of, embedding, \
+                                                                      (const long long *)version)
+  HCTR_DISPATCH_ROWS(width, al, CALL);
+#undef CALL
+  count_launches(1);
+  return launch_status();
+}
+
+extern "C" int hctr_p2p_recv_scan(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const uint8_t *uniq_owner,
+                                  uint8_t *flags, uint32_t *recv_index, uint32_t *scratch, uint32_t epoch,
+                                  void *stream) {
+  if (c->nrank > 1024 || epoch == 0) return (int)cudaErrorInvalidValue;
+  if (u_max == 0) return 0;
+  const unsigned grid = (unsigned)((u_max + kTile - 1) / kTile);
+  p2p_recv_scan<<<grid, kTileThreads, 0, (cudaStream_t)stream>>>(*c, meta, u_max, uniq_owner, flags, recv_index,
+                                                                 reinterpret_cast<u64 *>(scratch), epoch);
   count_launches(1);
   return launch_status();
 }

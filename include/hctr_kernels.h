@@ -298,6 +298,23 @@ int hctr_p2p_recv_flags(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_ma
 int hctr_p2p_recv_index(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const uint8_t *uniq_owner,
                         const uint32_t *recv_slot, uint32_t *recv_index, void *stream);
 
+/* Fused forms of the owner's and the requester's flag + scan steps (one launch each instead of three).
+ * scratch: hctr_p2p_scan_scratch_words(entries) words, 8-byte aligned, zero-initialised ONCE; epoch non-zero and
+ * different from every earlier launch on the same scratch.
+ * hctr_p2p_stale_scan = hctr_p2p_stale_check + exclusive scan + list of returned queries: flag bytes go to the
+ * requesters' mailboxes, ret_slot[q] (Q + 1 entries) is the slot of query q's row among the returned rows,
+ * ret_q[slot] the flat query index of the row in that slot (entries = nrank * cap).
+ * hctr_p2p_gather_listed = the row-moving half of hctr_p2p_gather for a list that already exists.
+ * hctr_p2p_recv_scan = hctr_p2p_recv_flags + exclusive scan + hctr_p2p_recv_index (entries = u_max). */
+size_t hctr_p2p_scan_scratch_words(size_t entries);
+int hctr_p2p_stale_scan(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
+                        const int64_t *version, int64_t pull_bound, uint32_t *ret_slot, uint32_t *ret_q,
+                        uint32_t *scratch, uint32_t epoch, void *stream);
+int hctr_p2p_gather_listed(const hctr_p2p_ctx *c, const uint32_t *ret_q, const uint32_t *ret_slot,
+                           const int32_t *row_of, const float *embedding, const int64_t *version, void *stream);
+int hctr_p2p_recv_scan(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const uint8_t *uniq_owner,
+                       uint8_t *flags, uint32_t *recv_index, uint32_t *scratch, uint32_t epoch, void *stream);
+
 typedef struct hctr_reduce_args {
   size_t n_unique;            /* U of the previous batch (host value) */
   size_t width;               /* W */
