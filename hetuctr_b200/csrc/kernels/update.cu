@@ -2,6 +2,7 @@
 // apply and the packing of pushed rows, and the owner-side apply of received rows.
 #include <cooperative_groups.h>
 
+#include <algorithm>
 #include <cstring>
 
 #include "rowops.cuh"
@@ -431,7 +432,10 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKerne
   typedef RowT<true> R;
   typedef float4 T;
   const unsigned lane = threadIdx.x & 31;
-  const u64 warp = ((u64)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  // The warps of one thread block take shares that lie far apart in the key space: the shares that fall on long
+  // runs (left to the long-run kernel) are empty, and they are neighbours, so consecutive shares per block
+  // would leave whole blocks - and with them whole SMs - without work.
+  const u64 warp = (u64)(threadIdx.x >> 5) * gridDim.x + blockIdx.x;
   const u64 n_warps = ((u64)gridDim.x * kThreads) >> 5;
   const size_t E = a.width / 4;
   const u32 U = (u32)a.n_unique;
@@ -974,11 +978,12 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
       if (e != cudaSuccess) return (int)e;
       if (per_sm < 1) per_sm = 1;
     }
-    // two rounds of equal-cost thread blocks (one, two and four rounds measured the same); small batches get
-    // fewer, not thinner, warps
-    size_t ctas = (size_t)kSMs * per_sm * 2;
-    const size_t enough = (3 * a.n_unique / 48 * 32 + kThreads - 1) / kThreads + 1;
-    if (ctas > enough) ctas = enough;
+    // Equal-cost thread blocks, at most one resident round of them (one, two and three rounds measured the
+    // same; a few blocks left over for another round would double the kernel's duration).  A warp should get
+    // at least ~48 row transfers; every key costs at least 3, so 3U bounds the total from below.
+    const size_t slots = (size_t)kSMs * per_sm;
+    const size_t wanted = (3 * a.n_unique / 48 * 32 + kThreads - 1) / kThreads + 1;
+    const size_t ctas = std::min(wanted, slots);
     kernel<<<(unsigned)ctas, kThreads, smem, s>>>(ka);
   } else if (al && a.width % 4 == 0 && a.width >= 128) {
     size_t ctas = ((a.n_unique + kWideChunk - 1) / kWideChunk * 32 + kThreads - 1) / kThreads;
