@@ -1,6 +1,6 @@
 """Builds the REFERENCE's own implementation as a checker (TEST INFRASTRUCTURE, never shipped).
 
-  python oracle/build_ref.py [--reference /root/reference]
+  python oracle/build_ref.py [--reference DIR]      (DIR = checkout of the reference project)
 
 Compiles the reference's sources where they lie (nothing is copied into this repository) for sm_100a and links
 them with oracle/ref_binding.cu into oracle/_ref/hetuCTR_ref<ext>.so.  The reference's ZMQ rendezvous cannot be
