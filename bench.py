@@ -39,6 +39,11 @@ def parse_args():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--timeline", action="store_true",
                     help="after the run, time three more steps phase by phase and print where they ran (stderr)")
+    ap.add_argument("--layout", default="benchmark", choices=["benchmark", "graph", "random"],
+                    help="benchmark: the reference benchmark's layout (random owners, per-rank batch streams). "
+                         "graph / random: batches drawn from one clustered click log that is laid out by the offline "
+                         "partitioner or dealt at random (the config-5 comparison, N > 1)")
+    ap.add_argument("--log-samples", type=int, default=0, help="click log size for --layout graph/random")
     ap.add_argument("--width", type=int, default=0, help="override the row width (small ncu captures only)")
     ap.add_argument("--rows", type=int, default=0,
                     help="override the table length (small ncu captures only; the line is then not a bench value)")
@@ -95,6 +100,23 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def make_job_workload(cfg, nrank, rank, layout, log_samples):
+    """Batches of one shared clustered click log; owners, caches and the rank of every sample either from the
+    offline partitioner ("graph") or dealt at random ("random")."""
+    from hetuctr_b200.workloads import partitioned_job, random_job
+    c = dict(CONFIGS[cfg])
+    log_samples = log_samples or 64 * c["samples"] * nrank
+    cache_rows = max(int(c["rows"] * 0.02), 1)
+    if layout == "graph":
+        root, storage, mine, data = partitioned_job(cfg, nrank, log_samples, cache_rows,
+                                                    log=(lambda m: print(m, file=sys.stderr)) if rank == 0 else None)
+    else:
+        root, storage, mine, data = random_job(cfg, nrank, log_samples, cache_rows)
+    rng = np.random.RandomState(1000 * int(cfg[3]) + rank)
+    batches = [data[rng.choice(mine[rank], c["samples"])].reshape(-1).astype(np.int64) for _ in range(N_BATCHES)]
+    return c, root, storage[rank], batches
+
+
 def make_workload(cfg, nrank, rank, rows=0, width=0):
     c = dict(CONFIGS[cfg])
     if rows:
@@ -135,7 +157,10 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    c, root, storage, batches = make_workload(args.config, world, rank, args.rows, args.width)
+    if args.layout == "benchmark":
+        c, root, storage, batches = make_workload(args.config, world, rank, args.rows, args.width)
+    else:
+        c, root, storage, batches = make_job_workload(args.config, world, rank, args.layout, args.log_samples)
     W, B = c["width"], c["samples"] * c["fields"]
     addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
     port = int(os.environ.get("MASTER_PORT", 29500)) + 101
@@ -256,7 +281,10 @@ def run_ours(args):
                        "unique_per_gpu_per_step": stats["unique"], "key_distribution":
                        "uniform" if c["alpha"] is None else f"zipf({c['alpha']}) per field, {c['fields']} fields",
                        "cache_fraction": c["cache"] if world > 1 else 0.0, "pull_bound": c["pull_bound"],
-                       "push_bound": c["push_bound"], "lr": c["lr"], "partition": f"random owners x{world}",
+                       "push_bound": c["push_bound"], "lr": c["lr"], "partition": {"benchmark": f"random owners x{world}",
+                                     "graph": f"offline partitioner (5 rounds) x{world}, clustered click log",
+                                     "random": f"random owners x{world}, clustered click log"}[args.layout],
+                       "rows_moved_per_gpu_per_step": stats["pushed_rows"] + stats["received_rows"],
                        "l2": f"{N_BATCHES} rotating batches; >= {2 * B * 4 * W / 1e6:.0f} MB streamed per step exceeds the 126 MB L2"
                        if 2 * B * 4 * W > 126e6 else f"{N_BATCHES} rotating batches (per-step data smaller than L2)",
                        "transport": table.exchange_name()},
@@ -359,7 +387,10 @@ def run_reference(args):
                 "e2e": {"value": cb["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
                 "total_s": time.perf_counter() - t0}
 
-    c, root, storage, batches = make_workload(args.config, world, rank, args.rows, args.width)
+    if args.layout == "benchmark":
+        c, root, storage, batches = make_workload(args.config, world, rank, args.rows, args.width)
+    else:
+        c, root, storage, batches = make_job_workload(args.config, world, rank, args.layout, args.log_samples)
     W = c["width"]
     addr = os.environ.get("MASTER_ADDR", "127.0.0.1")
     port = int(os.environ.get("MASTER_PORT", 29500)) + 203

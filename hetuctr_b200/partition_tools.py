@@ -45,9 +45,11 @@ def direct_partition(data, nparts, ngpus, batch_size, rerun, seed=0, log=None):
         mine = idx_partition == i
         pr = priority[i].copy()
         pr[mine] = -1  # rows the rank owns need no cache slot
-        # descending priority, row id ascending among equals (the reference's argsort leaves ties unordered)
-        order = np.lexsort((np.arange(pr.size), -pr))
-        out[str(i)] = order[: pr.size - int(mine.sum())]
+        # descending priority, row id ascending among equals (the reference's argsort leaves ties unordered).
+        # Only rows some sample of the rank uses have a priority; the rest follow in id order without sorting.
+        used = np.flatnonzero(pr > 0)
+        used = used[np.lexsort((used, -pr[used]))]
+        out[str(i)] = np.concatenate([used, np.flatnonzero(pr == 0)])
     return out
 
 

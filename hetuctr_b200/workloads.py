@@ -108,3 +108,65 @@ def storage_with_cache(root, rank, sampler, cache_rows):
     prob = np.concatenate(cand_p)
     order = np.argsort(-prob, kind="stable")[:cache_rows]
     return np.concatenate([owned, np.sort(keys[order])])
+
+
+class ClusteredSampler(KeySampler):
+    """Click log with co-occurrence structure (config 5): every sample belongs to one of `clusters` seeded groups.
+    In the large fields a sample draws, with probability `affinity`, from its group's own slice of the field's
+    popularity ranking (the ranks congruent to the group id modulo `clusters`, power-law inside the slice) and
+    otherwise from the whole field; small fields (fewer than 20 ranks per group) are always drawn globally.
+    Samples of one group therefore share most of their rows, which is what a graph partitioner can exploit."""
+
+    def __init__(self, rows, fields, alpha, ratio, clusters=1000, affinity=0.8, perm_seed=7):
+        super().__init__(rows, fields, alpha, ratio, perm_seed)
+        self.clusters, self.affinity = clusters, affinity
+        self._slice_cdf = {}
+        for f, v in enumerate(self.vocab):
+            per = int(v) // clusters
+            if per >= 20:
+                w = np.arange(1, per + 1, dtype=np.float64) ** (-(alpha or 1.0))
+                c = np.cumsum(w)
+                self._slice_cdf[f] = c / c[-1]
+
+    def log(self, samples, rng):
+        """[samples, fields] int64 keys and the group of every sample."""
+        group = rng.randint(self.clusters, size=samples)
+        out = self.batch(samples, rng).reshape(samples, self.fields)  # global draws everywhere first
+        for f, cdf in self._slice_cdf.items():
+            own = rng.random_sample(samples) < self.affinity
+            local = np.minimum(np.searchsorted(cdf, rng.random_sample(samples), side="left"), len(cdf) - 1)
+            rank = local * self.clusters + group
+            out[:, f] = np.where(own, self.key_of_rank(f, rank), out[:, f])
+        return out, group
+
+
+def partitioned_job(cfg, nrank, log_samples, cache_rows, seed=0, rounds=5, log=None):
+    """Config-5 style job laid out by the offline partitioner: returns (root_arr, [storage_arr per rank],
+    [sample indices per rank], click log).  Deterministic, so every rank of a job can compute it on its own."""
+    from . import partition_tools as pt
+    c = CONFIGS[cfg]
+    sampler = ClusteredSampler(c["rows"], c["fields"], c["alpha"], c["ratio"])
+    data, _ = sampler.log(log_samples, np.random.RandomState(1000 * int(cfg[3]) + 77))
+    part = pt.direct_partition(data.astype(np.int32), nrank, nrank, c["samples"] * nrank, rounds, seed=seed, log=log)
+    arrays = [pt.table_arrays(part, r, cache_rows, length=c["rows"]) for r in range(nrank)]
+    mine = [np.where(part["data_partition"] == r)[0] for r in range(nrank)]
+    return arrays[0][0], [a[1] for a in arrays], mine, data
+
+
+def random_job(cfg, nrank, log_samples, cache_rows):
+    """The same click log without the partitioner: random owners (the reference benchmark's choice), samples
+    dealt to ranks regardless of content, every rank caches the globally most frequent rows of the log."""
+    c = CONFIGS[cfg]
+    sampler = ClusteredSampler(c["rows"], c["fields"], c["alpha"], c["ratio"])
+    data, _ = sampler.log(log_samples, np.random.RandomState(1000 * int(cfg[3]) + 77))
+    root = random_owners(c["rows"], nrank)
+    freq = np.bincount(data.reshape(-1), minlength=c["rows"])
+    order = np.argsort(-freq, kind="stable")
+    storage = []
+    for r in range(nrank):
+        owned = np.where(root == r)[0].astype(np.int64)
+        cand = order[root[order] != r][:cache_rows]
+        cand = cand[freq[cand] > 0]
+        storage.append(np.sort(np.concatenate([owned, cand.astype(np.int64)])))
+    mine = [np.arange(r, log_samples, nrank) for r in range(nrank)]
+    return root, storage, mine, data

@@ -136,3 +136,29 @@ def test_glue_arrays(tmp_path):
              "-o", str(tmp_path / "p.npz")])
     z = np.load(tmp_path / "p.npz")
     assert sorted(z.files) == sorted(["embed_partition", "data_partition", "0", "1", "2", "3"])
+
+
+def test_clustered_job_layouts():
+    """The config-5 style job builders: same click log for both layouts, the partitioned one needs far fewer
+    remote rows per batch than random owners with samples dealt regardless of content."""
+    from hetuctr_b200 import workloads as w
+    w.CONFIGS["cfg5_tiny"] = dict(w.CONFIGS["cfg5_sweep"], rows=400_000, samples=512)
+    try:
+        root_g, storage_g, mine_g, data_g = w.partitioned_job("cfg5_tiny", 4, 40_000, 4000)
+        root_r, storage_r, mine_r, data_r = w.random_job("cfg5_tiny", 4, 40_000, 4000)
+    finally:
+        del w.CONFIGS["cfg5_tiny"]
+    assert np.array_equal(data_g, data_r) and data_g.shape == (40_000, 26)
+    assert data_g.min() >= 0 and data_g.max() < 400_000
+    for root, storage, mine in ((root_g, storage_g, mine_g), (root_r, storage_r, mine_r)):
+        assert root.dtype == np.uint8 and root.size == 400_000 and root.max() == 3
+        assert sorted(np.concatenate(mine).tolist()) == list(range(40_000))  # every sample on exactly one rank
+        for r in range(4):
+            assert (np.diff(storage[r]) > 0).all()
+            assert np.isin(np.where(root == r)[0], storage[r]).all()
+
+    def remote_rows(root, mine):
+        rng = np.random.RandomState(0)
+        return sum(int((root[np.unique(data_g[rng.choice(mine[r], 512)])] != r).sum()) for r in range(4))
+
+    assert remote_rows(root_g, mine_g) < 0.8 * remote_rows(root_r, mine_r)
