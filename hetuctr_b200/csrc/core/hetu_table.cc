@@ -316,9 +316,24 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   const int n = nrank_;
   const size_t meta_words = HCTR_META_WORDS + n + 1;
 
-  HCTR_CUDA(cudaMemcpyAsync(cur.keys.p, data_ptr, sizeof(index_t) * batch_size, cudaMemcpyDefault, stream_main_));
-  HCTR_CUDA(cudaEventRecord(ev_keys_, stream_main_));
-  HCTR_CUDA(cudaMemsetAsync(cur.meta.p, 0, meta_words * sizeof(uint32_t), stream_main_));
+  bool keys_on_device = false;
+  if (batch_size > 0) {
+    cudaPointerAttributes attr;
+    if (cudaPointerGetAttributes(&attr, data_ptr) == cudaSuccess)
+      keys_on_device = attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged;
+    else
+      cudaGetLastError();
+  }
+  if (keys_on_device) {
+    // one launch: private copy of the keys + cleared meta words
+    HCTR_LAUNCH(hctr_ingest_keys(reinterpret_cast<const int64_t *>(data_ptr), cur.keys.as<int64_t>(), batch_size, cur.meta.as<uint32_t>(),
+                                 (unsigned)meta_words, stream_main_));
+    HCTR_CUDA(cudaEventRecord(ev_keys_, stream_main_));
+  } else {
+    HCTR_CUDA(cudaMemcpyAsync(cur.keys.p, data_ptr, sizeof(index_t) * batch_size, cudaMemcpyDefault, stream_main_));
+    HCTR_CUDA(cudaEventRecord(ev_keys_, stream_main_));
+    HCTR_CUDA(cudaMemsetAsync(cur.meta.p, 0, meta_words * sizeof(uint32_t), stream_main_));
+  }
 
   hctr_dedupe_args a;
   a.keys = cur.keys.as<int64_t>();

@@ -273,9 +273,27 @@ __global__ void __launch_bounds__(1024) dedupe_order_heavy(hctr_dedupe_args a, u
   }
 }
 
+// Private copy of a device-resident key batch + cleared meta words in one launch (one device operation
+// in front of the pipeline instead of a copy and a memset).
+__global__ void __launch_bounds__(kThreads) ingest_keys(const long long *__restrict__ src, long long *__restrict__ dst,
+                                                        size_t n, u32 *__restrict__ meta, unsigned meta_words) {
+  const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i < meta_words) meta[i] = 0;
+  if (i < n) dst[i] = src[i];
+}
+
 }  // namespace hctr
 
 using namespace hctr;
+
+extern "C" int hctr_ingest_keys(const int64_t *src, int64_t *dst, size_t n, uint32_t *meta, unsigned meta_words,
+                                void *stream) {
+  const size_t items = n > meta_words ? n : meta_words;
+  ingest_keys<<<grid_for(items ? items : 1, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+      (const long long *)src, (long long *)dst, n, meta, meta_words);
+  count_launches(1);
+  return launch_status();
+}
 
 extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
   cudaStream_t s = (cudaStream_t)stream;

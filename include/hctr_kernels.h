@@ -175,6 +175,10 @@ typedef struct hctr_dedupe_args {
  * again.  Keys out of range set HCTR_ERR_KEY_RANGE in meta[HCTR_META_ERR] and get idx_map = -1. */
 int hctr_dedupe_map(const hctr_dedupe_args *a, void *stream);
 
+/* Front of the pipeline for keys that already live in device memory: dst[0..n) = src[0..n) (the table's private
+ * copy, so that the caller may reuse its buffer) and meta[0..meta_words) = 0, in one launch. */
+int hctr_ingest_keys(const int64_t *src, int64_t *dst, size_t n, uint32_t *meta, unsigned meta_words, void *stream);
+
 /* The run-ordering half of the pipeline alone (positions of every unique key's run in ascending batch order
  * inside sorted_pos), for callers that deferred it: same args as the hctr_dedupe_map call it completes, on a
  * stream that has waited for that call's fork_event.  Nothing but the next gradient reduction (and a reader
