@@ -590,8 +590,8 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   if (n == 1) {
     // Single rank: every key is owned and stored here; the pull is a local gather.
     int sp = tic(kPhExpand);
-    HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
-                                 nullptr, d_embedding_.as<float>(), dst_dev, stream_main_));
+    HCTR_LAUNCH(hctr_expand_rows_bulk(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
+                                 nullptr, d_embedding_.as<float>(), dst_dev, d_err_.as<uint32_t>() + 8, stream_main_));
     toc(sp);
   } else if (use_p2p_) {
     exchangeP2P(dst_dev);
@@ -767,9 +767,9 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
                                    stream_main_));
     toc(sp);
     sp = tic(kPhExpand);
-    HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
+    HCTR_LAUNCH(hctr_expand_rows_bulk(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
                                  d_recv_slot_.as<uint32_t>(), d_rval_r_.as<float>(), d_embedding_.as<float>(), dst_dev,
-                                 stream_main_));
+                                 d_err_.as<uint32_t>() + 8, stream_main_));
     toc(sp);
     if (*h_err) {
       HCTR_CUDA(cudaStreamSynchronize(stream_main_));
@@ -779,8 +779,14 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
 
   if (dst_staged)
     HCTR_CUDA(cudaMemcpyAsync(dst, dst_dev, cur.batch_size * W * sizeof(embed_t), cudaMemcpyDeviceToHost, stream_main_));
+  uint32_t *h_expand_err = h_pinned_ + h_pinned_words_ - 1;  // bounded waits of the expand kernel
+  HCTR_CUDA(cudaMemcpyAsync(h_expand_err, d_err_.as<uint32_t>() + 8, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
   HCTR_CUDA(cudaStreamSynchronize(stream_main_));
   collectSpans();
+  if (*h_expand_err) {
+    HCTR_CUDA(cudaMemsetAsync(d_err_.as<uint32_t>() + 8, 0, sizeof(uint32_t), stream_main_));
+    throw std::runtime_error("push_pull: the row expansion gave up waiting for a bulk copy");
+  }
   if (cur.pending) {
     finalizeBatch();
     stats_.unique = cur.unique_size;
@@ -910,8 +916,8 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
                                  d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
   toc(sp);
   sp = tic(kPhExpand);
-  HCTR_LAUNCH(hctr_expand_rows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
-                               d_recv_idx_.as<uint32_t>(), mine.rval, d_embedding_.as<float>(), dst_dev, stream_main_));
+  HCTR_LAUNCH(hctr_expand_rows_bulk(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
+                               d_recv_idx_.as<uint32_t>(), mine.rval, d_embedding_.as<float>(), dst_dev, d_err_.as<uint32_t>() + 8, stream_main_));
   toc(sp);
 
   // counts and the error word come back with the step's final synchronisation

@@ -1,5 +1,8 @@
 // Pull side of a step: query versions, owner-side staleness check + row gather, requester-side cache
 // refresh and the final expansion of unique rows to batch order.
+#include <cstdlib>
+#include <string>
+
 #include "rowops.cuh"
 
 namespace hctr {
@@ -159,6 +162,128 @@ __global__ void __launch_bounds__(kThreads) expand_rows(size_t batch, size_t wid
   }
 }
 
+
+// ---- expand through the bulk-copy engine ---------------------------------------------------------------
+// Each lane moves whole rows with two asynchronous bulk copies (cp.async.bulk): table (or receive-buffer) row ->
+// shared memory, completion counted on the warp's mbarrier, then shared memory -> dst.  A warp owns two buffers
+// of `rows_per_round` row slots and loads round r+1 while round r is being stored, so tens of row transfers per
+// warp are in flight without occupying registers or issue slots.  Waits on the mbarrier are bounded; when one
+// runs out the kernel records HCTR_ERR_TIMEOUT, drains its own copies and returns.
+constexpr int kBulkWarps = 4;
+constexpr unsigned kBulkBufBytes = 8192;  // per warp and buffer
+
+__device__ __forceinline__ unsigned smem_u32(const void *p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+  for (int tries = 0; tries < (1 << 22); tries++) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+
+__global__ void __launch_bounds__(kBulkWarps * 32) expand_rows_bulk(size_t batch, unsigned row_bytes,
+                                                                    unsigned rows_per_round,
+                                                                    const int32_t *__restrict__ pos_row,
+                                                                    const int32_t *__restrict__ idx_map,
+                                                                    const u32 *__restrict__ recv_slot,
+                                                                    const float *__restrict__ recv_val,
+                                                                    const float *__restrict__ embedding,
+                                                                    float *__restrict__ dst, u32 *__restrict__ err) {
+  extern __shared__ __align__(128) unsigned char bulk_smem[];
+  __shared__ __align__(8) unsigned long long bars[kBulkWarps][2];
+  const unsigned lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  unsigned char *my_buf = bulk_smem + (size_t)warp * 2 * kBulkBufBytes;
+  const unsigned bar0 = smem_u32(&bars[warp][0]), bar1 = smem_u32(&bars[warp][1]);
+  if (lane == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 32;" ::"r"(bar0) : "memory");
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 32;" ::"r"(bar1) : "memory");
+  }
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  __syncwarp();
+
+  const size_t n_warps = (size_t)gridDim.x * kBulkWarps;
+  const size_t gwarp = (size_t)blockIdx.x * kBulkWarps + warp;
+  const size_t stride = n_warps * rows_per_round;
+  const bool active = lane < rows_per_round;
+  const size_t row_elems = row_bytes / sizeof(float);
+
+  // issue the loads of the round that starts at position i0 into buffer b (all lanes arrive on its barrier)
+  auto load_round = [&](size_t i0, unsigned b) {
+    const size_t i = i0 + lane;
+    const float *src = nullptr;
+    bool zero_fill = false;
+    if (active && i < batch) {
+      const int32_t row = pos_row[i];
+      if (row >= 0) {
+        src = embedding + (size_t)row * row_elems;
+      } else {
+        const int32_t u = idx_map[i];  // < 0: key was out of range (the host reports it); write zeros
+        if (u >= 0 && recv_slot) src = recv_val + (size_t)recv_slot[u] * row_elems;
+        else zero_fill = true;
+      }
+    }
+    unsigned char *slot = my_buf + (size_t)b * kBulkBufBytes + (size_t)lane * row_bytes;
+    const unsigned bar = b ? bar1 : bar0;
+    if (src) {
+      asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(row_bytes) : "memory");
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                       smem_u32(slot)),
+                   "l"(src), "r"(row_bytes), "r"(bar)
+                   : "memory");
+    } else {
+      if (zero_fill) {
+        for (unsigned o = 0; o < row_bytes; o += 16) *reinterpret_cast<float4 *>(slot + o) = make_float4(0.f, 0.f, 0.f, 0.f);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the bulk store
+      }
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+    }
+  };
+
+  size_t i0 = gwarp * rows_per_round;
+  unsigned parity0 = 0, parity1 = 0, b = 0;
+  bool failed = false;
+  if (i0 < batch) load_round(i0, 0);
+  for (; i0 < batch; i0 += stride, b ^= 1) {
+    const size_t next = i0 + stride;
+    if (next < batch) {
+      // the other buffer was the source of the stores of the previous round: they must have read it
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+      __syncwarp();
+      load_round(next, b ^ 1);
+    }
+    const bool ok = mbar_wait(b ? bar1 : bar0, b ? parity1 : parity0);
+    if (b) parity1 ^= 1;
+    else parity0 ^= 1;
+    if (!__all_sync(0xffffffffu, ok)) {
+      failed = true;
+      break;
+    }
+    const size_t i = i0 + lane;
+    if (active && i < batch) {
+      const unsigned char *slot = my_buf + (size_t)b * kBulkBufBytes + (size_t)lane * row_bytes;
+      asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst + i * row_elems),
+                   "r"(smem_u32(slot)), "r"(row_bytes)
+                   : "memory");
+    }
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  }
+  asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+  if (failed) {
+    if (lane == 0) atomicOr(err, HCTR_ERR_TIMEOUT);
+    // loads of the round issued last may still be in flight into this block's shared memory: give them a bounded
+    // chance to land before the block (and its shared memory) goes away
+    mbar_wait(b ? bar0 : bar1, b ? parity0 : parity1);
+  }
+}
+
 }  // namespace hctr
 
 using namespace hctr;
@@ -234,6 +359,35 @@ extern "C" int hctr_cache_refresh(size_t n_unique, size_t width, const uint8_t *
       embedding, (long long *)version)
   HCTR_DISPATCH_ROWS(width, al, CALL);
 #undef CALL
+  count_launches(1);
+  return launch_status();
+}
+
+extern "C" int hctr_expand_rows_bulk(size_t batch, size_t width, const int32_t *pos_row, const int32_t *idx_map,
+                                     const uint32_t *recv_slot, const float *recv_val, const float *embedding,
+                                     float *dst, uint32_t *err, void *stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (batch == 0) return 0;
+  const size_t row_bytes = width * sizeof(float);
+  const bool al = host_aligned16(recv_val) && host_aligned16(embedding) && host_aligned16(dst);
+  static const bool opted_in = getenv("HCTR_EXPAND") && std::string(getenv("HCTR_EXPAND")) == "bulk";
+  if (!opted_in || !al || width % 4 != 0 || row_bytes < 128 || row_bytes > kBulkBufBytes / 2 || err == nullptr)
+    return hctr_expand_rows(batch, width, pos_row, idx_map, recv_slot, recv_val, embedding, dst, stream);
+  unsigned rows_per_round = (unsigned)(kBulkBufBytes / row_bytes);
+  if (rows_per_round > 32) rows_per_round = 32;
+  const size_t smem = (size_t)kBulkWarps * 2 * kBulkBufBytes;  // 64 KB
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(expand_rows_bulk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  const size_t rounds = (batch + rows_per_round - 1) / rows_per_round;
+  size_t ctas = (rounds + kBulkWarps - 1) / kBulkWarps;
+  const size_t cap = (size_t)kSMs * 3;  // 3 blocks of 64 KB per SM
+  if (ctas > cap) ctas = cap;
+  expand_rows_bulk<<<(unsigned)ctas, kBulkWarps * 32, smem, s>>>(batch, (unsigned)row_bytes, rows_per_round, pos_row,
+                                                                idx_map, recv_slot, recv_val, embedding, dst, err);
   count_launches(1);
   return launch_status();
 }

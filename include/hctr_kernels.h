@@ -429,6 +429,13 @@ int hctr_expand_rows(size_t batch, size_t width, const int32_t *pos_row, const i
                      const uint32_t *recv_slot, const float *recv_val, const float *embedding,
                      float *dst, void *stream);
 
+/* Same result through the bulk-copy engine (cp.async.bulk row -> shared memory -> dst, double-buffered per warp,
+ * mbarrier completion with bounded waits: a wait that runs out sets HCTR_ERR_TIMEOUT in *err).  Needs 16-byte
+ * aligned buffers, width % 4 == 0 and rows of at most 4 KB; anything else goes to hctr_expand_rows. */
+int hctr_expand_rows_bulk(size_t batch, size_t width, const int32_t *pos_row, const int32_t *idx_map,
+                          const uint32_t *recv_slot, const float *recv_val, const float *embedding, float *dst,
+                          uint32_t *err, void *stream);
+
 #ifdef __cplusplus
 }
 #endif
