@@ -30,7 +30,7 @@ N_BATCHES = 6  # distinct pre-generated batches / gradient buffers, cycled
 def parse_args():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=3000)
     ap.add_argument("--warmup", type=int, default=50)
     ap.add_argument("--config", default="cfg2_hybrid", choices=sorted(CONFIGS))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
