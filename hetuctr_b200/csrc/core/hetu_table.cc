@@ -76,6 +76,12 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
   HCTR_CHECK(device_id >= 0 && device_id < num_gpus, "InCorrect device number.");
   HCTR_CUDA(cudaSetDevice(device_id_));
   {
+    const char *env = std::getenv("HCTR_EXPAND");
+    const std::string mode = env ? env : "default";
+    HCTR_CHECK(mode == "default" || mode == "bulk", "HCTR_EXPAND must be default or bulk");
+    expand_bulk_ = mode == "bulk";
+  }
+  {
     // stream_main_ carries many short, latency-bound kernels; it gets the highest priority so that their
     // CTAs are placed ahead of the bulk gradient-reduction CTAs that run concurrently on stream_reduce_
     int lo = 0, hi = 0;
@@ -430,6 +436,15 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   finalizeBatch();
 }
 
+// The row expansion: the register kernel, or (HCTR_EXPAND=bulk) the bulk-copy engine variant.
+int HetuTable::expandRows(size_t batch, size_t width, const int32_t *pos_row, const int32_t *idx_map,
+                          const uint32_t *recv_slot, const float *recv_val, const float *embedding, float *dst,
+                          uint32_t *err, cudaStream_t stream) {
+  if (expand_bulk_)
+    return hctr_expand_rows_bulk(batch, width, pos_row, idx_map, recv_slot, recv_val, embedding, dst, err, stream);
+  return hctr_expand_rows(batch, width, pos_row, idx_map, recv_slot, recv_val, embedding, dst, stream);
+}
+
 void HetuTable::flushOrdering(BatchDesc &b) {
   if (!b.order_pending) return;
   b.order_pending = false;
@@ -590,7 +605,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   if (n == 1) {
     // Single rank: every key is owned and stored here; the pull is a local gather.
     int sp = tic(kPhExpand);
-    HCTR_LAUNCH(hctr_expand_rows_bulk(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
+    HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
                                  nullptr, d_embedding_.as<float>(), dst_dev, d_err_.as<uint32_t>() + 8, stream_main_));
     toc(sp);
   } else if (use_p2p_) {
@@ -767,7 +782,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
                                    stream_main_));
     toc(sp);
     sp = tic(kPhExpand);
-    HCTR_LAUNCH(hctr_expand_rows_bulk(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
+    HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
                                  d_recv_slot_.as<uint32_t>(), d_rval_r_.as<float>(), d_embedding_.as<float>(), dst_dev,
                                  d_err_.as<uint32_t>() + 8, stream_main_));
     toc(sp);
@@ -916,7 +931,7 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
                                  d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
   toc(sp);
   sp = tic(kPhExpand);
-  HCTR_LAUNCH(hctr_expand_rows_bulk(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
+  HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
                                d_recv_idx_.as<uint32_t>(), mine.rval, d_embedding_.as<float>(), dst_dev, d_err_.as<uint32_t>() + 8, stream_main_));
   toc(sp);
 

@@ -158,6 +158,8 @@ class HetuTable {
   void releaseAll();
   void finalizeBatch();
   void finalizePending();
+  int expandRows(size_t batch, size_t width, const int32_t *pos_row, const int32_t *idx_map, const uint32_t *recv_slot,
+                 const float *recv_val, const float *embedding, float *dst, uint32_t *err, cudaStream_t stream);
   void flushOrdering(BatchDesc &b);  // enqueues a batch's deferred run ordering
   void quiesce();  // every stream drained, pending batch sizes read back
   void exchangeP2P(embed_t *dst_dev);
@@ -176,6 +178,7 @@ class HetuTable {
   std::unique_ptr<P2PMailbox> p2p_;  // device-driven exchange (one process per GPU, peer access); else NCCL groups
   bool use_p2p_ = false;
   bool p2p_counts_pending_ = false;
+  bool expand_bulk_ = false;         // HCTR_EXPAND=bulk
   bool batch_open_ = false;          // preprocess done, push_pull not yet
   bool prev_push_valid_ = false;     // d_push_count_/d_push_base_ describe prev_batch_
 

@@ -1,8 +1,5 @@
 // Pull side of a step: query versions, owner-side staleness check + row gather, requester-side cache
 // refresh and the final expansion of unique rows to batch order.
-#include <cstdlib>
-#include <string>
-
 #include "rowops.cuh"
 
 namespace hctr {
@@ -370,8 +367,7 @@ extern "C" int hctr_expand_rows_bulk(size_t batch, size_t width, const int32_t *
   if (batch == 0) return 0;
   const size_t row_bytes = width * sizeof(float);
   const bool al = host_aligned16(recv_val) && host_aligned16(embedding) && host_aligned16(dst);
-  static const bool opted_in = getenv("HCTR_EXPAND") && std::string(getenv("HCTR_EXPAND")) == "bulk";
-  if (!opted_in || !al || width % 4 != 0 || row_bytes < 128 || row_bytes > kBulkBufBytes / 2 || err == nullptr)
+  if (!al || width % 4 != 0 || row_bytes < 128 || row_bytes > kBulkBufBytes / 2 || err == nullptr)
     return hctr_expand_rows(batch, width, pos_row, idx_map, recv_slot, recv_val, embedding, dst, stream);
   unsigned rows_per_round = (unsigned)(kBulkBufBytes / row_bytes);
   if (rows_per_round > 32) rows_per_round = 32;

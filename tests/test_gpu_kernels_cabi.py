@@ -88,3 +88,93 @@ def test_dedupe_launcher_standalone(nrank):
         assert int(meta[2]) == int(np.sum(np.diff(runs) > 32))
         # persistent scratch is all-zero again
         assert int(t["bits"].abs().sum()) == 0 and int(t["blk_flag"].sum()) == 0 and int(t["cnt"].abs().sum()) == 0
+
+
+def _expand_inputs(rng, batch, width, n_rows, n_recv, dev):
+    emb = rng.normal(size=(n_rows, width)).astype(np.float32)
+    recv = rng.normal(size=(n_recv, width)).astype(np.float32)
+    pos_row = rng.randint(n_rows, size=batch).astype(np.int32)
+    idx_map = rng.randint(n_recv, size=batch).astype(np.int32)
+    recv_slot = rng.permutation(n_recv).astype(np.uint32)
+    remote = rng.rand(batch) < 0.3
+    pos_row[remote] = -1
+    bad = rng.rand(batch) < 0.02  # out-of-range keys: no row, no unique index -> zeros
+    pos_row[bad] = -1
+    idx_map[bad] = -1
+    exp = np.where(pos_row[:, None] >= 0, emb[np.maximum(pos_row, 0)], recv[recv_slot[np.maximum(idx_map, 0)]])
+    exp[bad] = 0
+    t = [torch.from_numpy(x).to(dev) for x in (pos_row, idx_map, recv_slot.view(np.int32), recv, emb)]
+    return t, exp.astype(np.float32)
+
+
+@pytest.mark.parametrize("width", [32, 64, 128, 256, 1024])
+@pytest.mark.parametrize("batch", [1, 37, 5000])
+def test_expand_launchers_agree(width, batch):
+    """Register kernel and bulk-copy kernel of the row expansion on caller-owned buffers, against numpy."""
+    L = hb.lib()
+    L.hctr_expand_rows.argtypes = [sz, sz, vp, vp, vp, vp, vp, vp, vp]
+    L.hctr_expand_rows_bulk.argtypes = [sz, sz, vp, vp, vp, vp, vp, vp, vp, vp]
+    dev = torch.device("cuda:0")
+    rng = np.random.RandomState(width + batch)
+    (pos_row, idx_map, recv_slot, recv, emb), exp = _expand_inputs(rng, batch, width, 3000, 700, dev)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    for bulk in (False, True):
+        dst = torch.full((batch, width), float("nan"), device=dev)
+        if bulk:
+            rc = L.hctr_expand_rows_bulk(batch, width, pos_row.data_ptr(), idx_map.data_ptr(), recv_slot.data_ptr(),
+                                         recv.data_ptr(), emb.data_ptr(), dst.data_ptr(), err.data_ptr(), None)
+        else:
+            rc = L.hctr_expand_rows(batch, width, pos_row.data_ptr(), idx_map.data_ptr(), recv_slot.data_ptr(),
+                                    recv.data_ptr(), emb.data_ptr(), dst.data_ptr(), None)
+        assert rc == 0
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0
+        assert np.array_equal(dst.cpu().numpy(), exp), f"bulk={bulk}"
+
+
+def test_ingest_keys_and_deferred_ordering():
+    """hctr_ingest_keys (copy + cleared meta in one launch) and the split pipeline: hctr_dedupe_map without the
+    run ordering (fork event only), hctr_dedupe_order later on another stream."""
+    L = hb.lib()
+    L.hctr_ingest_keys.argtypes = [vp, vp, sz, vp, ctypes.c_uint, vp]
+    L.hctr_dedupe_map.argtypes = [ctypes.POINTER(DedupeArgs), vp]
+    L.hctr_dedupe_order.argtypes = [ctypes.POINTER(DedupeArgs), vp]
+    L.hctr_scan_chained_scratch_words.restype = sz
+    L.hctr_scan_chained_scratch_words.argtypes = [sz]
+    dev = torch.device("cuda:0")
+    N, B = 20_000, 9_000
+    n_pad = (N + 4095) // 4096 * 4096
+    words, blocks = n_pad // 64, n_pad // 4096
+    rng = np.random.RandomState(3)
+    keys = (rng.zipf(1.15, size=B) - 1) % N
+    keys[:2000] = 77  # a long run
+    user = torch.from_numpy(keys.astype(np.int64)).to(dev)
+
+    def z(n, dt):
+        return torch.zeros(max(int(n), 1), dtype=dt, device=dev)
+
+    private = z(B, torch.int64)
+    meta = torch.full((6,), 123, dtype=torch.int32, device=dev)
+    assert L.hctr_ingest_keys(user.data_ptr(), private.data_ptr(), B, meta.data_ptr(), 6, None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(private, user) and int(meta.abs().sum()) == 0
+
+    t = dict(owner_of=z(N, torch.uint8), row_of=torch.arange(N, dtype=torch.int32, device=dev),
+             bits=z(words, torch.int64), blk_flag=z(blocks + 1, torch.uint8), cnt=z(B + 1, torch.int32),
+             chain_scratch=z(2 * (blocks // 8 + 2), torch.int32),
+             scan_scratch=z(L.hctr_scan_chained_scratch_words(B + 1), torch.int32), word_base=z(words, torch.int32),
+             sk=z(B, torch.int64), rank_in_run=z(B, torch.int32), uniq=z(B, torch.int64), uniq_owner=z(B, torch.uint8),
+             uniq_row=z(B, torch.int32), run_start=z(B + 1, torch.int32), sorted_pos=z(B, torch.int32),
+             idx_map=z(B, torch.int32), pos_row=z(B, torch.int32), heavy_list=z(B // 32 + 2, torch.int32), meta=meta)
+    side = torch.cuda.Stream(device=dev)
+    fork = torch.cuda.Event()
+    fork.record()  # creates the underlying event handle
+    a = DedupeArgs(keys=private.data_ptr(), batch=B, length=N, length_pad=n_pad, nrank=1, epoch=1,
+                   side_stream=side.cuda_stream, fork_event=fork.cuda_event, join_event=None,
+                   **{k: v.data_ptr() for k, v in t.items()})
+    assert L.hctr_dedupe_map(ctypes.byref(a), None) == 0  # ordering NOT enqueued, fork event recorded
+    side.wait_event(fork)
+    assert L.hctr_dedupe_order(ctypes.byref(a), side.cuda_stream) == 0
+    torch.cuda.synchronize()
+    idx_map = t["idx_map"].cpu().numpy()
+    assert np.array_equal(t["sorted_pos"].cpu().numpy().astype(np.int64), np.argsort(idx_map, kind="stable"))
