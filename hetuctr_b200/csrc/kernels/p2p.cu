@@ -201,7 +201,11 @@ __global__ void __launch_bounds__(kThreads) p2p_return_list(hctr_p2p_ctx c, cons
     if (flags32[q]) ret_q[ret_slot[q]] = (u32)q;
 }
 
-// One group of LANES lanes per returned row, rows written straight into the requester's mailbox.
+// One group of LANES lanes per returned row, rows written straight into the requester's mailbox.  A group takes
+// kGatherRows rows per iteration and issues the loads of all of them stage by stage (list entry, key, row number,
+// then the rows), so that the chains of dependent accesses of several rows overlap.
+constexpr int kGatherRows = 4;
+
 template <int LANES, bool VEC>
 __global__ void __launch_bounds__(kThreads) p2p_gather(hctr_p2p_ctx c, const u32 *__restrict__ ret_q,
                                                        const u32 *__restrict__ ret_slot,
@@ -219,18 +223,39 @@ __global__ void __launch_bounds__(kThreads) p2p_gather(hctr_p2p_ctx c, const u32
   const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
   const size_t E = R::elems(c.width);
   const hctr_p2p_box me = c.box[c.rank];
-  for (size_t r = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; r < n_ret; r += groups) {
-    const u32 qq = ret_q[r];
-    const unsigned s = source_of(qstart, c.nrank, qq);
-    const u32 j = qq - qstart[s];
-    const u32 slot = (u32)r - ret_slot[qstart[s]];
-    const int32_t row = row_of[me.qkey[(size_t)s * c.cap + j]];
-    const hctr_p2p_box b = c.box[s];
-    const size_t dst = (size_t)c.rank * c.cap + slot;
-    if (gl == 0) b.rver[dst] = version[row];
-    const T *from = reinterpret_cast<const T *>(embedding) + (size_t)row * E;
-    T *to = reinterpret_cast<T *>(b.rval) + dst * E;
-    for (size_t e = gl; e < E; e += LANES) to[e] = from[e];
+  for (size_t r0 = (((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES) * kGatherRows; r0 < n_ret;
+       r0 += groups * kGatherRows) {
+    u32 qq[kGatherRows];
+    unsigned src[kGatherRows];
+    long long key[kGatherRows];
+    int32_t row[kGatherRows];
+    size_t dst[kGatherRows];
+#pragma unroll
+    for (int k = 0; k < kGatherRows; k++) qq[k] = r0 + k < n_ret ? ret_q[r0 + k] : 0u;
+#pragma unroll
+    for (int k = 0; k < kGatherRows; k++) {
+      src[k] = source_of(qstart, c.nrank, qq[k]);
+      key[k] = r0 + k < n_ret ? me.qkey[(size_t)src[k] * c.cap + (qq[k] - qstart[src[k]])] : 0;
+    }
+#pragma unroll
+    for (int k = 0; k < kGatherRows; k++) {
+      row[k] = r0 + k < n_ret ? row_of[key[k]] : -1;
+      dst[k] = (size_t)c.rank * c.cap + ((u32)(r0 + k) - ret_slot[qstart[src[k]]]);
+    }
+    if (gl == 0) {
+#pragma unroll
+      for (int k = 0; k < kGatherRows; k++)
+        if (row[k] >= 0) c.box[src[k]].rver[dst[k]] = version[row[k]];
+    }
+    for (size_t e = gl; e < E; e += LANES) {
+      T v[kGatherRows];
+#pragma unroll
+      for (int k = 0; k < kGatherRows; k++)
+        if (row[k] >= 0) v[k] = reinterpret_cast<const T *>(embedding)[(size_t)row[k] * E + e];
+#pragma unroll
+      for (int k = 0; k < kGatherRows; k++)
+        if (row[k] >= 0) reinterpret_cast<T *>(c.box[src[k]].rval)[dst[k] * E + e] = v[k];
+    }
   }
 }
 

@@ -775,6 +775,23 @@ __global__ void __launch_bounds__(kThreads) owner_mark_sources(PushLists p, cons
   }
 }
 
+// entry of key k in source s2's key-sorted list
+__device__ __forceinline__ size_t push_entry_of(const PushLists &p, const u32 *start, int s2, long long k) {
+  const size_t off2 = p.src_off[s2];
+  size_t lo = 0, hi = start[s2 + 1] - start[s2];
+  while (lo < hi) {
+    const size_t mid = (lo + hi) >> 1;
+    if (p.key[off2 + mid] < k) lo = mid + 1;
+    else hi = mid;
+  }
+  return off2 + lo;
+}
+
+// A group of LANES lanes takes kApplyRows pushed rows per iteration and issues the loads of all of them before
+// it uses any: keys, then row numbers, then source masks, then the table rows and pushed rows themselves, so
+// that four chains of dependent memory accesses overlap instead of one.
+constexpr int kApplyRows = 4;
+
 template <int LANES, bool VEC>
 __global__ void __launch_bounds__(kThreads) owner_apply_sources(PushLists p, size_t width,
                                                                 const int32_t *__restrict__ row_of, size_t length,
@@ -790,35 +807,64 @@ __global__ void __launch_bounds__(kThreads) owner_apply_sources(PushLists p, siz
   const unsigned gl = threadIdx.x % LANES;
   const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
   const size_t E = R::elems(width);
-  for (size_t f = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; f < total; f += groups) {
-    const int s = push_source(start, p.nsrc, (u32)f);
-    const size_t ent = p.src_off[s] + (f - start[s]);
-    const long long k = p.key[ent];
-    const int32_t row = owned_row(row_of, length, n_cached, k);
-    if (row < 0) continue;  // reported by the marking pass
-    const u64 mk = mask[(size_t)row - n_cached] & 0xffffffffull;  // this step's epoch, set by the marking pass
-    if (mk & ((1ull << s) - 1)) continue;  // a lower source pushes this row too: it applies everything
-    T *emb = reinterpret_cast<T *>(embedding) + (size_t)row * E;
-    long long ver_add = p.upd[ent];
-    const T *v = reinterpret_cast<const T *>(p.val) + ent * E;
-    for (size_t e = gl; e < E; e += LANES) emb[e] = R::add(emb[e], R::ld_once(v + e));
-    u64 rest = (mk >> (s + 1)) << (s + 1);  // higher sources that also push it
-    while (rest) {
-      const int s2 = __ffsll((long long)rest) - 1;
-      rest &= rest - 1;
-      // entry of key k in source s2's key-sorted list
-      const size_t off2 = p.src_off[s2];
-      size_t lo = 0, hi = start[s2 + 1] - start[s2];
-      while (lo < hi) {
-        const size_t mid = (lo + hi) >> 1;
-        if (p.key[off2 + mid] < k) lo = mid + 1;
-        else hi = mid;
+  for (size_t f0 = (((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES) * kApplyRows; f0 < total;
+       f0 += groups * kApplyRows) {
+    int src[kApplyRows];
+    size_t ent[kApplyRows];
+    long long key[kApplyRows];
+    int32_t row[kApplyRows];
+    u64 rest[kApplyRows];
+#pragma unroll
+    for (int r = 0; r < kApplyRows; r++) {
+      const size_t f = f0 + r;
+      src[r] = -1;
+      key[r] = -1;
+      if (f < total) {
+        src[r] = push_source(start, p.nsrc, (u32)f);
+        ent[r] = p.src_off[src[r]] + (f - start[src[r]]);
+        key[r] = p.key[ent[r]];
       }
-      ver_add += p.upd[off2 + lo];
-      const T *v2 = reinterpret_cast<const T *>(p.val) + (off2 + lo) * E;
-      for (size_t e = gl; e < E; e += LANES) emb[e] = R::add(emb[e], R::ld_once(v2 + e));
     }
-    if (gl == 0) version[row] = (long long)((u64)version[row] + (u64)ver_add);
+#pragma unroll
+    for (int r = 0; r < kApplyRows; r++) row[r] = src[r] >= 0 ? owned_row(row_of, length, n_cached, key[r]) : -1;
+#pragma unroll
+    for (int r = 0; r < kApplyRows; r++) {
+      rest[r] = 0;
+      if (row[r] >= 0) {  // rows that are not owned here were reported by the marking pass
+        const u64 mk = mask[(size_t)row[r] - n_cached] & 0xffffffffull;  // this step's epoch, set by the marking pass
+        if (mk & ((1ull << src[r]) - 1)) row[r] = -1;  // a lower source pushes this row too: it applies everything
+        else rest[r] = (mk >> (src[r] + 1)) << (src[r] + 1);  // higher sources that also push it
+      }
+    }
+    for (size_t e = gl; e < E; e += LANES) {
+      T acc[kApplyRows], v[kApplyRows];
+#pragma unroll
+      for (int r = 0; r < kApplyRows; r++) {
+        if (row[r] >= 0) {
+          acc[r] = reinterpret_cast<const T *>(embedding)[(size_t)row[r] * E + e];
+          v[r] = R::ld_once(reinterpret_cast<const T *>(p.val) + ent[r] * E + e);
+        }
+      }
+#pragma unroll
+      for (int r = 0; r < kApplyRows; r++) {
+        if (row[r] < 0) continue;
+        acc[r] = R::add(acc[r], v[r]);
+        for (u64 m = rest[r]; m; m &= m - 1) {  // ascending source order, as source-by-source launches would
+          const size_t ent2 = push_entry_of(p, start, __ffsll((long long)m) - 1, key[r]);
+          acc[r] = R::add(acc[r], R::ld_once(reinterpret_cast<const T *>(p.val) + ent2 * E + e));
+        }
+        reinterpret_cast<T *>(embedding)[(size_t)row[r] * E + e] = acc[r];
+      }
+    }
+    if (gl == 0) {
+#pragma unroll
+      for (int r = 0; r < kApplyRows; r++) {
+        if (row[r] < 0) continue;
+        long long ver_add = p.upd[ent[r]];
+        for (u64 m = rest[r]; m; m &= m - 1) ver_add += p.upd[push_entry_of(p, start, __ffsll((long long)m) - 1, key[r])];
+        version[row[r]] = (long long)((u64)version[row[r]] + (u64)ver_add);
+      }
+    }
   }
 }
 
@@ -887,7 +933,7 @@ extern "C" int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width
   const bool al = host_aligned16(val) && host_aligned16(embedding);
 #define CALL(L, V)                                                                                    \
   do {                                                                                                \
-    size_t g_ = (rows_hint * L + kThreads - 1) / kThreads;                                            \
+    size_t g_ = ((rows_hint + kApplyRows - 1) / kApplyRows * L + kThreads - 1) / kThreads;            \
     if (g_ > (size_t)kSMs * 8) g_ = (size_t)kSMs * 8;                                                 \
     owner_apply_sources<L, V><<<(unsigned)g_, kThreads, 0, st>>>(p, width, row_of, length, n_cached,  \
                                                                  row_mask, embedding, (long long *)version); \
