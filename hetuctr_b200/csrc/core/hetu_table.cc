@@ -315,6 +315,7 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   flushOrdering(cur_batch_);  // normally done by push_pull already; two preprocess calls in a row get here
   std::swap(cur_batch_, prev_batch_);
   BatchDesc &cur = cur_batch_, &prev = prev_batch_;
+  cur.decided = false;
   reserveBatch(cur, std::max<size_t>(batch_size, 1));
   reserveShared(std::max<size_t>(batch_size, 1));
   if (use_p2p_) p2p_->reserve(std::max<size_t>(batch_size, 1), stream_main_);  // collective when it grows
@@ -386,17 +387,7 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   // Push decision for the previous batch (csrc/core/preprocess.cu:167-182).  With one rank every
   // row is owned, nothing is ever pushed.
   const bool decide = n > 1 && prev.unique_size > 0;
-  if (decide) {
-    // on the reduction's stream: only the reduction (and the counts published after it) need the result
-    int spd = tic(kPhPushDecide, stream_reduce_);
-    HCTR_LAUNCH(hctr_push_decide_fused(prev.meta.as<uint32_t>(), n, rank_, prev.unique_size,
-                                       prev.uniq_owner.as<uint8_t>(), prev.uniq_row.as<int32_t>(),
-                                       prev.run_start.as<uint32_t>(), d_updates_.as<int64_t>(), push_bound_,
-                                       d_need_push_.as<uint32_t>(), d_push_slot_.as<uint32_t>(),
-                                       d_chain3_.as<uint32_t>(), nextEpoch(), d_push_count_.as<uint32_t>(),
-                                       d_push_base_.as<uint32_t>(), d_err_.as<uint32_t>(), stream_reduce_));
-    toc(spd, stream_reduce_);
-  }
+  if (decide && !prev.decided) launchPushDecide(prev);  // normally done at the end of the previous push_pull
   HCTR_CUDA(cudaEventRecord(ev_decide_, stream_reduce_));
   int sp = tic(kPhDedupe);
   HCTR_LAUNCH(hctr_dedupe_map(&a, stream_main_));
@@ -443,6 +434,20 @@ int HetuTable::expandRows(size_t batch, size_t width, const int32_t *pos_row, co
   if (expand_bulk_)
     return hctr_expand_rows_bulk(batch, width, pos_row, idx_map, recv_slot, recv_val, embedding, dst, err, stream);
   return hctr_expand_rows(batch, width, pos_row, idx_map, recv_slot, recv_val, embedding, dst, stream);
+}
+
+// Push decision for batch b (csrc/core/preprocess.cu:167-182), on the reduction's stream: only the reduction of
+// b's gradient (and the counts published after it) need the result.  It depends on the pending-update counts as
+// the previous reduction left them, so it can run as soon as b's own push_pull is over.
+void HetuTable::launchPushDecide(BatchDesc &b) {
+  int spd = tic(kPhPushDecide, stream_reduce_);
+  HCTR_LAUNCH(hctr_push_decide_fused(b.meta.as<uint32_t>(), nrank_, rank_, b.unique_size, b.uniq_owner.as<uint8_t>(),
+                                     b.uniq_row.as<int32_t>(), b.run_start.as<uint32_t>(), d_updates_.as<int64_t>(),
+                                     push_bound_, d_need_push_.as<uint32_t>(), d_push_slot_.as<uint32_t>(),
+                                     d_chain3_.as<uint32_t>(), nextEpoch(), d_push_count_.as<uint32_t>(),
+                                     d_push_base_.as<uint32_t>(), d_err_.as<uint32_t>(), stream_reduce_));
+  toc(spd, stream_reduce_);
+  b.decided = true;
 }
 
 void HetuTable::flushOrdering(BatchDesc &b) {
@@ -822,6 +827,9 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     p2p_err = h_cnt[3 * n];
     if (p2p_err) HCTR_CUDA(cudaMemsetAsync(d_err_.p, 0, sizeof(uint32_t), stream_main_));
   }
+  // The push decision for the batch just pulled runs now, while the caller computes its gradient: everything it
+  // reads is final, and the next step's reduction no longer has to wait for it.
+  if (n > 1 && p2p_err == 0 && cur.unique_size > 0 && !cur.decided) launchPushDecide(cur);
   if (p2p_err & HCTR_ERR_TIMEOUT)
     throw std::runtime_error("push_pull: a peer's message did not arrive in time (is every rank calling push_pull?)");
   if (p2p_err & HCTR_ERR_NOT_OWNER)

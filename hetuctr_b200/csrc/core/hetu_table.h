@@ -61,6 +61,7 @@ struct BatchDesc {
   bool pending = false;  // sizes not yet read back from the device (single-rank tables defer this)
   cudaEvent_t ev_order = nullptr;  // completion of this batch's run ordering (on the ordering stream)
   bool order_recorded = false;
+  bool decided = false;            // the push decision for this batch has been enqueued
   bool order_pending = false;      // the run-ordering kernels of this batch are not enqueued yet
   hctr_dedupe_args order_args;     // what they will be launched with
   DevBuf keys, idx_map, sorted_pos, uniq, uniq_owner, uniq_row, run_start, meta, pos_row, heavy;
@@ -160,6 +161,7 @@ class HetuTable {
   void finalizePending();
   int expandRows(size_t batch, size_t width, const int32_t *pos_row, const int32_t *idx_map, const uint32_t *recv_slot,
                  const float *recv_val, const float *embedding, float *dst, uint32_t *err, cudaStream_t stream);
+  void launchPushDecide(BatchDesc &b);
   void flushOrdering(BatchDesc &b);  // enqueues a batch's deferred run ordering
   void quiesce();  // every stream drained, pending batch sizes read back
   void exchangeP2P(embed_t *dst_dev);

@@ -158,6 +158,7 @@ void HetuTable::importState(const std::string &path) {
     b->batch_size = 0;
     b->unique_size = 0;
     b->n_heavy = 0;
+    b->decided = false;
     std::fill(b->seg.begin(), b->seg.end(), 0);
     for (auto *v : {&b->query_send, &b->query_recv, &b->push_send, &b->push_recv, &b->ret_send, &b->ret_recv})
       std::fill(v->begin(), v->end(), 0);
