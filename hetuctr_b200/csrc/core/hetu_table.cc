@@ -80,6 +80,13 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
     const std::string mode = env ? env : "default";
     HCTR_CHECK(mode == "default" || mode == "bulk", "HCTR_EXPAND must be default or bulk");
     expand_bulk_ = mode == "bulk";
+    const char *ks = std::getenv("HCTR_KEY_STRIDE");
+    if (ks && std::string(ks) != "auto") {
+      const long v = std::strtol(ks, nullptr, 10);
+      HCTR_CHECK(v >= 0 && v <= 4096, "HCTR_KEY_STRIDE must be auto or a number of fields (0..4096)");
+      key_stride_ = (uint32_t)v;
+      key_stride_known_ = true;
+    }
   }
   {
     // stream_main_ carries many short, latency-bound kernels; it gets the highest priority so that their
@@ -342,7 +349,9 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
     HCTR_CUDA(cudaMemsetAsync(cur.meta.p, 0, meta_words * sizeof(uint32_t), stream_main_));
   }
 
+  if (!key_stride_known_ && batch_size >= 4096) detectKeyStride(cur);  // once per table
   hctr_dedupe_args a;
+  a.stride = key_stride_;
   a.keys = cur.keys.as<int64_t>();
   a.batch = batch_size;
   a.length = kEmbeddingIDMax;
@@ -434,6 +443,32 @@ int HetuTable::expandRows(size_t batch, size_t width, const int32_t *pos_row, co
   if (expand_bulk_)
     return hctr_expand_rows_bulk(batch, width, pos_row, idx_map, recv_slot, recv_val, embedding, dst, err, stream);
   return hctr_expand_rows(batch, width, pos_row, idx_map, recv_slot, recv_val, embedding, dst, stream);
+}
+
+// Looks at the first large batch (already in the table's private key buffer) for the period at which keys
+// repeat: in a sample-major batch of F fields the hot keys of a field recur at distances F, 2F, ..., and never
+// at other distances because fields use disjoint key ranges.  Costs one small kernel and one synchronisation,
+// once.  A batch without such structure (uniform keys, a single field) leaves the positions in order.
+void HetuTable::detectKeyStride(const BatchDesc &b) {
+  key_stride_known_ = true;
+  DevBuf scores;
+  scores.ensure(65 * sizeof(uint32_t));
+  uint32_t h[65] = {};
+  HCTR_LAUNCH(hctr_detect_key_stride(b.keys.as<int64_t>(), b.batch_size, scores.as<uint32_t>(), stream_main_));
+  HCTR_CUDA(cudaMemcpyAsync(h, scores.p, sizeof(h), cudaMemcpyDeviceToHost, stream_main_));
+  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+  scores.release();
+  uint32_t best = 0;
+  for (int d = 1; d <= 64; d++) best = std::max(best, h[d]);
+  key_stride_ = 0;
+  if (best >= 64) {  // enough repeats to tell
+    for (int d = 1; d <= 64; d++)
+      if (2 * (uint64_t)h[d] >= best) {
+        key_stride_ = (uint32_t)d;
+        break;
+      }
+  }
+  info(*this, "key batches look sample-major with ", key_stride_, " fields (0/1: no structure found)");
 }
 
 // Push decision for batch b (csrc/core/preprocess.cu:167-182), on the reduction's stream: only the reduction of

@@ -181,6 +181,12 @@ class HetuTable {
   bool use_p2p_ = false;
   bool p2p_counts_pending_ = false;
   bool expand_bulk_ = false;         // HCTR_EXPAND=bulk
+  // Field count of the (sample-major) key batches, used to give every warp of the dedupe kernels one field of
+  // 32 consecutive samples: HCTR_KEY_STRIDE = auto (default: found from the first large batch) or a number
+  // (0 or 1 = off).
+  uint32_t key_stride_ = 0;
+  bool key_stride_known_ = false;
+  void detectKeyStride(const BatchDesc &b);
   bool batch_open_ = false;          // preprocess done, push_pull not yet
   bool prev_push_valid_ = false;     // d_push_count_/d_push_base_ describe prev_batch_
 

@@ -27,32 +27,51 @@ constexpr int kThreads = 256;
 constexpr u32 kLightRun = HCTR_LIGHT_RUN;  // runs up to this length are ordered by one warp
 constexpr int kHeavyWindowBits = 1 << 20;  // positions covered by one shared-memory window (128 KB)
 
+// Thread -> batch position.  CTR batches are sample-major: position = sample * F + field, and the keys of one
+// field come from one contiguous (often small) key range, while neighbouring positions belong to different
+// fields.  With the identity mapping the 32 lanes of a warp touch 32 unrelated places of the bitmap and of the
+// per-key arrays, and the few cache lines of a small vocabulary receive thousands of separate requests per
+// batch.  With stride F a warp takes the SAME field of 32 consecutive samples: its lanes hit the same lines
+// (one request instead of up to 32) and duplicates inside the warp are merged before they reach an atomic.
+// Positions beyond the last whole group of 32 samples keep the identity mapping.  Any mapping gives the same
+// results: which thread handles a position is invisible in the outputs.
+__device__ __forceinline__ size_t mapped_pos(size_t t, size_t batch, u32 stride) {
+  if (stride <= 1) return t;
+  const size_t group = (size_t)32 * stride;
+  if (t >= batch / group * group) return t;
+  const size_t r = t % group;
+  return t - r + (r % 32) * stride + r / 32;
+}
+
 // The kernel is a chain of dependent memory operations per position (key -> owner -> bitmap word ->
 // atomic), so it is latency-bound; a single-rank table skips the owner lookup (every key is rank 0's).
 __global__ void __launch_bounds__(kThreads) dedupe_mark(hctr_dedupe_args a) {
-  const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
-  if (i >= a.batch) return;
-  const long long key = a.keys[i];
-  unsigned o = 0;
-  bool ok = key >= 0 && (size_t)key < a.length;
-  if (ok && a.nrank > 1) {
-    o = a.owner_of[key];
-    ok = o < (unsigned)a.nrank;
+  const size_t t = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  const unsigned lane = threadIdx.x & 31;
+  u64 sk = ~0ull;
+  bool ok = false;
+  if (t < a.batch) {
+    const size_t i = mapped_pos(t, a.batch, a.stride);
+    const long long key = a.keys[i];
+    unsigned o = 0;
+    ok = key >= 0 && (size_t)key < a.length;
+    if (ok && a.nrank > 1) {
+      o = a.owner_of[key];
+      ok = o < (unsigned)a.nrank;
+    }
+    if (ok) sk = (u64)key + (u64)a.length_pad * o;
+    else atomicOr(&a.meta[HCTR_META_ERR], HCTR_ERR_KEY_RANGE);
+    a.sk[i] = sk;
   }
-  if (!ok) {
-    atomicOr(&a.meta[HCTR_META_ERR], HCTR_ERR_KEY_RANGE);
-    a.sk[i] = ~0ull;
-    return;
-  }
-  const u64 sk = (u64)key + (u64)a.length_pad * o;
-  a.sk[i] = sk;
+  // one lane per distinct key of the warp goes on (whole warps get here: no thread has returned)
+  const unsigned peers = __match_any_sync(0xffffffffu, ok ? sk : ~(u64)lane);
+  if (!ok || lane != (unsigned)(__ffs(peers) - 1)) return;
   // the bitmap is addressed as 32-bit words here (little-endian halves of the 64-bit words)
   const u32 bit = 1u << (sk & 31);
   u32 *word = reinterpret_cast<u32 *>(a.bits) + (sk >> 5);
-  // Small vocabularies are contiguous key ranges, so thousands of positions of a batch land on the same
-  // few cache lines of the bitmap.  Skip the atomic when an earlier duplicate is already visible, and let
-  // only the first setter of a bit touch the block flag (unconditional flag stores from every position
-  // made one L2 slice 12x hotter than the average in profiles).
+  // Skip the atomic when an earlier duplicate is already visible, and let only the first setter of a bit touch
+  // the block flag (unconditional flag stores from every position made one L2 slice 12x hotter than the
+  // average in profiles).
   if (*word & bit) return;
   const u32 old = atomicOr(word, bit);
   if (!(old & bit)) a.blk_flag[sk >> 12] = 1;
@@ -132,18 +151,32 @@ __global__ void __launch_bounds__(kThreads) dedupe_block_ranks(hctr_dedupe_args 
 }
 
 __global__ void __launch_bounds__(kThreads) dedupe_rank(hctr_dedupe_args a) {
-  const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
-  if (i >= a.batch) return;
-  const u64 sk = a.sk[i];
-  if (sk == ~0ull) {
-    a.idx_map[i] = -1;
-    return;
+  const size_t t = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  const unsigned lane = threadIdx.x & 31;
+  size_t i = 0;
+  u64 sk = ~0ull;
+  if (t < a.batch) {
+    i = mapped_pos(t, a.batch, a.stride);
+    sk = a.sk[i];
   }
-  const u64 w = sk >> 6;
-  const u64 below = a.bits[w] & ((1ull << (sk & 63)) - 1);
-  const u32 u = a.word_base[w] + __popcll(below);
-  a.idx_map[i] = (int32_t)u;
-  const u32 rk = atomicAdd(&a.cnt[u], 1u);
+  const bool ok = sk != ~0ull;
+  u32 u = 0;
+  if (ok) {
+    const u64 w = sk >> 6;
+    const u64 below = a.bits[w] & ((1ull << (sk & 63)) - 1);
+    u = a.word_base[w] + __popcll(below);
+    a.idx_map[i] = (int32_t)u;
+  } else if (t < a.batch) {
+    a.idx_map[i] = -1;
+  }
+  // duplicates inside the warp take their ranks from one atomic: the lowest lane adds the group's size
+  const unsigned peers = __match_any_sync(0xffffffffu, ok ? (u64)u : ~(u64)lane);
+  const unsigned leader = (unsigned)(__ffs(peers) - 1);
+  u32 base = 0;
+  if (ok && lane == leader) base = atomicAdd(&a.cnt[u], (u32)__popc(peers));
+  base = __shfl_sync(0xffffffffu, base, leader);
+  if (!ok) return;
+  const u32 rk = base + __popc(peers & ((1u << lane) - 1));
   a.rank_in_run[i] = rk;
   if (rk == 0) {  // exactly one position per unique key
     const long long key = a.keys[i];
@@ -154,8 +187,9 @@ __global__ void __launch_bounds__(kThreads) dedupe_rank(hctr_dedupe_args a) {
 }
 
 __global__ void __launch_bounds__(kThreads) dedupe_scatter(hctr_dedupe_args a) {
-  const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
-  if (i >= a.batch) return;
+  const size_t t = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  if (t >= a.batch) return;
+  const size_t i = mapped_pos(t, a.batch, a.stride);
   const u64 sk = a.sk[i];
   if (sk == ~0ull) {
     a.pos_row[i] = HCTR_INVALID_ROW;
@@ -273,6 +307,21 @@ __global__ void __launch_bounds__(1024) dedupe_order_heavy(hctr_dedupe_args a, u
   }
 }
 
+// scores[d] = number of i < limit - d with keys[i] == keys[i + d]; one thread block per distance d = 1..64
+__global__ void __launch_bounds__(kThreads) key_stride_scores(const long long *__restrict__ keys, size_t n,
+                                                              u32 *__restrict__ scores) {
+  __shared__ u32 total;
+  const size_t d = blockIdx.x + 1;
+  const size_t limit = n < 32768 ? n : 32768;
+  if (threadIdx.x == 0) total = 0;
+  __syncthreads();
+  u32 mine = 0;
+  for (size_t i = threadIdx.x; i + d < limit; i += kThreads) mine += keys[i] == keys[i + d] ? 1u : 0u;
+  atomicAdd(&total, mine);
+  __syncthreads();
+  if (threadIdx.x == 0) scores[d] = total;
+}
+
 // Private copy of a device-resident key batch + cleared meta words in one launch (one device operation
 // in front of the pipeline instead of a copy and a memset).
 __global__ void __launch_bounds__(kThreads) ingest_keys(const long long *__restrict__ src, long long *__restrict__ dst,
@@ -285,6 +334,12 @@ __global__ void __launch_bounds__(kThreads) ingest_keys(const long long *__restr
 }  // namespace hctr
 
 using namespace hctr;
+
+extern "C" int hctr_detect_key_stride(const int64_t *keys, size_t n, uint32_t *scores, void *stream) {
+  key_stride_scores<<<64, kThreads, 0, (cudaStream_t)stream>>>((const long long *)keys, n, scores);
+  count_launches(1);
+  return launch_status();
+}
 
 extern "C" int hctr_ingest_keys(const int64_t *src, int64_t *dst, size_t n, uint32_t *meta, unsigned meta_words,
                                 void *stream) {

@@ -162,6 +162,11 @@ typedef struct hctr_dedupe_args {
   void *side_stream;
   void *fork_event;
   void *join_event;
+  /* optional: the number of fields of a sample-major batch (position = sample * stride + field).  With a
+   * stride > 1 a warp works on one field of 32 consecutive samples, which turns the scattered accesses of
+   * small-vocabulary fields into shared cache lines and merged atomics.  0 or 1 = positions in order.  The
+   * outputs do not depend on it.  hctr_detect_key_stride finds it from a batch. */
+  uint32_t stride;
 } hctr_dedupe_args;
 
 #define HCTR_META_UNIQUE 0   /* number of unique keys U                         */
@@ -174,6 +179,11 @@ typedef struct hctr_dedupe_args {
  * = index of the first unique key owned by p (entry nrank = U), and the bitmap scratch is all-zero
  * again.  Keys out of range set HCTR_ERR_KEY_RANGE in meta[HCTR_META_ERR] and get idx_map = -1. */
 int hctr_dedupe_map(const hctr_dedupe_args *a, void *stream);
+
+/* Finds the field count of a sample-major batch: scores[d] (d = 1..64, 65 words, scores[0] unused) = number of
+ * positions i among the first 32768 with keys[i] == keys[i + d].  Keys of different fields never coincide and hot
+ * keys of one field repeat from sample to sample, so the smallest d with a large score is the field count. */
+int hctr_detect_key_stride(const int64_t *keys, size_t n, uint32_t *scores, void *stream);
 
 /* Front of the pipeline for keys that already live in device memory: dst[0..n) = src[0..n) (the table's private
  * copy, so that the caller may reuse its buffer) and meta[0..meta_words) = 0, in one launch. */

@@ -23,11 +23,12 @@ class DedupeArgs(ctypes.Structure):  # field order of hctr_dedupe_args
                 ("chain_scratch", vp), ("scan_scratch", vp), ("epoch", u32), ("word_base", vp), ("sk", vp),
                 ("rank_in_run", vp), ("uniq", vp), ("uniq_owner", vp), ("uniq_row", vp), ("run_start", vp),
                 ("sorted_pos", vp), ("idx_map", vp), ("pos_row", vp), ("heavy_list", vp), ("meta", vp),
-                ("side_stream", vp), ("fork_event", vp), ("join_event", vp)]
+                ("side_stream", vp), ("fork_event", vp), ("join_event", vp), ("stride", u32)]
 
 
+@pytest.mark.parametrize("stride", [0, 7, 26])
 @pytest.mark.parametrize("nrank", [1, 3])
-def test_dedupe_launcher_standalone(nrank):
+def test_dedupe_launcher_standalone(nrank, stride):
     L = hb.lib()
     L.hctr_dedupe_map.argtypes = [ctypes.POINTER(DedupeArgs), vp]
     L.hctr_scan_chained_scratch_words.restype = sz
@@ -59,7 +60,7 @@ def test_dedupe_launcher_standalone(nrank):
         kd = torch.from_numpy(keys.astype(np.int64)).to(dev)
         t["meta"].zero_()
         a = DedupeArgs(keys=kd.data_ptr(), batch=B, length=N, length_pad=n_pad, nrank=nrank, epoch=epoch,
-                       side_stream=None, fork_event=None, join_event=None,
+                       side_stream=None, fork_event=None, join_event=None, stride=stride,
                        **{k: v.data_ptr() for k, v in t.items()})
         assert L.hctr_dedupe_map(ctypes.byref(a), None) == 0
         torch.cuda.synchronize()
