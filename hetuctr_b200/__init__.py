@@ -148,7 +148,7 @@ class Table:
     (reference csrc/pybind/pybind.cu:62-69); init is (kind, a, b)."""
 
     _STATS = ("batch", "unique", "prev_batch", "prev_unique", "pushed_rows", "received_push_rows", "queried_keys",
-              "returned_rows", "received_rows", "stored_rows", "cached_rows")
+              "returned_rows", "received_rows", "stored_rows", "cached_rows", "wait_queries_us", "wait_returns_us")
 
     def __init__(self, rank, nrank, device_id, ip, port, length, width, pull_bound, push_bound, root_arr,
                  storage_arr, init=(INIT_ZERO, 0.0, 0.0), learning_rate=0.01, verbose=0):
@@ -216,12 +216,12 @@ class Table:
         self._check(self._lib.hctr_table_import(self._h, str(path).encode()))
 
     def stats(self):
-        out = (ctypes.c_longlong * 11)()
+        out = (ctypes.c_longlong * len(self._STATS))()
         self._lib.hctr_table_stats(self._h, out)
         return dict(zip(self._STATS, list(out)))
 
     PHASES = ("dedupe", "push_decide", "reduce", "query", "exchange", "owner_update", "stale_gather", "refresh",
-              "expand")
+              "expand", "owner_apply")
 
     def profile(self, enable=True):
         """False/0: off; True/1: time every step; k > 1: time every k-th step."""

@@ -140,7 +140,7 @@ int hctr_table_import(hctr_table *t, const char *path) {
   return guarded([&] { t->impl->importState(path); });
 }
 
-int hctr_table_stats(hctr_table *t, long long out[11]) {
+int hctr_table_stats(hctr_table *t, long long out[13]) {
   const hetuCTR::StepStats &s = t->impl->stats();
   out[0] = (long long)s.batch;
   out[1] = (long long)s.unique;
@@ -153,6 +153,8 @@ int hctr_table_stats(hctr_table *t, long long out[11]) {
   out[8] = (long long)s.received_rows;
   out[9] = (long long)t->impl->kStorageMax;
   out[10] = (long long)t->impl->kNonLocalStorageMax;
+  out[11] = (long long)s.wait_queries_us;
+  out[12] = (long long)s.wait_returns_us;
   return 0;
 }
 

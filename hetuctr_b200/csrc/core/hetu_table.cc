@@ -111,6 +111,13 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
     HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
     HCTR_CUDA(cudaStreamCreateWithPriority(&stream_reduce_side_, cudaStreamNonBlocking, hi));
   }
+  {
+    int lo = 0, hi = 0;
+    HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_apply_, cudaStreamNonBlocking, hi));
+  }
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_afork_, cudaEventDisableTiming));
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_ajoin_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_rfork_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_rjoin_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_decide_, cudaEventDisableTiming));
@@ -123,6 +130,7 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
     initComm(ip, port);
     info(*this, "communicator ready");
     initTable(root_id_arr, storage_id_arr);
+    if (p2p_) p2p_->setErr(d_err_.as<uint32_t>());
 
     int kind;
     switch (init.type) {
@@ -148,7 +156,7 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
       reserveBatch(*b, 1);
     }
     reserveShared(1);
-    h_pinned_words_ = HCTR_META_WORDS + (size_t)nrank_ + 1 + 8 * (size_t)nrank_ + 8;
+    h_pinned_words_ = HCTR_META_WORDS + (size_t)nrank_ + 1 + 12 * (size_t)nrank_ + 16;
     HCTR_CUDA(cudaMallocHost(&h_pinned_, h_pinned_words_ * sizeof(uint32_t)));
     HCTR_CUDA(cudaMallocHost(&h_src_, (size_t)nrank_ * 16 + 32));
   } catch (...) {
@@ -165,7 +173,9 @@ void HetuTable::initComm(const std::string &ip, int port) {
   const char *env = std::getenv("HCTR_EXCHANGE");
   const std::string mode = env ? env : "auto";
   HCTR_CHECK(mode == "auto" || mode == "p2p" || mode == "nccl", "HCTR_EXCHANGE must be auto, p2p or nccl");
-  if (mode != "nccl" && transport_->multiProcess()) {
+  // Thread ranks of one process (in-process transport) use their memcpy exchange unless p2p is asked for by name:
+  // the mailbox kernels then run on one GPU with a host barrier between publishing and consuming.
+  if (mode != "nccl" && (transport_->multiProcess() || mode == "p2p")) {
     p2p_ = std::make_unique<P2PMailbox>(rank_, nrank_, device_id_, kEmbeddingWidth, transport_.get());
     use_p2p_ = p2p_->usable();
     if (!use_p2p_) p2p_.reset();
@@ -271,6 +281,10 @@ void HetuTable::reserveBatch(BatchDesc &b, size_t batch) {
   b.meta.ensure((HCTR_META_WORDS + nrank_ + 1) * sizeof(uint32_t));
   b.pos_row.ensure(batch * sizeof(int32_t));
   b.heavy.ensure((batch / 32 + 2) * sizeof(uint32_t));
+  if (nrank_ > 1) {
+    b.need_push.ensure((batch + 1) * sizeof(uint32_t));
+    b.push_slot.ensure((batch + 1) * sizeof(uint32_t));
+  }
   b.capacity = batch;
 }
 
@@ -289,8 +303,6 @@ void HetuTable::reserveShared(size_t batch) {
   d_rank_.ensure(batch * sizeof(uint32_t));
   d_cnt_.ensure((batch + 1) * sizeof(uint32_t));  // all-zero between calls, like the bitmap
   HCTR_CUDA(cudaMemsetAsync(d_cnt_.p, 0, d_cnt_.bytes, stream_main_));
-  d_need_push_.ensure((batch + 1) * sizeof(uint32_t));
-  d_push_slot_.ensure((batch + 1) * sizeof(uint32_t));
   d_push_count_.ensure((size_t)nrank_ * sizeof(uint32_t));
   d_push_base_.ensure((size_t)nrank_ * sizeof(uint32_t));
   d_recv_idx_.ensure((batch + 1) * sizeof(uint32_t));
@@ -478,7 +490,7 @@ void HetuTable::launchPushDecide(BatchDesc &b) {
   int spd = tic(kPhPushDecide, stream_reduce_);
   HCTR_LAUNCH(hctr_push_decide_fused(b.meta.as<uint32_t>(), nrank_, rank_, b.unique_size, b.uniq_owner.as<uint8_t>(),
                                      b.uniq_row.as<int32_t>(), b.run_start.as<uint32_t>(), d_updates_.as<int64_t>(),
-                                     push_bound_, d_need_push_.as<uint32_t>(), d_push_slot_.as<uint32_t>(),
+                                     push_bound_, b.need_push.as<uint32_t>(), b.push_slot.as<uint32_t>(),
                                      d_chain3_.as<uint32_t>(), nextEpoch(), d_push_count_.as<uint32_t>(),
                                      d_push_base_.as<uint32_t>(), d_err_.as<uint32_t>(), stream_reduce_));
   toc(spd, stream_reduce_);
@@ -613,8 +625,8 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     r.n_heavy = prev.n_heavy;
     r.uniq = prev.uniq.as<int64_t>();
     r.uniq_row = prev.uniq_row.as<int32_t>();
-    r.need_push = n > 1 ? d_need_push_.as<uint32_t>() : nullptr;
-    r.push_slot = n > 1 ? d_push_slot_.as<uint32_t>() : nullptr;
+    r.need_push = n > 1 ? prev.need_push.as<uint32_t>() : nullptr;
+    r.push_slot = n > 1 ? prev.push_slot.as<uint32_t>() : nullptr;
     r.embedding = d_embedding_.as<float>();
     r.version = d_version_.as<int64_t>();
     r.pending = d_gradient_.as<float>();
@@ -705,11 +717,13 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
         h_start[n] = (uint32_t)off;
         HCTR_CUDA(cudaMemcpyAsync(d_src_off_.p, h_off, n * sizeof(unsigned long long), cudaMemcpyHostToDevice, stream_main_));
         HCTR_CUDA(cudaMemcpyAsync(d_src_cnt_.p, h_start, (n + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_main_));
+        d_ent_row_.ensure((push_recv + 1) * sizeof(int32_t));
         HCTR_LAUNCH(hctr_owner_update_merged(n, push_recv, W, d_pkey_r_.as<int64_t>(),
                                              d_pupd_r_.as<int64_t>(), d_pval_r_.as<float>(),
                                              d_src_off_.as<unsigned long long>(), d_src_cnt_.as<uint32_t>(),
                                              d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
-                                             d_row_mask_.as<unsigned long long>(), nextEpoch(), d_embedding_.as<float>(),
+                                             d_row_mask_.as<unsigned long long>(), nextEpoch(),
+                                             d_ent_row_.as<int32_t>(), d_embedding_.as<float>(),
                                              d_version_.as<int64_t>(), d_err_.as<uint32_t>(), stream_main_));
       } else {
         size_t off = 0;
@@ -850,16 +864,21 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   if (p2p_counts_pending_) {
     p2p_counts_pending_ = false;
     const uint32_t *h_cnt = h_pinned_ + HCTR_META_WORDS + n + 1 + 4 * n;
-    stats_.queried_keys = stats_.received_push_rows = stats_.received_rows = 0;
+    stats_.queried_keys = stats_.received_push_rows = stats_.received_rows = stats_.pushed_rows = 0;
     for (int p = 0; p < n; p++) {
       cur.query_recv[p] = h_cnt[p];
       prev.push_recv[p] = h_cnt[n + p];
       cur.ret_recv[p] = h_cnt[2 * n + p];
+      prev.push_send[p] = p2p_pushed_valid_ ? h_cnt[5 * n + 7 + p] : 0;
       stats_.queried_keys += h_cnt[p];
       stats_.received_push_rows += h_cnt[n + p];
       stats_.received_rows += h_cnt[2 * n + p];
+      stats_.pushed_rows += prev.push_send[p];
     }
-    p2p_err = h_cnt[3 * n];
+    stats_.wait_queries_us = h_cnt[HCTR_P2P_WAIT0(n)];
+    stats_.wait_returns_us = h_cnt[HCTR_P2P_WAIT1(n)];
+    stats_.returned_rows = h_cnt[HCTR_P2P_SERVED(n)];
+    p2p_err = h_cnt[6 * n + 7];
     if (p2p_err) HCTR_CUDA(cudaMemsetAsync(d_err_.p, 0, sizeof(uint32_t), stream_main_));
   }
   // The push decision for the batch just pulled runs now, while the caller computes its gradient: everything it
@@ -881,94 +900,87 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
   BatchDesc &cur = cur_batch_;
   const int n = nrank_;
   const size_t W = kEmbeddingWidth;
-  const hctr_p2p_ctx ctx_copy = [&] {
-    hctr_p2p_ctx c = p2p_->ctx();
-    c.err = d_err_.as<uint32_t>();
-    return c;
-  }();
-  const hctr_p2p_ctx *c = &ctx_copy;
+  const hctr_p2p_ctx *c = &p2p_->ctx();
   const uint32_t seq = p2p_->nextSeq();
   const size_t cap = p2p_->capacity();
   const size_t slots = (size_t)n * cap;
   const size_t u_max = cur.batch_size;  // U is only known on the device here
   const uint32_t *meta = cur.meta.as<uint32_t>();
-  d_flag32_.ensure((std::max(slots, u_max) + 1) * sizeof(uint32_t));
+  const bool split = p2p_->sameContext();  // thread ranks on one GPU: no kernel may wait for a peer's kernel
   d_ret_slot_.ensure((slots + 1) * sizeof(uint32_t));
+  d_ret_q_.ensure((slots + 1) * sizeof(uint32_t));
+  d_ret_row_.ensure((slots + 1) * sizeof(int32_t));
+  d_ent_row_.ensure((slots + 1) * sizeof(int32_t));
   d_flag_r_.ensure(u_max + 16);
-  d_retcnt_s_.ensure((size_t)n * sizeof(uint32_t));
+  {
+    const size_t before = d_chain2_.bytes;
+    d_chain2_.ensure(hctr_p2p_scan_scratch_words(std::max(slots, u_max) + 1) * sizeof(uint32_t));
+    if (d_chain2_.bytes != before)  // epoch tags must not match leftovers of an earlier allocation
+      HCTR_CUDA(cudaMemsetAsync(d_chain2_.p, 0, d_chain2_.bytes, stream_main_));
+  }
+  // In split mode every rank drains its stream after publishing and meets the others at a host barrier, so the
+  // kernel that consumes finds every sequence number in place and never polls.
+  auto meet = [&] {
+    if (!split) return;
+    HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+    p2p_->hostBarrier();
+  };
 
-  // B. queries straight into the owners' mailboxes, then publish counts + sequence number
+  // B. queries straight into the owners' mailboxes; the last thread block publishes counts + sequence number
   int sp = tic(kPhQuery);
   HCTR_LAUNCH(hctr_p2p_query_send(c, meta, u_max, cur.uniq.as<int64_t>(), cur.uniq_owner.as<uint8_t>(),
-                                  cur.uniq_row.as<int32_t>(), d_version_.as<int64_t>(), stream_main_));
+                                  cur.uniq_row.as<int32_t>(), d_version_.as<int64_t>(), seq,
+                                  prev_push_valid_ && prev_batch_.unique_size > 0 ? d_push_count_.as<uint32_t>()
+                                                                                   : nullptr,
+                                  stream_main_));
   toc(sp);
-  sp = tic(kPhExchange);
-  HCTR_LAUNCH(hctr_p2p_signal_wait(c, 0, seq, meta, prev_push_valid_ && prev_batch_.unique_size > 0
-                                                        ? d_push_count_.as<uint32_t>() : nullptr, nullptr,
-                                   stream_main_));
-  toc(sp);
+  meet();
 
   // C. owner applies the pushed rows of each source in rank order
   const hctr_p2p_box mine = p2p_->mine();
   sp = tic(kPhOwnerUpdate);
-  if (n >= 4 && n <= 32) {
-    // all sources in two launches, same per-row order as source-by-source (source s's rows are sub-region s
-    // of this rank's mailbox; the counts only exist on the device)
-    if (p2p_off_cap_ != cap) {
-      std::vector<unsigned long long> off(n);
-      for (int s = 0; s < n; s++) off[s] = (unsigned long long)s * cap;
-      HCTR_CUDA(cudaMemcpyAsync(d_src_off_.p, off.data(), n * sizeof(unsigned long long), cudaMemcpyHostToDevice,
-                                stream_main_));
-      HCTR_CUDA(cudaStreamSynchronize(stream_main_));
-      p2p_off_cap_ = cap;
-    }
-    HCTR_LAUNCH(hctr_owner_update_merged(n, cap, W, mine.pkey, mine.pupd, mine.pval,
-                                         d_src_off_.as<unsigned long long>(), c->cnt_in + 4 * n + 1, d_row_of_.as<int32_t>(),
-                                         kEmbeddingIDMax, kNonLocalStorageMax, d_row_mask_.as<unsigned long long>(),
-                                         nextEpoch(), d_embedding_.as<float>(), d_version_.as<int64_t>(),
-                                         d_err_.as<uint32_t>(), stream_main_));
-  } else if (n > 32) {
+  bool rows_forked = false;
+  if (n <= 32) {
+    // pass A waits for the peers' counts, then marks sources and finishes the versions; pass B (the rows) goes to a
+    // second stream and overlaps the staleness scan, which only reads versions
+    HCTR_LAUNCH(hctr_p2p_owner_mark(c, &mine, seq, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
+                                    d_row_mask_.as<unsigned long long>(), nextEpoch(), d_ent_row_.as<int32_t>(),
+                                    d_version_.as<int64_t>(), stream_main_));
+    toc(sp);
+    HCTR_CUDA(cudaEventRecord(ev_afork_, stream_main_));
+    HCTR_CUDA(cudaStreamWaitEvent(stream_apply_, ev_afork_, 0));
+    sp = tic(kPhOwnerApply, stream_apply_);
+    HCTR_LAUNCH(hctr_p2p_owner_apply(c, &mine, kNonLocalStorageMax, d_ent_row_.as<int32_t>(),
+                                     d_row_mask_.as<unsigned long long>(), d_embedding_.as<float>(), stream_apply_));
+    toc(sp, stream_apply_);
+    HCTR_CUDA(cudaEventRecord(ev_ajoin_, stream_apply_));
+    rows_forked = true;
+  } else {
     // more sources than a mask word holds: one cooperative launch with a grid-wide barrier between sources
+    HCTR_LAUNCH(hctr_p2p_wait(c, 0, seq, stream_main_));
     HCTR_LAUNCH(hctr_p2p_owner_update(c, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
                                       d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
-  } else {
-    for (int s = 0; s < n; s++) {
-      if (s == rank_) continue;  // a rank never pushes to itself
-      HCTR_LAUNCH(hctr_owner_update_dev(cap, c->cnt_in + n + s, W, mine.pkey + (size_t)s * cap,
-                                        mine.pupd + (size_t)s * cap, mine.pval + (size_t)s * cap * W,
-                                        d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
-                                        d_embedding_.as<float>(), d_version_.as<int64_t>(), d_err_.as<uint32_t>(),
-                                        stream_main_));
-    }
+    toc(sp);
   }
-  toc(sp);
 
   // D. staleness, per-requester counts, rows gathered into the requesters' mailboxes
-  sp = tic(kPhStaleGather);
   // flat index space: Q = all received queries (device value), at most `slots`; flags, slots and the list of
   // returned queries come out of one launch
-  {
-    const size_t before = d_chain2_.bytes;
-    d_chain2_.ensure(std::max(hctr_scan_chained_scratch_words(slots + 1), hctr_p2p_scan_scratch_words(slots)) *
-                     sizeof(uint32_t));
-    if (d_chain2_.bytes != before)  // epoch tags must not match leftovers of an earlier allocation
-      HCTR_CUDA(cudaMemsetAsync(d_chain2_.p, 0, d_chain2_.bytes, stream_main_));
-  }
-  d_ret_q_.ensure((slots + 1) * sizeof(uint32_t));
+  sp = tic(kPhStaleGather);
   HCTR_LAUNCH(hctr_p2p_stale_scan(c, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
                                   d_version_.as<int64_t>(), pull_bound_, d_ret_slot_.as<uint32_t>(),
-                                  d_ret_q_.as<uint32_t>(), d_chain2_.as<uint32_t>(), nextEpoch(), stream_main_));
-  HCTR_LAUNCH(hctr_p2p_gather_listed(c, d_ret_q_.as<uint32_t>(), d_ret_slot_.as<uint32_t>(), d_row_of_.as<int32_t>(),
-                                     d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
+                                  d_ret_q_.as<uint32_t>(), d_ret_row_.as<int32_t>(), d_chain2_.as<uint32_t>(),
+                                  nextEpoch(), stream_main_));
+  if (rows_forked) HCTR_CUDA(cudaStreamWaitEvent(stream_main_, ev_ajoin_, 0));  // the gather reads updated rows
+  HCTR_LAUNCH(hctr_p2p_gather(c, seq, d_ret_q_.as<uint32_t>(), d_ret_row_.as<int32_t>(), d_ret_slot_.as<uint32_t>(),
+                              d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
   toc(sp);
-  sp = tic(kPhExchange);
-  HCTR_LAUNCH(hctr_p2p_signal_wait(c, 1, seq, meta, nullptr, d_ret_slot_.as<uint32_t>(), stream_main_));
-  toc(sp);
+  meet();
 
-  // E. requester: flags -> row indices in its own mailbox, cache refresh, expand
+  // E. requester: wait for the owners, flags -> row indices in its own mailbox, cache refresh, expand
   sp = tic(kPhRefresh);
-  HCTR_LAUNCH(hctr_p2p_recv_scan(c, meta, u_max, cur.uniq_owner.as<uint8_t>(), d_flag_r_.as<uint8_t>(),
-                                 d_recv_idx_.as<uint32_t>(), d_chain_.as<uint32_t>(), nextEpoch(), stream_main_));
+  HCTR_LAUNCH(hctr_p2p_recv_scan(c, seq, meta, u_max, cur.uniq_owner.as<uint8_t>(), d_flag_r_.as<uint8_t>(),
+                                 d_recv_idx_.as<uint32_t>(), d_chain2_.as<uint32_t>(), nextEpoch(), stream_main_));
   HCTR_LAUNCH(hctr_cache_refresh(u_max, W, d_flag_r_.as<uint8_t>(), d_recv_idx_.as<uint32_t>(),
                                  cur.uniq_row.as<int32_t>(), mine.rval, mine.rver, d_gradient_.as<float>(),
                                  d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
@@ -978,11 +990,13 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
                                d_recv_idx_.as<uint32_t>(), mine.rval, d_embedding_.as<float>(), dst_dev, d_err_.as<uint32_t>() + 8, stream_main_));
   toc(sp);
 
-  // counts and the error word come back with the step's final synchronisation
-  uint32_t *h_cnt = h_pinned_ + HCTR_META_WORDS + n + 1 + 4 * n;  // [3n] + error word
-  HCTR_CUDA(cudaMemcpyAsync(h_cnt, c->cnt_in, 3 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
-  HCTR_CUDA(cudaMemcpyAsync(h_cnt + 3 * n, d_err_.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+  // counts, wait times and the error word come back with the step's final synchronisation
+  uint32_t *h_cnt = h_pinned_ + HCTR_META_WORDS + n + 1 + 4 * n;  // [5n+7] + [n] push counts + error word
+  HCTR_CUDA(cudaMemcpyAsync(h_cnt, c->cnt_in, (5 * n + 7) * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+  HCTR_CUDA(cudaMemcpyAsync(h_cnt + 5 * n + 7, d_push_count_.p, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+  HCTR_CUDA(cudaMemcpyAsync(h_cnt + 6 * n + 7, d_err_.p, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
   p2p_counts_pending_ = true;
+  p2p_pushed_valid_ = prev_push_valid_ && prev_batch_.unique_size > 0;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -1127,7 +1141,7 @@ long long HetuTable::dump(const std::string &what, bool prev, void *out) {
   if (what == "push_shape_exchanged") return copy_sizes(b.push_recv, nrank_, out);
   if (what == "return_shape") return copy_sizes(b.ret_send, nrank_, out);
   if (what == "return_shape_exchanged") return copy_sizes(b.ret_recv, nrank_, out);
-  if (what == "need_update") return copy_widen<uint32_t>(d_need_push_.p, prev_batch_.unique_size, out, s);
+  if (what == "need_update") return copy_widen<uint32_t>(prev_batch_.need_push.p, nrank_ > 1 ? prev_batch_.unique_size : 0, out, s);
   if (what == "version") return copy_widen<long long>(d_version_.p, kStorageMax, out, s);
   if (what == "updates") return copy_widen<long long>(d_updates_.p, kNonLocalStorageMax, out, s);
   if (what == "stored_keys") return copy_widen<long long>(d_stored_keys_.p, kStorageMax, out, s);
@@ -1173,13 +1187,14 @@ void HetuTable::releaseAll() {
   cudaSetDevice(device_id_);
   if (stream_side_) cudaStreamSynchronize(stream_side_);
   if (stream_reduce_side_) cudaStreamSynchronize(stream_reduce_side_);
+  if (stream_apply_) cudaStreamSynchronize(stream_apply_);
   if (stream_reduce_) cudaStreamSynchronize(stream_reduce_);
   if (stream_main_) cudaStreamSynchronize(stream_main_);
   p2p_.reset();
   transport_.reset();
   DevBuf *all[] = {&d_embedding_, &d_gradient_, &d_updates_, &d_version_, &d_root_, &d_row_of_, &d_stored_keys_,
-                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_chain_, &d_chain2_, &d_chain3_, &d_ret_q_, &d_row_mask_, &d_src_off_, &d_src_cnt_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_cnt_,
-                   &d_need_push_, &d_push_slot_, &d_push_count_, &d_push_base_, &d_recv_idx_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
+                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_chain_, &d_chain2_, &d_chain3_, &d_ret_q_, &d_ret_row_, &d_ent_row_, &d_row_mask_, &d_src_off_, &d_src_cnt_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_cnt_,
+                   &d_push_count_, &d_push_base_, &d_recv_idx_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
                    &d_qkey_r_, &d_qver_r_, &d_pkey_s_, &d_pupd_s_, &d_pval_s_, &d_pkey_r_, &d_pupd_r_, &d_pval_r_,
                    &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,
                    &d_retcnt_r_, &d_rver_s_, &d_rval_s_, &d_rver_r_, &d_rval_r_, &d_stage_grad_, &d_stage_dst_};
@@ -1190,7 +1205,7 @@ void HetuTable::releaseAll() {
   }
   for (BatchDesc *b : {&cur_batch_, &prev_batch_})
     for (DevBuf *d : {&b->keys, &b->idx_map, &b->sorted_pos, &b->uniq, &b->uniq_owner, &b->uniq_row,
-                      &b->run_start, &b->meta, &b->pos_row, &b->heavy})
+                      &b->run_start, &b->meta, &b->pos_row, &b->heavy, &b->need_push, &b->push_slot})
       d->release();
   for (Span &sp : spans_) {
     cudaEventDestroy(sp.a);
@@ -1211,6 +1226,11 @@ void HetuTable::releaseAll() {
   if (ev_rfork_) cudaEventDestroy(ev_rfork_);
   if (ev_rjoin_) cudaEventDestroy(ev_rjoin_);
   ev_decide_ = ev_reduce_ = ev_rfork_ = ev_rjoin_ = nullptr;
+  if (ev_afork_) cudaEventDestroy(ev_afork_);
+  if (ev_ajoin_) cudaEventDestroy(ev_ajoin_);
+  ev_afork_ = ev_ajoin_ = nullptr;
+  if (stream_apply_) cudaStreamDestroy(stream_apply_);
+  stream_apply_ = nullptr;
   if (stream_reduce_side_) cudaStreamDestroy(stream_reduce_side_);
   stream_reduce_side_ = nullptr;
   if (stream_reduce_) cudaStreamDestroy(stream_reduce_);

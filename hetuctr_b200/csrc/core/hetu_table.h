@@ -65,6 +65,10 @@ struct BatchDesc {
   bool order_pending = false;      // the run-ordering kernels of this batch are not enqueued yet
   hctr_dedupe_args order_args;     // what they will be launched with
   DevBuf keys, idx_map, sorted_pos, uniq, uniq_owner, uniq_row, run_start, meta, pos_row, heavy;
+  // Push decision of this batch (multi-rank tables): flag and send slot per unique key.  They belong to the batch
+  // because the decision is taken at the end of the batch's own push_pull and consumed by the next one; a larger
+  // batch arriving in between must not move them.
+  DevBuf need_push, push_slot;
   std::vector<size_t> seg;         // [n+1] first unique of each owner
   std::vector<size_t> query_send;  // [n] unique keys addressed to each owner
   std::vector<size_t> query_recv;  // [n] keys each requester sends to me
@@ -77,6 +81,8 @@ struct BatchDesc {
 struct StepStats {  // sizes of the last push_pull, for roofline arithmetic
   size_t batch = 0, unique = 0, prev_batch = 0, prev_unique = 0;
   size_t pushed_rows = 0, received_push_rows = 0, queried_keys = 0, returned_rows = 0, received_rows = 0;
+  // peer-to-peer exchange: longest in-kernel wait of the step for a peer's queries / returned rows (peer skew)
+  size_t wait_queries_us = 0, wait_returns_us = 0;
 };
 
 // Phases timed with CUDA events on the table's stream when profiling is enabled.
@@ -86,10 +92,11 @@ enum Phase {
   kPhReduce,          // hctr_grad_reduce_apply_pack
   kPhQuery,           // hctr_query_versions
   kPhExchange,        // transport groups (all of a step)
-  kPhOwnerUpdate,     // hctr_owner_update (all sources)
+  kPhOwnerUpdate,     // hctr_owner_update (all sources); peer-to-peer: wait for the peers + sources and versions
   kPhStaleGather,     // hctr_stale_check + hctr_gather_rows
   kPhRefresh,         // hctr_recv_slots + hctr_cache_refresh
   kPhExpand,          // hctr_expand_rows
+  kPhOwnerApply,      // peer-to-peer: row pass of the owner update (second stream, overlaps the staleness scan)
   kPhCount
 };
 
@@ -174,12 +181,15 @@ class HetuTable {
   // reads updated rows or versions.
   cudaStream_t stream_reduce_ = nullptr;
   cudaStream_t stream_reduce_side_ = nullptr;  // long-run reduce kernel, forked from stream_reduce_
+  cudaStream_t stream_apply_ = nullptr;        // row pass of the owner update (peer-to-peer exchange)
+  cudaEvent_t ev_afork_ = nullptr, ev_ajoin_ = nullptr;
   cudaEvent_t ev_decide_ = nullptr, ev_reduce_ = nullptr, ev_rfork_ = nullptr, ev_rjoin_ = nullptr;
   cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr, ev_keys_ = nullptr;
   std::unique_ptr<Transport> transport_;
   std::unique_ptr<P2PMailbox> p2p_;  // device-driven exchange (one process per GPU, peer access); else NCCL groups
   bool use_p2p_ = false;
   bool p2p_counts_pending_ = false;
+  bool p2p_pushed_valid_ = false;    // the push counts read back with the step describe a real previous batch
   bool expand_bulk_ = false;         // HCTR_EXPAND=bulk
   // Field count of the (sample-major) key batches, used to give every warp of the dedupe kernels one field of
   // 32 consecutive samples: HCTR_KEY_STRIDE = auto (default: found from the first large batch) or a number
@@ -195,8 +205,8 @@ class HetuTable {
   size_t length_pad_ = 0;
 
   // dedupe scratch (persistent, all-zero between calls) and per-step scratch
-  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_row_mask_, d_src_off_, d_src_cnt_, d_word_base_, d_scan_, d_sk_, d_rank_, d_cnt_;
-  DevBuf d_need_push_, d_push_slot_, d_push_count_, d_push_base_, d_recv_idx_, d_err_;
+  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_ret_row_, d_ent_row_, d_row_mask_, d_src_off_, d_src_cnt_, d_word_base_, d_scan_, d_sk_, d_rank_, d_cnt_;
+  DevBuf d_push_count_, d_push_base_, d_recv_idx_, d_err_;
   size_t shared_capacity_ = 0;
   uint32_t dedupe_epoch_ = 0;
   uint32_t nextEpoch() { return ++dedupe_epoch_ ? dedupe_epoch_ : ++dedupe_epoch_; }  // never 0

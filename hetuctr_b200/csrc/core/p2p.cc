@@ -19,11 +19,16 @@ P2PMailbox::P2PMailbox(int rank, int nrank, int device_id, size_t width, Transpo
   // map every other rank's device memory (same NVLink domain, peer access possible).
   std::vector<int> devs(nrank_, -1);
   bootstrap_->allgatherHost(&device_id_, devs.data(), sizeof(int));
+  same_context_ = !bootstrap_->multiProcess();
   int ok = 1;
   for (int p = 0; p < nrank_; p++) {
     if (p == rank_) continue;
+    if (same_context_) {
+      if (devs[p] != device_id_) ok = 0;  // thread ranks share mailboxes by plain pointer: one device only
+      continue;
+    }
     if (devs[p] == device_id_) {
-      ok = 0;  // two ranks on one GPU: their wait kernels could starve each other
+      ok = 0;  // two processes on one GPU: their wait kernels could starve each other
       continue;
     }
     int can = 0;
@@ -37,7 +42,20 @@ P2PMailbox::P2PMailbox(int rank, int nrank, int device_id, size_t width, Transpo
   ctx_.rank = rank_;
   ctx_.width = width_;
   ctx_.timeout_ns = 10ull * 1000 * 1000 * 1000;
-  if (const char *e = std::getenv("HCTR_P2P_TIMEOUT_MS")) ctx_.timeout_ns = std::strtoull(e, nullptr, 10) * 1000000ull;
+  if (const char *e = std::getenv("HCTR_P2P_TIMEOUT_MS")) {
+    // an unparsable value must not turn into 0 (every wait would give up at once) and a huge one must not make the
+    // device-side poll unbounded in practice
+    char *end = nullptr;
+    const unsigned long long ms = std::strtoull(e, &end, 10);
+    HCTR_CHECK(end != e && *end == 0 && ms >= 1 && ms <= 60000, "HCTR_P2P_TIMEOUT_MS must be a number of milliseconds in [1, 60000]");
+    ctx_.timeout_ns = ms * 1000000ull;
+  }
+}
+
+void P2PMailbox::hostBarrier() {
+  int token = 0;
+  std::vector<int> tokens(nrank_);
+  bootstrap_->allgatherHost(&token, tokens.data(), sizeof(int));
 }
 
 size_t P2PMailbox::bytesFor(size_t cap) const {
@@ -77,7 +95,7 @@ hctr_p2p_box P2PMailbox::carve(char *base) const {
 
 void P2PMailbox::releaseMappings() {
   for (int p = 0; p < nrank_; p++) {
-    if (p != rank_ && mapped_[p]) cudaIpcCloseMemHandle(mapped_[p]);
+    if (p != rank_ && mapped_[p] && !same_context_) cudaIpcCloseMemHandle(mapped_[p]);
     mapped_[p] = nullptr;
   }
   if (mine_) cudaFree(mine_);
@@ -89,6 +107,7 @@ void P2PMailbox::reserve(size_t cap, cudaStream_t stream) {
   HCTR_CHECK(usable_, "peer-to-peer exchange is not usable on this set of devices");
   HCTR_CHECK(cap < (size_t)1 << 31, "batch too large for the peer-to-peer exchange");
   HCTR_CUDA(cudaStreamSynchronize(stream));
+  if (same_context_) hostBarrier();  // thread ranks: nobody frees a mailbox while a peer's last step still runs
   // Every rank has finished the step that last used the old mailboxes before it gets here (a step only
   // ends after all peers' rows for it have arrived), so they can be unmapped and freed.
   releaseMappings();
@@ -97,25 +116,31 @@ void P2PMailbox::reserve(size_t cap, cudaStream_t stream) {
   HCTR_CUDA(cudaMalloc(reinterpret_cast<void **>(&mine_), bytes));
   HCTR_CUDA(cudaMemset(mine_, 0, bytes));  // sequence numbers start at 0
   HCTR_CUDA(cudaDeviceSynchronize());
-  cudaIpcMemHandle_t h;
-  HCTR_CUDA(cudaIpcGetMemHandle(&h, mine_));
-  std::vector<cudaIpcMemHandle_t> all(nrank_);
-  bootstrap_->allgatherHost(&h, all.data(), sizeof(h));  // also a barrier: every mailbox is zeroed by now
   std::vector<hctr_p2p_box> boxes(nrank_);
-  for (int p = 0; p < nrank_; p++) {
-    if (p == rank_) {
-      mapped_[p] = mine_;
-    } else {
-      void *ptr = nullptr;
-      HCTR_CUDA(cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess));
-      mapped_[p] = static_cast<char *>(ptr);
+  if (same_context_) {
+    std::vector<char *> all(nrank_);
+    bootstrap_->allgatherHost(&mine_, all.data(), sizeof(char *));  // also a barrier: every mailbox is zeroed by now
+    for (int p = 0; p < nrank_; p++) mapped_[p] = all[p];
+  } else {
+    cudaIpcMemHandle_t h;
+    HCTR_CUDA(cudaIpcGetMemHandle(&h, mine_));
+    std::vector<cudaIpcMemHandle_t> all(nrank_);
+    bootstrap_->allgatherHost(&h, all.data(), sizeof(h));  // also a barrier: every mailbox is zeroed by now
+    for (int p = 0; p < nrank_; p++) {
+      if (p == rank_) {
+        mapped_[p] = mine_;
+      } else {
+        void *ptr = nullptr;
+        HCTR_CUDA(cudaIpcOpenMemHandle(&ptr, all[p], cudaIpcMemLazyEnablePeerAccess));
+        mapped_[p] = static_cast<char *>(ptr);
+      }
     }
-    boxes[p] = carve(mapped_[p]);
   }
+  for (int p = 0; p < nrank_; p++) boxes[p] = carve(mapped_[p]);
   if (!d_boxes_) HCTR_CUDA(cudaMalloc(reinterpret_cast<void **>(&d_boxes_), nrank_ * sizeof(hctr_p2p_box)));
   if (!d_cnt_in_) {
-    HCTR_CUDA(cudaMalloc(reinterpret_cast<void **>(&d_cnt_in_), (5 * nrank_ + 2) * sizeof(uint32_t)));
-    HCTR_CUDA(cudaMemset(d_cnt_in_, 0, (5 * nrank_ + 2) * sizeof(uint32_t)));
+    HCTR_CUDA(cudaMalloc(reinterpret_cast<void **>(&d_cnt_in_), HCTR_P2P_CNT_WORDS(nrank_) * sizeof(uint32_t)));
+    HCTR_CUDA(cudaMemset(d_cnt_in_, 0, HCTR_P2P_CNT_WORDS(nrank_) * sizeof(uint32_t)));
   }
   HCTR_CUDA(cudaMemcpy(d_boxes_, boxes.data(), nrank_ * sizeof(hctr_p2p_box), cudaMemcpyHostToDevice));
   mine_box_ = boxes[rank_];

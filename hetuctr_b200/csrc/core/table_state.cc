@@ -11,6 +11,8 @@
 #include <stdexcept>
 #include <string>
 
+#include <unistd.h>
+
 #include "core/hetu_table.h"
 #include "utils/errors.h"
 
@@ -69,7 +71,7 @@ void HetuTable::quiesce() {
   HCTR_CUDA(cudaSetDevice(device_id_));
   finalizePending();
   flushOrdering(cur_batch_);
-  for (cudaStream_t s : {stream_main_, stream_side_, stream_reduce_, stream_reduce_side_})
+  for (cudaStream_t s : {stream_main_, stream_side_, stream_reduce_, stream_reduce_side_, stream_apply_})
     if (s) HCTR_CUDA(cudaStreamSynchronize(s));
 }
 
@@ -86,7 +88,10 @@ void HetuTable::exportState(const std::string &path) {
   h.cached = (int64_t)C;
   h.pull_bound = pull_bound_;
   h.push_bound = push_bound_;
-  File out(path, "wb");
+  // Written beside the target and renamed over it at the end: a crash or a full disk half-way leaves the previous
+  // file of that name intact instead of a truncated one.
+  const std::string tmp = path + ".tmp";
+  File out(tmp, "wb");
   out.write(&h, sizeof(h));
   Pinned stage;
   auto section = [&](const void *dev, size_t bytes) {
@@ -103,8 +108,11 @@ void HetuTable::exportState(const std::string &path) {
   section(d_updates_.p, C * sizeof(version_t));
   section(d_gradient_.p, C * W * sizeof(embed_t));
   const uint64_t sum = out.hash;
-  if (std::fwrite(&sum, 1, sizeof(sum), out.f) != sizeof(sum) || std::fflush(out.f) != 0)
-    throw std::runtime_error("short write to " + path);
+  if (std::fwrite(&sum, 1, sizeof(sum), out.f) != sizeof(sum) || std::fflush(out.f) != 0 || fsync(fileno(out.f)) != 0)
+    throw std::runtime_error("short write to " + tmp);
+  std::fclose(out.f);
+  out.f = nullptr;
+  if (std::rename(tmp.c_str(), path.c_str()) != 0) throw std::runtime_error("cannot rename " + tmp + " to " + path);
 }
 
 void HetuTable::importState(const std::string &path) {

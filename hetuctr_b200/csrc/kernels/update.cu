@@ -5,6 +5,7 @@
 #include <algorithm>
 #include <cstring>
 
+#include "p2p.cuh"
 #include "rowops.cuh"
 
 namespace hctr {
@@ -716,21 +717,28 @@ __global__ void __launch_bounds__(kThreads) owner_update(size_t n_rows_max, cons
 
 // ---- owner-side apply of all sources, order-preserving, two launches ------------------------------
 // The reference applies the sources one after the other because two sources may push the same row
-// and fp32 adds must happen in a fixed order.  Here pass A records, per owned row, WHICH sources push it
-// (one bit per source); pass B lets the lowest such source apply every contribution to the row in
-// ascending source order.  Each source's list is sorted by key (it is a slice of that source's unique
-// list), so the other sources' entries are found by binary search - only for the few rows that really
-// have several pushers.  Same arithmetic and order as source-by-source launches, hence bit-identical.
+// and fp32 adds must happen in a fixed order.  Here pass A (mark) records, per owned row, WHICH sources push it
+// (one bit per source) and adds every entry's update count to the row's version - integer adds commute, so the
+// versions are final after pass A and the owner's staleness test can start while pass B still moves rows.  Pass B
+// (apply) lets the lowest source of each row add every contribution to the row in ascending source order.  Each
+// source's list is sorted by key (it is a slice of that source's unique list), so the other sources' entries are
+// found by binary search, all of them at once: one lane of the row's lane group per source.  Same arithmetic
+// and order as source-by-source launches, hence bit-identical.
 // A mask word is [epoch:32 | source bits:32]; bits under an older epoch count as empty, so nothing has to be
 // cleared between steps (clearing inside pass B would race with the readers of the same word).
 struct PushLists {  // where every source's pushed rows are, as seen by the owner
   const long long *key;
   const long long *upd;
   const float *val;
-  const unsigned long long *src_off;  // device [nsrc]: first entry of source s in key/upd/val
+  const unsigned long long *src_off;  // device [nsrc]: first entry of source s in key/upd/val; null: s * src_stride
+  size_t src_stride;
   const u32 *flat_start;              // device [nsrc+1]: exclusive prefix of the per-source row counts
   int nsrc;
 };
+
+__device__ __forceinline__ size_t push_list_base(const PushLists &p, int s) {
+  return p.src_off ? (size_t)p.src_off[s] : (size_t)s * p.src_stride;
+}
 
 __device__ __forceinline__ int32_t owned_row(const int32_t *row_of, size_t length, size_t n_cached, long long k) {
   int32_t row = -1;
@@ -738,32 +746,35 @@ __device__ __forceinline__ int32_t owned_row(const int32_t *row_of, size_t lengt
   return (row < 0 || (size_t)row < n_cached) ? -1 : row;
 }
 
-// flat row index f in [0, total) -> source
-__device__ __forceinline__ int push_source(const u32 *start, int nsrc, u32 f) {
-  int lo = 0, hi = nsrc;  // start[lo] <= f < start[hi]
-  while (hi - lo > 1) {
-    const int mid = (lo + hi) >> 1;
-    if (start[mid] <= f) lo = mid;
-    else hi = mid;
+// Pass A.  ent_row[f] = owned row of flat entry f, or -1 (reported through err).  With WAIT the kernel first waits
+// (bounded) for the peers' counts of this step (peer-to-peer exchange: the lists are the sub-regions of this rank's
+// mailbox) and block 0 records them for the kernels that follow.
+template <bool WAIT>
+__global__ void __launch_bounds__(kThreads) owner_mark_sources(PushLists p, hctr_p2p_ctx c, u32 seq,
+                                                               const int32_t *__restrict__ row_of, size_t length,
+                                                               size_t n_cached, u64 *__restrict__ mask, u32 epoch,
+                                                               int32_t *__restrict__ ent_row,
+                                                               long long *__restrict__ version, u32 *err) {
+  __shared__ u32 start[kMaxRanks + 1];
+  if (WAIT) {
+    __shared__ u32 qstart[kMaxRanks + 1];
+    wait_queries(c, seq, qstart, start, blockIdx.x == 0);
+  } else {
+    for (int i = threadIdx.x; i <= p.nsrc; i += kThreads) start[i] = p.flat_start[i];
+    __syncthreads();
   }
-  return lo;
-}
-
-__global__ void __launch_bounds__(kThreads) owner_mark_sources(PushLists p, const int32_t *__restrict__ row_of,
-                                                               size_t length, size_t n_cached, u64 *__restrict__ mask,
-                                                               u32 epoch, u32 *err) {
-  __shared__ u32 start[33];
-  if (threadIdx.x <= (unsigned)p.nsrc) start[threadIdx.x] = p.flat_start[threadIdx.x];
-  __syncthreads();
   const u32 total = start[p.nsrc];
   for (size_t f = (size_t)blockIdx.x * kThreads + threadIdx.x; f < total; f += (size_t)gridDim.x * kThreads) {
-    const int s = push_source(start, p.nsrc, (u32)f);
-    const long long k = p.key[p.src_off[s] + (f - start[s])];
+    const int s = (int)segment_of(start, p.nsrc, (u32)f);
+    const size_t ent = push_list_base(p, s) + (f - start[s]);
+    const long long k = p.key[ent];
     const int32_t row = owned_row(row_of, length, n_cached, k);
+    ent_row[f] = row;
     if (row < 0) {
       atomicOr(err, HCTR_ERR_NOT_OWNER);
       continue;
     }
+    atomicAdd(reinterpret_cast<u64 *>(version) + row, (u64)p.upd[ent]);
     u64 *w = &mask[(size_t)row - n_cached];
     u64 old = *w;
     for (;;) {  // terminates: at most nsrc writers per word, each CAS failure means another one got through
@@ -777,7 +788,7 @@ __global__ void __launch_bounds__(kThreads) owner_mark_sources(PushLists p, cons
 
 // entry of key k in source s2's key-sorted list
 __device__ __forceinline__ size_t push_entry_of(const PushLists &p, const u32 *start, int s2, long long k) {
-  const size_t off2 = p.src_off[s2];
+  const size_t off2 = push_list_base(p, s2);
   size_t lo = 0, hi = start[s2 + 1] - start[s2];
   while (lo < hi) {
     const size_t mid = (lo + hi) >> 1;
@@ -787,17 +798,12 @@ __device__ __forceinline__ size_t push_entry_of(const PushLists &p, const u32 *s
   return off2 + lo;
 }
 
-// A group of LANES lanes takes kApplyRows pushed rows per iteration and issues the loads of all of them before
-// it uses any: keys, then row numbers, then source masks, then the table rows and pushed rows themselves, so
-// that four chains of dependent memory accesses overlap instead of one.
-constexpr int kApplyRows = 4;
-
+// Pass B.  One group of LANES lanes per pushed entry; the group of a row's lowest source adds all contributions.
 template <int LANES, bool VEC>
-__global__ void __launch_bounds__(kThreads) owner_apply_sources(PushLists p, size_t width,
-                                                                const int32_t *__restrict__ row_of, size_t length,
-                                                                size_t n_cached, const u64 *__restrict__ mask,
-                                                                float *__restrict__ embedding,
-                                                                long long *__restrict__ version) {
+__global__ void __launch_bounds__(kThreads) owner_apply_sources(PushLists p, size_t width, size_t n_cached,
+                                                                const int32_t *__restrict__ ent_row,
+                                                                const u64 *__restrict__ mask,
+                                                                float *__restrict__ embedding) {
   typedef RowT<VEC> R;
   typedef typename R::T T;
   __shared__ u32 start[33];
@@ -805,65 +811,54 @@ __global__ void __launch_bounds__(kThreads) owner_apply_sources(PushLists p, siz
   __syncthreads();
   const u32 total = start[p.nsrc];
   const unsigned gl = threadIdx.x % LANES;
+  // lanes of this group inside its warp, for the shuffles
+  const unsigned gmask = LANES == 32 ? 0xffffffffu : ((1u << LANES) - 1u) << ((threadIdx.x & 31u) / LANES * LANES);
   const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
   const size_t E = R::elems(width);
-  for (size_t f0 = (((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES) * kApplyRows; f0 < total;
-       f0 += groups * kApplyRows) {
-    int src[kApplyRows];
-    size_t ent[kApplyRows];
-    long long key[kApplyRows];
-    int32_t row[kApplyRows];
-    u64 rest[kApplyRows];
-#pragma unroll
-    for (int r = 0; r < kApplyRows; r++) {
-      const size_t f = f0 + r;
-      src[r] = -1;
-      key[r] = -1;
-      if (f < total) {
-        src[r] = push_source(start, p.nsrc, (u32)f);
-        ent[r] = p.src_off[src[r]] + (f - start[src[r]]);
-        key[r] = p.key[ent[r]];
-      }
+  const T *val = reinterpret_cast<const T *>(p.val);
+  for (size_t f = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; f < total; f += groups) {
+    const int32_t row = ent_row[f];
+    if (row < 0) continue;  // not owned here: reported by pass A
+    const int s = (int)segment_of(start, p.nsrc, (u32)f);
+    const u32 mk = (u32)mask[(size_t)row - n_cached];  // this step's epoch, set by pass A
+    if (mk & ((1u << s) - 1u)) continue;                // a lower source pushes this row too: it applies everything
+    u32 rest = mk & ~((2u << s) - 1u);                  // higher sources that also push it
+    const size_t ent = push_list_base(p, s) + (f - start[s]);
+    T *emb = reinterpret_cast<T *>(embedding) + (size_t)row * E;
+    if (rest == 0) {
+      for (size_t e = gl; e < E; e += LANES) emb[e] = R::add(emb[e], R::ld_once(val + ent * E + e));
+      continue;
     }
-#pragma unroll
-    for (int r = 0; r < kApplyRows; r++) row[r] = src[r] >= 0 ? owned_row(row_of, length, n_cached, key[r]) : -1;
-#pragma unroll
-    for (int r = 0; r < kApplyRows; r++) {
-      rest[r] = 0;
-      if (row[r] >= 0) {  // rows that are not owned here were reported by the marking pass
-        const u64 mk = mask[(size_t)row[r] - n_cached] & 0xffffffffull;  // this step's epoch, set by the marking pass
-        if (mk & ((1ull << src[r]) - 1)) row[r] = -1;  // a lower source pushes this row too: it applies everything
-        else rest[r] = (mk >> (src[r] + 1)) << (src[r] + 1);  // higher sources that also push it
-      }
-    }
-    for (size_t e = gl; e < E; e += LANES) {
-      T acc[kApplyRows], v[kApplyRows];
-#pragma unroll
-      for (int r = 0; r < kApplyRows; r++) {
-        if (row[r] >= 0) {
-          acc[r] = reinterpret_cast<const T *>(embedding)[(size_t)row[r] * E + e];
-          v[r] = R::ld_once(reinterpret_cast<const T *>(p.val) + ent[r] * E + e);
+    const long long key = p.key[ent];
+    bool first = true;
+    while (rest) {
+      // up to LANES further sources per round: lane j finds the entry of the j-th of them
+      const int cnt = min(__popc(rest), LANES);
+      size_t mine = 0;
+      if ((int)gl < cnt) mine = push_entry_of(p, start, (int)__fns(rest, 0, (int)gl + 1), key);
+      for (int j = 0; j < cnt; j++) rest &= rest - 1;
+      for (size_t e0 = 0; e0 < E; e0 += LANES) {  // same trip count in every lane: the loop body shuffles
+        const size_t e = e0 + gl;
+        const bool act = e < E;
+        T acc = R::zero();
+        if (act) {
+          acc = emb[e];
+          if (first) acc = R::add(acc, R::ld_once(val + ent * E + e));
         }
-      }
+        for (int j0 = 0; j0 < cnt; j0 += 4) {  // ascending source order, as source-by-source launches would
+          T v[4];
 #pragma unroll
-      for (int r = 0; r < kApplyRows; r++) {
-        if (row[r] < 0) continue;
-        acc[r] = R::add(acc[r], v[r]);
-        for (u64 m = rest[r]; m; m &= m - 1) {  // ascending source order, as source-by-source launches would
-          const size_t ent2 = push_entry_of(p, start, __ffsll((long long)m) - 1, key[r]);
-          acc[r] = R::add(acc[r], R::ld_once(reinterpret_cast<const T *>(p.val) + ent2 * E + e));
+          for (int j = 0; j < 4; j++) {
+            const size_t ej = __shfl_sync(gmask, mine, (j0 + j) % LANES, LANES);
+            if (act && j0 + j < cnt) v[j] = R::ld_once(val + ej * E + e);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; j++)
+            if (act && j0 + j < cnt) acc = R::add(acc, v[j]);
         }
-        reinterpret_cast<T *>(embedding)[(size_t)row[r] * E + e] = acc[r];
+        if (act) emb[e] = acc;
       }
-    }
-    if (gl == 0) {
-#pragma unroll
-      for (int r = 0; r < kApplyRows; r++) {
-        if (row[r] < 0) continue;
-        long long ver_add = p.upd[ent[r]];
-        for (u64 m = rest[r]; m; m &= m - 1) ver_add += p.upd[push_entry_of(p, start, __ffsll((long long)m) - 1, key[r])];
-        version[row[r]] = (long long)((u64)version[row[r]] + (u64)ver_add);
-      }
+      first = false;
     }
   }
 }
@@ -912,11 +907,34 @@ __global__ void __launch_bounds__(kThreads) owner_update_all(hctr_p2p_ctx c, con
 
 using namespace hctr;
 
+static int launch_owner_apply(const PushLists &p, size_t rows_hint, size_t width, size_t n_cached,
+                              const int32_t *ent_row, const unsigned long long *row_mask, float *embedding,
+                              cudaStream_t st) {
+  const bool al = host_aligned16(p.val) && host_aligned16(embedding);
+#define CALL(L, V)                                                                                                \
+  do {                                                                                                            \
+    size_t g_ = (rows_hint * L + kThreads - 1) / kThreads;                                                        \
+    if (g_ > (size_t)kSMs * 8) g_ = (size_t)kSMs * 8;                                                             \
+    owner_apply_sources<L, V><<<(unsigned)g_, kThreads, 0, st>>>(p, width, n_cached, ent_row, row_mask, embedding); \
+  } while (0)
+  HCTR_DISPATCH_ROWS(width, al, CALL);
+#undef CALL
+  count_launches(1);
+  return launch_status();
+}
+
+static unsigned mark_grid(size_t rows_hint) {
+  size_t g = (rows_hint + kThreads - 1) / kThreads;
+  if (g > (size_t)kSMs * 8) g = (size_t)kSMs * 8;
+  return (unsigned)(g ? g : 1);
+}
+
 extern "C" int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width, const int64_t *key,
                                         const int64_t *updates, const float *val, const unsigned long long *src_off,
                                         const uint32_t *flat_start, const int32_t *row_of, size_t length,
                                         size_t n_cached, unsigned long long *row_mask, uint32_t epoch,
-                                        float *embedding, int64_t *version, uint32_t *err, void *stream) {
+                                        int32_t *ent_row, float *embedding, int64_t *version, uint32_t *err,
+                                        void *stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (nsrc > 32 || epoch == 0) return (int)cudaErrorInvalidValue;
   if (rows_hint == 0) return 0;
@@ -925,23 +943,47 @@ extern "C" int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width
   p.upd = (const long long *)updates;
   p.val = val;
   p.src_off = src_off;
+  p.src_stride = 0;
   p.flat_start = flat_start;
   p.nsrc = nsrc;
-  size_t g = (rows_hint + kThreads - 1) / kThreads;
-  if (g > (size_t)kSMs * 8) g = (size_t)kSMs * 8;
-  owner_mark_sources<<<(unsigned)g, kThreads, 0, st>>>(p, row_of, length, n_cached, row_mask, epoch, err);
-  const bool al = host_aligned16(val) && host_aligned16(embedding);
-#define CALL(L, V)                                                                                    \
-  do {                                                                                                \
-    size_t g_ = ((rows_hint + kApplyRows - 1) / kApplyRows * L + kThreads - 1) / kThreads;            \
-    if (g_ > (size_t)kSMs * 8) g_ = (size_t)kSMs * 8;                                                 \
-    owner_apply_sources<L, V><<<(unsigned)g_, kThreads, 0, st>>>(p, width, row_of, length, n_cached,  \
-                                                                 row_mask, embedding, (long long *)version); \
-  } while (0)
-  HCTR_DISPATCH_ROWS(width, al, CALL);
-#undef CALL
-  count_launches(2);
+  hctr_p2p_ctx none;
+  memset(&none, 0, sizeof(none));
+  owner_mark_sources<false><<<mark_grid(rows_hint), kThreads, 0, st>>>(p, none, 0u, row_of, length, n_cached, row_mask,
+                                                                      epoch, ent_row, (long long *)version, err);
+  count_launches(1);
+  return launch_owner_apply(p, rows_hint, width, n_cached, ent_row, row_mask, embedding, st);
+}
+
+static PushLists mailbox_lists(const hctr_p2p_ctx *c, const hctr_p2p_box *mine) {
+  PushLists p;
+  p.key = (const long long *)mine->pkey;
+  p.upd = (const long long *)mine->pupd;
+  p.val = mine->pval;
+  p.src_off = nullptr;
+  p.src_stride = c->cap;
+  p.flat_start = c->cnt_in + 4 * c->nrank + 1;
+  p.nsrc = c->nrank;
+  return p;
+}
+
+extern "C" int hctr_p2p_owner_mark(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, uint32_t seq,
+                                   const int32_t *row_of, size_t length, size_t n_cached,
+                                   unsigned long long *row_mask, uint32_t epoch, int32_t *ent_row, int64_t *version,
+                                   void *stream) {
+  if (c->nrank > 32 || epoch == 0) return (int)cudaErrorInvalidValue;
+  const PushLists p = mailbox_lists(c, mine);
+  owner_mark_sources<true><<<mark_grid(c->cap), kThreads, 0, (cudaStream_t)stream>>>(
+      p, *c, seq, row_of, length, n_cached, row_mask, epoch, ent_row, (long long *)version, c->err);
+  count_launches(1);
   return launch_status();
+}
+
+extern "C" int hctr_p2p_owner_apply(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, size_t n_cached,
+                                    const int32_t *ent_row, const unsigned long long *row_mask, float *embedding,
+                                    void *stream) {
+  if (c->nrank > 32) return (int)cudaErrorInvalidValue;
+  return launch_owner_apply(mailbox_lists(c, mine), c->cap, c->width, n_cached, ent_row, row_mask, embedding,
+                            (cudaStream_t)stream);
 }
 
 extern "C" int hctr_p2p_owner_update(const hctr_p2p_ctx *cp, const int32_t *row_of, size_t length, size_t n_cached,

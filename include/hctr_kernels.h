@@ -257,77 +257,82 @@ typedef struct hctr_p2p_ctx {
   uint32_t cap;             /* rows per (mailbox, source) sub-region */
   size_t width;
   const hctr_p2p_box *box;  /* device array [nrank]; box[rank] is this rank's own mailbox */
-  uint32_t *cnt_in;         /* device [5*nrank+2]: query, push and return counts received from each peer,
-                               then the exclusive prefixes of the query counts and of the push counts
-                               (nrank+1 entries each) */
+  uint32_t *cnt_in;         /* device [HCTR_P2P_CNT_WORDS(nrank)], zero-initialised once: query, push and return counts
+                               received from each peer ([0,n), [n,2n), [2n,3n)), the exclusive prefixes of the query
+                               counts ([3n,4n]) and of the push counts ([4n+1,5n+1]), the longest wait of the last step
+                               for a peer's queries and for a peer's returned rows in microseconds (5n+2, 5n+3), and
+                               two arrival counters of the publishing kernels */
   uint32_t *err;            /* device error word */
   unsigned long long timeout_ns;
 } hctr_p2p_ctx;
+#define HCTR_P2P_CNT_WORDS(n) (5 * (size_t)(n) + 8)
+#define HCTR_P2P_WAIT0(n) (5 * (n) + 2)   /* index in cnt_in: longest wait for a peer's queries, microseconds */
+#define HCTR_P2P_WAIT1(n) (5 * (n) + 3)   /* longest wait for a peer's returned rows */
+#define HCTR_P2P_TICKET0(n) (5 * (n) + 4) /* arrival counters of the two publishing kernels */
+#define HCTR_P2P_TICKET1(n) (5 * (n) + 5)
+#define HCTR_P2P_SERVED(n) (5 * (n) + 6)  /* rows this rank returned to its peers in the last step */
 
-/* Requester: (key, local version) of every unique key, written into its owner's mailbox.
- * U and the per-owner segment starts are read from the batch's meta words. */
+/* Requester: (key, local version) of every unique key, written into its owner's mailbox; the thread block that
+ * finishes last then publishes this rank's counts for the step (queries per owner from the batch's meta words,
+ * pushed rows per owner from push_counts, null = none) and releases sequence number `seq` to every peer.
+ * Replaces generateQuery + the first half of all2allExchangeQuery, csrc/core/generate_query.cu:91-106,
+ * csrc/core/all2all.cu:18-44.  nrank <= 256. */
 int hctr_p2p_query_send(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const int64_t *uniq,
-                        const uint8_t *uniq_owner, const int32_t *uniq_row, const int64_t *version, void *stream);
+                        const uint8_t *uniq_owner, const int32_t *uniq_row, const int64_t *version, uint32_t seq,
+                        const uint32_t *push_counts, void *stream);
 
-/* Publishes this rank's counts to every peer and releases sequence number `seq`.
+/* Publishes this rank's counts to every peer and releases sequence number `seq` (what the last thread block of
+ * hctr_p2p_query_send / hctr_p2p_gather does, as a launch of its own).
  * phase 0: query count (from meta's segments) + push_count (null = zeros); phase 1: ret_count. */
 int hctr_p2p_signal(const hctr_p2p_ctx *c, int phase, uint32_t seq, const uint32_t *meta,
                     const uint32_t *counts, void *stream);
 
-/* Waits (bounded) until every peer has released `seq` for `phase`; copies the announced counts into
- * c->cnt_in.  On timeout sets HCTR_ERR_TIMEOUT and records zero counts for the silent peers. */
+/* Waits (bounded by c->timeout_ns) until every peer has released `seq` for `phase`; copies the announced counts
+ * into c->cnt_in.  On timeout sets HCTR_ERR_TIMEOUT in *c->err, records zero counts for the silent peers and
+ * returns normally.  hctr_p2p_owner_mark (phase 0) and hctr_p2p_recv_scan (phase 1) do the same wait in their
+ * first instructions; this launch is for the paths that do not use them. */
 int hctr_p2p_wait(const hctr_p2p_ctx *c, int phase, uint32_t seq, void *stream);
 
-/* hctr_p2p_signal followed by hctr_p2p_wait in one launch.  Phase 0 as hctr_p2p_signal; phase 1 computes
- * the return counts itself from the exclusive scan ret_slot of the stale flags (counts is ignored). */
-int hctr_p2p_signal_wait(const hctr_p2p_ctx *c, int phase, uint32_t seq, const uint32_t *meta,
-                         const uint32_t *counts, const uint32_t *ret_slot, void *stream);
-
 /* Owner: applies the pushed rows of every source, source after source in rank order, in one cooperative
- * launch (grid-wide barrier between sources).  Same arithmetic as hctr_owner_update. */
+ * launch (grid-wide barrier between sources).  Same arithmetic as hctr_owner_update.  For more than 32 ranks. */
 int hctr_p2p_owner_update(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
                           float *embedding, int64_t *version, void *stream);
 
-/* Owner: staleness flags for all received queries, indexed FLAT: q in [0, Q) runs over the queries of
- * source 0, then source 1, ... (Q and the per-source starts are in c->cnt_in).  Flag bytes are stored
- * into the requesters' mailboxes, flags32[q] = 0/1. */
-int hctr_p2p_stale_check(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
-                         const int64_t *version, int64_t pull_bound, uint32_t *flags32, void *stream);
+/* Owner, up to 32 ranks: hctr_owner_update_merged split in its two passes, on the pushed rows in this rank's own
+ * mailbox (`mine` = host copy of box[rank]).  hctr_p2p_owner_mark first waits (bounded) for the peers' phase-0
+ * counts of step `seq` and records them in c->cnt_in, then marks sources, resolves rows (ent_row, nrank * cap
+ * entries) and adds the update counts to the versions: versions are final when it ends.  hctr_p2p_owner_apply adds
+ * the rows; it may run on another stream, concurrently with hctr_p2p_stale_scan. */
+int hctr_p2p_owner_mark(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, uint32_t seq, const int32_t *row_of,
+                        size_t length, size_t n_cached, unsigned long long *row_mask, uint32_t epoch,
+                        int32_t *ent_row, int64_t *version, void *stream);
+int hctr_p2p_owner_apply(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, size_t n_cached, const int32_t *ent_row,
+                         const unsigned long long *row_mask, float *embedding, void *stream);
 
-/* Owner: ret_count[s] = rows to return to requester s, from the exclusive scan ret_slot of flags32. */
-int hctr_p2p_return_counts(const hctr_p2p_ctx *c, const uint32_t *ret_slot, uint32_t *ret_count, void *stream);
-
-/* Owner: flagged rows (+ versions) gathered straight into the requesters' mailboxes.  ret_q is scratch
- * for one word per returned row (at most nrank*cap). */
-int hctr_p2p_gather(const hctr_p2p_ctx *c, const uint32_t *flags32, const uint32_t *ret_slot, uint32_t *ret_q,
-                    const int32_t *row_of, const float *embedding, const int64_t *version, void *stream);
-
-/* Requester: flags of its unique keys collected from its mailbox (flags[u], flags32[u]; zeros for
- * u >= U up to u_max). */
-int hctr_p2p_recv_flags(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const uint8_t *uniq_owner,
-                        uint8_t *flags, uint32_t *flags32, void *stream);
-
-/* Requester: recv_index[u] = row index (in units of rows, relative to box[rank].rval / rver) of the row
- * returned for unique key u, from the exclusive scan recv_slot of flags32. */
-int hctr_p2p_recv_index(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const uint8_t *uniq_owner,
-                        const uint32_t *recv_slot, uint32_t *recv_index, void *stream);
-
-/* Fused forms of the owner's and the requester's flag + scan steps (one launch each instead of three).
+/* Fused flag + scan steps of the owner and of the requester.
  * scratch: hctr_p2p_scan_scratch_words(entries) words, 8-byte aligned, zero-initialised ONCE; epoch non-zero and
  * different from every earlier launch on the same scratch.
- * hctr_p2p_stale_scan = hctr_p2p_stale_check + exclusive scan + list of returned queries: flag bytes go to the
- * requesters' mailboxes, ret_slot[q] (Q + 1 entries) is the slot of query q's row among the returned rows,
- * ret_q[slot] the flat query index of the row in that slot (entries = nrank * cap).
- * hctr_p2p_gather_listed = the row-moving half of hctr_p2p_gather for a list that already exists.
- * hctr_p2p_recv_scan = hctr_p2p_recv_flags + exclusive scan + hctr_p2p_recv_index (entries = u_max). */
+ * hctr_p2p_stale_scan (entries = nrank * cap): staleness flag of every received query, indexed FLAT (q in [0, Q)
+ * runs over the queries of source 0, then source 1, ...; Q and the per-source starts are in c->cnt_in).  Flag
+ * bytes go to the requesters' mailboxes, ret_slot[q] (Q + 1 entries) is the slot of query q's row among the
+ * returned rows, ret_q[slot] the flat query index and ret_row[slot] the local row of the row in that slot.
+ * Replaces decide_outdated_kernel, the scan, the segmented reduce and the select of csrc/core/handle_query.cu:7-73.
+ * hctr_p2p_gather: the listed rows (+ versions) go straight into the requesters' mailboxes; the thread block that
+ * finishes last publishes the per-requester row counts and releases `seq` (phase 1).  Replaces
+ * write_return_value_kernel + all2allReturnOutdated / all2allReturnValue, csrc/core/handle_query.cu:24-40,
+ * csrc/core/all2all.cu:89-130.
+ * hctr_p2p_recv_scan (entries = u_max): waits (bounded) for the owners' phase-1 release of `seq`, then collects the
+ * flags of this rank's unique keys from its mailbox (flags[u]; zeros for u >= U up to u_max) and computes
+ * recv_index[u] = row index (relative to box[rank].rval / rver) of the row returned for unique key u. */
 size_t hctr_p2p_scan_scratch_words(size_t entries);
 int hctr_p2p_stale_scan(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
                         const int64_t *version, int64_t pull_bound, uint32_t *ret_slot, uint32_t *ret_q,
-                        uint32_t *scratch, uint32_t epoch, void *stream);
-int hctr_p2p_gather_listed(const hctr_p2p_ctx *c, const uint32_t *ret_q, const uint32_t *ret_slot,
-                           const int32_t *row_of, const float *embedding, const int64_t *version, void *stream);
-int hctr_p2p_recv_scan(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_max, const uint8_t *uniq_owner,
-                       uint8_t *flags, uint32_t *recv_index, uint32_t *scratch, uint32_t epoch, void *stream);
+                        int32_t *ret_row, uint32_t *scratch, uint32_t epoch, void *stream);
+int hctr_p2p_gather(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *ret_q, const int32_t *ret_row,
+                    const uint32_t *ret_slot, const float *embedding, const int64_t *version, void *stream);
+int hctr_p2p_recv_scan(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *meta, size_t u_max,
+                       const uint8_t *uniq_owner, uint8_t *flags, uint32_t *recv_index, uint32_t *scratch,
+                       uint32_t epoch, void *stream);
 
 typedef struct hctr_reduce_args {
   size_t n_unique;            /* U of the previous batch (host value) */
@@ -383,8 +388,9 @@ int hctr_query_versions(size_t n_unique, const int32_t *uniq_row, const int64_t 
 int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int64_t *updates,
                       const float *val, const int32_t *row_of, size_t length, size_t n_cached,
                       float *embedding, int64_t *version, uint32_t *err, void *stream);
-/* All sources at once, in two launches, with the same per-row apply order (ascending source rank) and
- * therefore the same bits as calling hctr_owner_update once per source.  Source s's rows start at entry
+/* All sources at once, in two launches (mark sources + versions, then rows), with the same per-row apply order
+ * (ascending source rank) and therefore the same bits as calling hctr_owner_update once per source.  ent_row is
+ * scratch for one 32-bit word per pushed row.  Source s's rows start at entry
  * src_off[s] of key/updates/val and number flat_start[s+1] - flat_start[s] (device arrays of nsrc and nsrc+1
  * entries; the counts may only exist on the device); every source's list must be sorted by key, as the
  * slices of a unique list are.  row_mask: one 64-bit word per OWNED row (row - n_cached), zero-initialised once; `epoch` must be
@@ -393,8 +399,8 @@ int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int
 int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width, const int64_t *key,
                              const int64_t *updates, const float *val, const unsigned long long *src_off,
                              const uint32_t *flat_start, const int32_t *row_of, size_t length, size_t n_cached,
-                             unsigned long long *row_mask, uint32_t epoch, float *embedding, int64_t *version,
-                             uint32_t *err, void *stream);
+                             unsigned long long *row_mask, uint32_t epoch, int32_t *ent_row, float *embedding,
+                             int64_t *version, uint32_t *err, void *stream);
 
 /* Same, with the row count read from device memory (at most n_rows_max). */
 int hctr_owner_update_dev(size_t n_rows_max, const uint32_t *n_rows_dev, size_t width, const int64_t *key,

@@ -76,20 +76,26 @@ int hctr_table_set_embedding(hctr_table *t, const float *rows);
  * versions and, for cached rows, pending gradients and pending-update counts of this rank to `path`.  The
  * importing table must have been created with the same rank, nrank, length, width and storage_arr; a file of
  * another shape, with other keys, truncated or with a wrong checksum is refused before anything is changed.
- * Import is legal between steps only; batches preprocessed earlier are dropped. */
+ * Import is legal between steps only; batches preprocessed earlier are dropped.  Export writes `path`.tmp and
+ * renames it over `path` once complete.  In a multi-rank job both calls are COLLECTIVE in the sense of the step
+ * protocol: every rank exports / imports (its own file) at the same point between two steps, because an import
+ * drops the batches preprocessed so far on the rank that does it. */
 int hctr_table_export(hctr_table *t, const char *path);
 int hctr_table_import(hctr_table *t, const char *path);
 
 /* Sizes of the last push_pull: {batch, unique, prev_batch, prev_unique, pushed_rows,
- * received_push_rows, queried_keys, returned_rows, received_rows, stored_rows, cached_rows}. */
-int hctr_table_stats(hctr_table *t, long long out[11]);
+ * received_push_rows, queried_keys, returned_rows, received_rows, stored_rows, cached_rows, wait_queries_us,
+ * wait_returns_us}; the last two are the longest in-kernel waits of the step for a peer's queries and for a
+ * peer's returned rows (peer-to-peer exchange; 0 otherwise). */
+int hctr_table_stats(hctr_table *t, long long out[13]);
 
 /* Per-phase device time.  hctr_table_profile(t, k): k = 0 off, 1 every step, k > 1 every k-th step (the
  * timing events cost the step a few microseconds per phase, sampling keeps that out of a benchmark).  In a
  * timed step each phase of preprocess/push_pull is bracketed by two CUDA events on the stream it runs on; hctr_table_phase_times returns the accumulated milliseconds and
  * call counts per phase (and clears them when reset != 0).  Phase order: dedupe, push_decide, reduce,
- * query, exchange, owner_update, stale_gather, refresh, expand. */
-#define HCTR_N_PHASES 9
+ * query, exchange, owner_update, stale_gather, refresh, expand, owner_apply (the row pass of the owner update in
+ * the peer-to-peer exchange: it runs on a second stream, concurrently with stale_gather). */
+#define HCTR_N_PHASES 10
 int hctr_table_profile(hctr_table *t, int enable);
 int hctr_table_phase_times(hctr_table *t, double ms[HCTR_N_PHASES], long long calls[HCTR_N_PHASES], int reset);
 /* The most recent timed phases (up to 256 are kept) as triples {phase index, start ms, end ms}, oldest first,

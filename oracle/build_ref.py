@@ -1,6 +1,8 @@
 """Builds the REFERENCE's own implementation as a checker (TEST INFRASTRUCTURE, never shipped).
 
-  python oracle/build_ref.py [--reference DIR]      (DIR = checkout of the reference project)
+  python oracle/build_ref.py [--reference DIR]      (DIR = checkout of the reference project; default: the
+                                                     HCTR_REFERENCE_DIR environment variable, else a directory
+                                                     named "reference" beside this repository)
 
 Compiles the reference's sources where they lie (nothing is copied into this repository) for sm_100a and links
 them with oracle/ref_binding.cu into oracle/_ref/hetuCTR_ref<ext>.so.  The reference's ZMQ rendezvous cannot be
@@ -26,7 +28,13 @@ REF_SOURCES = ["core/hetu_gpu_table.cu", "core/preprocess.cu", "core/preprocess_
                "core/debug.cu", "utils/initializer.cu"]
 
 
-def build(reference="/root/reference", force=False, verbose=False):
+def reference_dir():
+    """Where the reference project's checkout is: HCTR_REFERENCE_DIR, else `reference` beside this repository."""
+    return os.environ.get("HCTR_REFERENCE_DIR") or os.path.join(os.path.dirname(ROOT), "reference")
+
+
+def build(reference=None, force=False, verbose=False):
+    reference = reference or reference_dir()
     csrc = os.path.join(reference, "csrc")
     if not os.path.isdir(csrc):
         raise RuntimeError(f"reference sources not found at {csrc}")
@@ -75,7 +83,8 @@ def build(reference="/root/reference", force=False, verbose=False):
 PARTITION_MODULE = os.path.join(OUT, "partition", "hetuCTR_partition" + sysconfig.get_config_var("EXT_SUFFIX"))
 
 
-def build_partition(reference="/root/reference", force=False, verbose=False):
+def build_partition(reference=None, force=False, verbose=False):
+    reference = reference or reference_dir()
     """The reference's offline partitioner (csrc/partition/), compiled WITHOUT OpenMP: its `omp parallel for`
     pragmas are then ignored, the sweeps run sequentially and the result is reproducible (its rand() starts from
     the C library's default seed in a fresh process)."""
@@ -99,6 +108,6 @@ def build_partition(reference="/root/reference", force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    ref = sys.argv[sys.argv.index("--reference") + 1] if "--reference" in sys.argv else "/root/reference"
+    ref = sys.argv[sys.argv.index("--reference") + 1] if "--reference" in sys.argv else reference_dir()
     print(build(ref, force="--force" in sys.argv, verbose=True))
     print(build_partition(ref, force="--force" in sys.argv, verbose=True))

@@ -1,10 +1,17 @@
 """Test helper: all ranks of a job on ONE GPU, driven in lockstep through the table-level C-ABI.
 
 Mirrors the oracle's `World` API so a test can step both and compare.  With nrank > 1 the ranks are
-threads of this process using the library's in-process transport (ip="inproc"); every kernel of the
-multi-rank path runs exactly as it does under NCCL, only the byte movement between ranks differs.
+threads of this process (ip="inproc") and there are two ways for them to exchange data:
+
+  exchange="inproc"  the kernels of the NCCL path; bytes move between the ranks' buffers with cudaMemcpyAsync
+  exchange="p2p"     the kernels of the peer-to-peer mailbox exchange, the default of a one-process-per-GPU job:
+                     queries, pushed rows, flags and returned rows are stored straight into the destination rank's
+                     mailbox.  The ranks share one CUDA context here, so a peer's mailbox is a plain pointer; the
+                     table drains its stream and meets the other ranks at a host barrier between publishing and
+                     consuming, so no kernel ever waits for another launch on the same GPU.
 """
 import itertools
+import os
 import threading
 
 import numpy as np
@@ -36,8 +43,9 @@ def _parallel(fns):
 
 class GpuWorld:
     def __init__(self, nrank, length, width, pull_bound, push_bound, learning_rate, root_arr, storage_arrs,
-                 init=(hb.INIT_ZERO, 0.0, 0.0), device=0, keys_on_device=True):
+                 init=(hb.INIT_ZERO, 0.0, 0.0), device=0, keys_on_device=True, exchange="inproc"):
         self.nrank, self.length, self.width = nrank, length, width
+        self.exchange = exchange if nrank > 1 else "none"
         self.dev = torch.device("cuda", device)
         self.keys_on_device = keys_on_device
         self.tables = [None] * nrank
@@ -47,7 +55,23 @@ class GpuWorld:
             self.tables[r] = hb.Table(r, nrank, device, "inproc" if nrank > 1 else "127.0.0.1", port, length, width,
                                       pull_bound, push_bound, root_arr, storage_arrs[r], init, learning_rate, 0)
 
-        _parallel([lambda r=r: make(r) for r in range(nrank)])
+        # the exchange flavour is read from the environment when a table is constructed
+        saved = {k: os.environ.get(k) for k in ("HCTR_EXCHANGE", "HCTR_P2P_TIMEOUT_MS")}
+        if exchange == "p2p":
+            os.environ["HCTR_EXCHANGE"] = "p2p"
+            os.environ["HCTR_P2P_TIMEOUT_MS"] = "2000"
+        else:
+            os.environ.pop("HCTR_EXCHANGE", None)
+        try:
+            _parallel([lambda r=r: make(r) for r in range(nrank)])
+        finally:
+            for k, v in saved.items():
+                if v is None:
+                    os.environ.pop(k, None)
+                else:
+                    os.environ[k] = v
+        if nrank > 1:
+            assert self.tables[0].exchange_name() == exchange
         self._batch = [0] * nrank
         self._keep = []
 
@@ -79,6 +103,16 @@ class GpuWorld:
         _parallel([lambda r=r: self.tables[r].push_pull(grads[r], dsts[r]) for r in range(self.nrank)])
         return [d[:b].cpu().numpy() for d, b in zip(dsts, self._batch)]
 
+    def get_all(self, what, prev=False):
+        """`what` of every rank, fetched by all ranks at the same time (some views are collective)."""
+        out = [None] * self.nrank
+
+        def one(r):
+            out[r] = self.get(r, what, prev)
+
+        _parallel([lambda r=r: one(r) for r in range(self.nrank)])
+        return out
+
     def get(self, rank, what, prev=False):
         t = self.tables[rank]
         if what == "storage":
@@ -98,9 +132,11 @@ INDEX_ARRAYS = ("unique_idx", "idx_map", "sorted_arg", "run_length", "root", "of
 
 def assert_index_parity(gw, ow, ranks=None):
     """Bit-exact comparison of everything preprocess produces."""
-    for r in ranks if ranks is not None else range(gw.nrank):
-        for name in INDEX_ARRAYS:
-            g, o = gw.get(r, name), ow.get(r, name)
+    for name in INDEX_ARRAYS:
+        # with the mailbox exchange the peers' counts only reach the host on demand, collectively
+        every = gw.get_all(name) if name == "shape_exchanged" else None
+        for r in ranks if ranks is not None else range(gw.nrank):
+            g, o = every[r] if every else gw.get(r, name), ow.get(r, name)
             assert g.shape == o.shape and np.array_equal(g, o), f"rank {r}: {name} differs"
 
 

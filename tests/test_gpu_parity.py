@@ -156,20 +156,26 @@ def test_constructor_errors():
 
 
 # ------------------------------------------------------------------------------------------------
-# multi-rank (thread ranks on one GPU, in-process transport)
+# multi-rank: thread ranks on one GPU.  exchange="inproc" runs the kernels of the NCCL path (bytes moved by
+# cudaMemcpyAsync), exchange="p2p" the kernels of the peer-to-peer mailbox exchange that one-process-per-GPU jobs
+# use by default (see gpu_world.py).
 # ------------------------------------------------------------------------------------------------
+EXCHANGES = ["inproc", "p2p"]
+
+
 def _hybrid_storage(root, nrank, rng, frac):
     return [np.where((root == r) | (rng.rand(len(root)) < frac))[0] for r in range(nrank)]
 
 
 @pytest.mark.parametrize("nrank,pull,push,frac", [(2, 0, 0, 0.0), (2, 0, 0, 0.5), (4, 0, 0, 0.3), (4, 2, 3, 0.3),
-                                                   (3, 10, 10, 1.0), (8, 1, 0, 0.1)])
-def test_multi_rank_parity(oracle_mod, nrank, pull, push, frac):
+                                                   (3, 10, 10, 1.0), (8, 1, 0, 0.1), (8, 0, 0, 0.6)])
+@pytest.mark.parametrize("exchange", EXCHANGES)
+def test_multi_rank_parity(oracle_mod, nrank, pull, push, frac, exchange):
     N, W, B = 3000, 16, 700
     rng = np.random.RandomState(nrank * 100 + pull)
     root = rng.randint(nrank, size=N).astype(np.uint8)
     storage = _hybrid_storage(root, nrank, rng, frac)
-    gw, ow = make_worlds(oracle_mod, nrank, N, W, pull, push, 0.1, root, storage)
+    gw, ow = make_worlds(oracle_mod, nrank, N, W, pull, push, 0.1, root, storage, exchange=exchange)
     batches = [[(rng.zipf(1.2, size=B) - 1) % N for _ in range(nrank)] for _ in range(8)]
     batches[4] = [np.zeros(0, dtype=np.int64)] * nrank
     grads = [None] + [[rng.normal(0, 1, size=(len(k), W)).astype(np.float32) for k in batches[s - 1]]
@@ -180,14 +186,15 @@ def test_multi_rank_parity(oracle_mod, nrank, pull, push, frac):
 
 
 @pytest.mark.parametrize("width", [128, 132, 256, 260, 512, 640])
-def test_multi_rank_wide_rows(oracle_mod, width):
+@pytest.mark.parametrize("exchange", EXCHANGES)
+def test_multi_rank_wide_rows(oracle_mod, width, exchange):
     # rows of 128..512 floats take the streaming reduction, wider ones the register kernel; with caches and
     # bounds every storage class (not stored / owned / cached push / cached hold) occurs
     nrank, N, B = 3, 2500, 900
     rng = np.random.RandomState(width)
     root = rng.randint(nrank, size=N).astype(np.uint8)
     storage = _hybrid_storage(root, nrank, rng, 0.4)
-    gw, ow = make_worlds(oracle_mod, nrank, N, width, 2, 3, 0.1, root, storage)
+    gw, ow = make_worlds(oracle_mod, nrank, N, width, 2, 3, 0.1, root, storage, exchange=exchange)
     batches = [[(rng.zipf(1.15, size=B) - 1) % N for _ in range(nrank)] for _ in range(5)]
     grads = [None] + [[rng.normal(0, 1, size=(len(k), width)).astype(np.float32) for k in batches[s - 1]]
                       for s in range(1, 5)]
@@ -195,13 +202,49 @@ def test_multi_rank_wide_rows(oracle_mod, width):
     gw.close()
 
 
-def test_reference_update_script_exact_counts(oracle_mod):
+@pytest.mark.parametrize("exchange", EXCHANGES)
+@pytest.mark.parametrize("nrank,width,push", [(2, 16, 2), (4, 128, 3), (5, 36, 0)])
+def test_batch_size_grows_between_steps(oracle_mod, nrank, width, push, exchange):
+    # The batch size changes from step to step, twice beyond everything reserved so far: all per-batch buffers (and,
+    # with the mailbox exchange, the mailboxes themselves) are re-allocated between a batch's push decision - taken
+    # at the end of its own push_pull - and the reduction that consumes the decision one step later.
+    N = 4000
+    rng = np.random.RandomState(17 * nrank + width)
+    root = rng.randint(nrank, size=N).astype(np.uint8)
+    storage = _hybrid_storage(root, nrank, rng, 0.5)
+    gw, ow = make_worlds(oracle_mod, nrank, N, width, 1, push, 0.1, root, storage, exchange=exchange)
+    sizes = [256, 700, 300, 5000, 64, 5000]
+    batches = [[(rng.zipf(1.2, size=b) - 1) % N for _ in range(nrank)] for b in sizes]
+    grads = [None] + [[rng.normal(0, 1, size=(len(k), width)).astype(np.float32) for k in batches[s - 1]]
+                      for s in range(1, len(sizes))]
+    run_steps(gw, ow, batches, grads)
+    gw.close()
+
+
+@pytest.mark.parametrize("exchange", EXCHANGES)
+def test_many_pushers_per_row(oracle_mod, exchange):
+    # 8 ranks, every rank caches every row and pushes each step (push bound 0), keys from a small hot set: most
+    # owned rows receive pushes from several sources in one step, up to all seven peers - the case in which the
+    # owner must add the contributions in ascending source order
+    nrank, N, W, B = 8, 600, 128, 1500
+    rng = np.random.RandomState(8)
+    root = rng.randint(nrank, size=N).astype(np.uint8)
+    storage = [np.arange(N)] * nrank
+    gw, ow = make_worlds(oracle_mod, nrank, N, W, 0, 0, 0.1, root, storage, exchange=exchange)
+    batches = [[(rng.zipf(1.1, size=B) - 1) % N for _ in range(nrank)] for _ in range(4)]
+    grads = [None] + [[rng.normal(0, 1, size=(B, W)).astype(np.float32) for _ in range(nrank)] for _ in range(3)]
+    run_steps(gw, ow, batches, grads)
+    gw.close()
+
+
+@pytest.mark.parametrize("exchange", EXCHANGES)
+def test_reference_update_script_exact_counts(oracle_mod, exchange):
     # the reference's tests/test_update.py:17-43 through the CUDA path: 4 ranks, hybrid storage, lr=-1, grad=1
     nrank, W, N, B = 4, 128, 1024, 1024
     np.random.seed(0)
     root = np.random.randint(nrank, size=N)
     storage = [np.where(root <= r)[0] for r in range(nrank)]
-    gw = GpuWorld(nrank, N, W, 0, 0, -1.0, root, storage)
+    gw = GpuWorld(nrank, N, W, 0, 0, -1.0, root, storage, exchange=exchange)
     rngs = [np.random.RandomState(r) for r in range(nrank)]
     gw.preprocess([np.zeros(0, dtype=np.int64)] * nrank)
     ids = [np.zeros(0, dtype=np.int64)] * nrank
