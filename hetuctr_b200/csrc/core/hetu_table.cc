@@ -89,26 +89,19 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
     }
   }
   {
-    // stream_main_ carries many short, latency-bound kernels; it gets the highest priority so that their
-    // CTAs are placed ahead of the bulk gradient-reduction CTAs that run concurrently on stream_reduce_
+    // Multi-rank tables: stream_main_ carries the step's chain of short, latency-bound kernels and gets the highest
+    // priority, so that their thread blocks are placed ahead of the bulk gradient reduction that runs concurrently on
+    // stream_reduce_.  A single-rank table is the other way round: the row expansion does not need the dedupe
+    // pipeline (every key is stored here and the key ingest resolves the rows), so reduction + expansion on
+    // stream_reduce_ are the step's critical path and the dedupe on stream_main_ - whose results only the NEXT
+    // step's reduction reads - fills in behind them.
     int lo = 0, hi = 0;
     HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_main_, cudaStreamNonBlocking, hi));
-  }
-  {
+    const bool single = nrank == 1;
+    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_main_, cudaStreamNonBlocking, single ? lo : hi));
     // the side stream carries the few long-run CTAs that should start ahead of the bulk kernels
-    int lo = 0, hi = 0;
-    HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_side_, cudaStreamNonBlocking, hi));
-  }
-  {
-    int lo = 0, hi = 0;
-    HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_reduce_, cudaStreamNonBlocking, lo));
-  }
-  {
-    int lo = 0, hi = 0;
-    HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_side_, cudaStreamNonBlocking, single ? lo : hi));
+    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_reduce_, cudaStreamNonBlocking, single ? hi : lo));
     HCTR_CUDA(cudaStreamCreateWithPriority(&stream_reduce_side_, cudaStreamNonBlocking, hi));
   }
   {
@@ -124,7 +117,7 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_reduce_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
-  HCTR_CUDA(cudaEventCreateWithFlags(&ev_keys_, cudaEventDisableTiming | cudaEventBlockingSync));
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_keys_, cudaEventDisableTiming));
 
   try {
     initComm(ip, port);
@@ -281,6 +274,7 @@ void HetuTable::reserveBatch(BatchDesc &b, size_t batch) {
   b.meta.ensure((HCTR_META_WORDS + nrank_ + 1) * sizeof(uint32_t));
   b.pos_row.ensure(batch * sizeof(int32_t));
   b.heavy.ensure((batch / 32 + 2) * sizeof(uint32_t));
+  b.rank.ensure(batch * sizeof(uint32_t));
   if (nrank_ > 1) {
     b.need_push.ensure((batch + 1) * sizeof(uint32_t));
     b.push_slot.ensure((batch + 1) * sizeof(uint32_t));
@@ -300,7 +294,6 @@ void HetuTable::reserveShared(size_t batch) {
   HCTR_CUDA(cudaMemsetAsync(d_chain3_.p, 0, d_chain3_.bytes, stream_main_));
   HCTR_CUDA(cudaStreamSynchronize(stream_main_));  // the scratch is used from other streams as well
   d_sk_.ensure(batch * sizeof(unsigned long long));
-  d_rank_.ensure(batch * sizeof(uint32_t));
   d_cnt_.ensure((batch + 1) * sizeof(uint32_t));  // all-zero between calls, like the bitmap
   HCTR_CUDA(cudaMemsetAsync(d_cnt_.p, 0, d_cnt_.bytes, stream_main_));
   d_push_count_.ensure((size_t)nrank_ * sizeof(uint32_t));
@@ -350,16 +343,18 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
     else
       cudaGetLastError();
   }
-  if (keys_on_device) {
-    // one launch: private copy of the keys + cleared meta words
-    HCTR_LAUNCH(hctr_ingest_keys(reinterpret_cast<const int64_t *>(data_ptr), cur.keys.as<int64_t>(), batch_size, cur.meta.as<uint32_t>(),
-                                 (unsigned)meta_words, stream_main_));
-    HCTR_CUDA(cudaEventRecord(ev_keys_, stream_main_));
-  } else {
+  // One launch in front of the pipeline: private copy of the keys (host keys are copied first, then taken in place),
+  // cleared meta words, and the local row of every batch position - which is all the row expansion needs for keys
+  // that are stored here, so a single-rank table starts it without waiting for the dedupe.
+  const int64_t *key_src = reinterpret_cast<const int64_t *>(data_ptr);
+  if (!keys_on_device) {
     HCTR_CUDA(cudaMemcpyAsync(cur.keys.p, data_ptr, sizeof(index_t) * batch_size, cudaMemcpyDefault, stream_main_));
-    HCTR_CUDA(cudaEventRecord(ev_keys_, stream_main_));
-    HCTR_CUDA(cudaMemsetAsync(cur.meta.p, 0, meta_words * sizeof(uint32_t), stream_main_));
+    key_src = cur.keys.as<int64_t>();
   }
+  HCTR_LAUNCH(hctr_ingest_keys_rows(key_src, cur.keys.as<int64_t>(), batch_size, cur.meta.as<uint32_t>(),
+                                    (unsigned)meta_words, d_row_of_.as<int32_t>(), kEmbeddingIDMax,
+                                    cur.pos_row.as<int32_t>(), d_err_.as<uint32_t>() + 9, stream_main_));
+  HCTR_CUDA(cudaEventRecord(ev_keys_, stream_main_));
 
   if (!key_stride_known_ && batch_size >= 4096) detectKeyStride(cur);  // once per table
   hctr_dedupe_args a;
@@ -378,9 +373,9 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   a.word_base = d_word_base_.as<uint32_t>();
   a.scan_scratch = d_chain_.as<uint32_t>();
   a.sk = d_sk_.as<unsigned long long>();
-  a.rank_in_run = d_rank_.as<uint32_t>();
+  a.rank_in_run = cur.rank.as<uint32_t>();
   a.heavy_list = cur.heavy.as<uint32_t>();
-  a.pos_row = cur.pos_row.as<int32_t>();
+  a.pos_row = nullptr;  // resolved by the key ingest above
   a.uniq = cur.uniq.as<int64_t>();
   a.uniq_owner = cur.uniq_owner.as<uint8_t>();
   a.uniq_row = cur.uniq_row.as<int32_t>();
@@ -390,9 +385,10 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   a.idx_map = cur.idx_map.as<int32_t>();
   a.meta = cur.meta.as<uint32_t>();
   // run ordering happens on stream_side_, off this stream's critical path; the reduction of this batch
-  // (next step) waits on the batch's own event.  stream_side_ also stages through d_rank_, which the rank
-  // kernel below overwrites: make sure the previous batch's ordering is over first.
-  if (prev.order_recorded) HCTR_CUDA(cudaStreamWaitEvent(stream_main_, prev.ev_order, 0));
+  // (next step) waits on the batch's own event.  The ordering stages through the batch's own rank buffer, so the
+  // ordering of the previous batch may still run while this batch is deduplicated; only the descriptor being
+  // recycled (two batches old) must be out of use.
+  if (cur.order_recorded) HCTR_CUDA(cudaStreamWaitEvent(stream_main_, cur.ev_order, 0));
   if (!cur.ev_order) HCTR_CUDA(cudaEventCreateWithFlags(&cur.ev_order, cudaEventDisableTiming));
   a.side_stream = stream_side_;
   a.fork_event = ev_fork_;
@@ -410,15 +406,20 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   const bool decide = n > 1 && prev.unique_size > 0;
   if (decide && !prev.decided) launchPushDecide(prev);  // normally done at the end of the previous push_pull
   HCTR_CUDA(cudaEventRecord(ev_decide_, stream_reduce_));
-  int sp = tic(kPhDedupe);
-  HCTR_LAUNCH(hctr_dedupe_map(&a, stream_main_));
-  toc(sp);
   prev_push_valid_ = decide;
-
-  uint32_t *h_meta = h_pinned_;
+  cur.dedupe_pending = true;
+  cur.pending = true;
+  if (n == 1) {
+    // Single rank: nothing of this step reads what the dedupe produces (the expansion has the rows from the key
+    // ingest), so its launches are left to push_pull, AFTER the reduction and the expansion have been enqueued: the
+    // host reaches those sooner.  Wait only until the caller's key buffer has been consumed.
+    HCTR_CUDA(cudaEventSynchronize(ev_keys_));
+    return;
+  }
+  flushDedupe(cur);
+  int sp;
   uint32_t *h_cnt_s = h_pinned_ + meta_words;
   uint32_t *h_cnt_r = h_cnt_s + 2 * n;
-  HCTR_CUDA(cudaMemcpyAsync(h_meta, cur.meta.p, meta_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
   if (n > 1 && !use_p2p_) {
     // One packed count exchange instead of the reference's two all2allExchangeShape rounds
     // (csrc/core/preprocess.cu:135,176): per peer {keys I will query, rows I will push}.
@@ -434,13 +435,12 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
     HCTR_CUDA(cudaMemcpyAsync(h_cnt_s, d_cnt_s_.p, 2 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
     HCTR_CUDA(cudaMemcpyAsync(h_cnt_r, d_cnt_r_.p, 2 * n * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
   }
-  if (n == 1 || use_p2p_) {
-    // (Single rank, or the device-driven exchange where counts never visit the host.)
+  if (use_p2p_) {
+    // (The device-driven exchange, where counts never visit the host.)
     // Nothing on the host depends on the result before push_pull: wait only until the caller's key
     // buffer has been consumed and let the rest of the pipeline run under the next call's launches.
     // The batch's sizes (and a key-range error, if any) are picked up at the next synchronisation.
     HCTR_CUDA(cudaEventSynchronize(ev_keys_));
-    cur.pending = true;
     return;
   }
   HCTR_CUDA(cudaStreamSynchronize(stream_main_));
@@ -497,6 +497,18 @@ void HetuTable::launchPushDecide(BatchDesc &b) {
   b.decided = true;
 }
 
+// Enqueues the dedupe pipeline of batch b on stream_main_ (behind the batch's key ingest) and the copy of its
+// meta words to pinned memory.
+void HetuTable::flushDedupe(BatchDesc &b) {
+  if (!b.dedupe_pending) return;
+  b.dedupe_pending = false;
+  int sp = tic(kPhDedupe);
+  HCTR_LAUNCH(hctr_dedupe_map(&b.order_args, stream_main_));
+  toc(sp);
+  const size_t meta_words = HCTR_META_WORDS + nrank_ + 1;
+  HCTR_CUDA(cudaMemcpyAsync(h_pinned_, b.meta.p, meta_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+}
+
 void HetuTable::flushOrdering(BatchDesc &b) {
   if (!b.order_pending) return;
   b.order_pending = false;
@@ -539,6 +551,7 @@ void HetuTable::finalizeBatch() {
 
 void HetuTable::finalizePending() {
   if (!cur_batch_.pending) return;
+  flushDedupe(cur_batch_);
   HCTR_CUDA(cudaStreamSynchronize(stream_main_));
   collectSpans();
   finalizeBatch();
@@ -649,17 +662,25 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     HCTR_LAUNCH(hctr_grad_reduce_apply_pack(&r, stream_reduce_));
     toc(sp, stream_reduce_);
     HCTR_CUDA(cudaEventRecord(ev_reduce_, stream_reduce_));
-    // everything below reads rows / versions the reduction updates
-    HCTR_CUDA(cudaStreamWaitEvent(stream_main_, ev_reduce_, 0));
+    // everything below reads rows / versions the reduction updates (a single-rank table runs it on the reduction's
+    // own stream instead, and its dedupe on stream_main_ needs nothing from here)
+    if (n > 1) HCTR_CUDA(cudaStreamWaitEvent(stream_main_, ev_reduce_, 0));
   }
-  flushOrdering(cur);  // the current batch's run ordering, deferred by preprocess
+  if (n > 1) flushOrdering(cur);  // the current batch's run ordering, deferred by preprocess
 
+  // the stream the step ends on
+  cudaStream_t tail = n == 1 ? stream_reduce_ : stream_main_;
   if (n == 1) {
-    // Single rank: every key is owned and stored here; the pull is a local gather.
-    int sp = tic(kPhExpand);
+    // Single rank: every key is owned and stored here; the pull is a local gather that only needs the rows the
+    // key ingest resolved (ev_keys_) and the reduction in front of it on this stream.  The dedupe of this batch
+    // keeps running on stream_main_; nothing of this step reads its results.
+    HCTR_CUDA(cudaStreamWaitEvent(tail, ev_keys_, 0));
+    int sp = tic(kPhExpand, tail);
     HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
-                                 nullptr, d_embedding_.as<float>(), dst_dev, d_err_.as<uint32_t>() + 8, stream_main_));
-    toc(sp);
+                                 nullptr, d_embedding_.as<float>(), dst_dev, d_err_.as<uint32_t>() + 8, tail));
+    toc(sp, tail);
+    flushDedupe(cur);    // behind the step's critical path on stream_main_: only the next step's reduction needs it
+    flushOrdering(cur);
   } else if (use_p2p_) {
     exchangeP2P(dst_dev);
   } else {
@@ -847,18 +868,25 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   }
 
   if (dst_staged)
-    HCTR_CUDA(cudaMemcpyAsync(dst, dst_dev, cur.batch_size * W * sizeof(embed_t), cudaMemcpyDeviceToHost, stream_main_));
-  uint32_t *h_expand_err = h_pinned_ + h_pinned_words_ - 1;  // bounded waits of the expand kernel
-  HCTR_CUDA(cudaMemcpyAsync(h_expand_err, d_err_.as<uint32_t>() + 8, sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
-  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+    HCTR_CUDA(cudaMemcpyAsync(dst, dst_dev, cur.batch_size * W * sizeof(embed_t), cudaMemcpyDeviceToHost, tail));
+  // two error words: bounded waits of the expand kernel, key range check of the key ingest
+  uint32_t *h_expand_err = h_pinned_ + h_pinned_words_ - 2;
+  HCTR_CUDA(cudaMemcpyAsync(h_expand_err, d_err_.as<uint32_t>() + 8, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost, tail));
+  HCTR_CUDA(cudaStreamSynchronize(tail));
   collectSpans();
-  if (*h_expand_err) {
-    HCTR_CUDA(cudaMemsetAsync(d_err_.as<uint32_t>() + 8, 0, sizeof(uint32_t), stream_main_));
+  if (h_expand_err[0]) {
+    HCTR_CUDA(cudaMemsetAsync(d_err_.as<uint32_t>() + 8, 0, sizeof(uint32_t), tail));
     throw std::runtime_error("push_pull: the row expansion gave up waiting for a bulk copy");
   }
-  if (cur.pending) {
+  if (cur.pending && n > 1) {
     finalizeBatch();
     stats_.unique = cur.unique_size;
+  }
+  if (n == 1 && h_expand_err[1]) {
+    // a key outside the table: the dedupe has seen it too; wait for it and report from here
+    HCTR_CUDA(cudaMemsetAsync(d_err_.as<uint32_t>() + 9, 0, sizeof(uint32_t), tail));
+    HCTR_CUDA(cudaStreamSynchronize(tail));
+    finalizePending();
   }
   uint32_t p2p_err = 0;
   if (p2p_counts_pending_) {
@@ -1193,7 +1221,7 @@ void HetuTable::releaseAll() {
   p2p_.reset();
   transport_.reset();
   DevBuf *all[] = {&d_embedding_, &d_gradient_, &d_updates_, &d_version_, &d_root_, &d_row_of_, &d_stored_keys_,
-                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_chain_, &d_chain2_, &d_chain3_, &d_ret_q_, &d_ret_row_, &d_ent_row_, &d_row_mask_, &d_src_off_, &d_src_cnt_, &d_word_base_, &d_scan_, &d_sk_, &d_rank_, &d_cnt_,
+                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_chain_, &d_chain2_, &d_chain3_, &d_ret_q_, &d_ret_row_, &d_ent_row_, &d_row_mask_, &d_src_off_, &d_src_cnt_, &d_word_base_, &d_scan_, &d_sk_, &d_cnt_,
                    &d_push_count_, &d_push_base_, &d_recv_idx_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
                    &d_qkey_r_, &d_qver_r_, &d_pkey_s_, &d_pupd_s_, &d_pval_s_, &d_pkey_r_, &d_pupd_r_, &d_pval_r_,
                    &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,
@@ -1205,7 +1233,7 @@ void HetuTable::releaseAll() {
   }
   for (BatchDesc *b : {&cur_batch_, &prev_batch_})
     for (DevBuf *d : {&b->keys, &b->idx_map, &b->sorted_pos, &b->uniq, &b->uniq_owner, &b->uniq_row,
-                      &b->run_start, &b->meta, &b->pos_row, &b->heavy, &b->need_push, &b->push_slot})
+                      &b->run_start, &b->meta, &b->pos_row, &b->heavy, &b->need_push, &b->push_slot, &b->rank})
       d->release();
   for (Span &sp : spans_) {
     cudaEventDestroy(sp.a);

@@ -63,12 +63,16 @@ struct BatchDesc {
   bool order_recorded = false;
   bool decided = false;            // the push decision for this batch has been enqueued
   bool order_pending = false;      // the run-ordering kernels of this batch are not enqueued yet
-  hctr_dedupe_args order_args;     // what they will be launched with
+  bool dedupe_pending = false;     // single-rank tables: the dedupe pipeline of this batch is not enqueued yet
+  hctr_dedupe_args order_args;     // what both will be launched with
   DevBuf keys, idx_map, sorted_pos, uniq, uniq_owner, uniq_row, run_start, meta, pos_row, heavy;
   // Push decision of this batch (multi-rank tables): flag and send slot per unique key.  They belong to the batch
   // because the decision is taken at the end of the batch's own push_pull and consumed by the next one; a larger
   // batch arriving in between must not move them.
   DevBuf need_push, push_slot;
+  // rank of every position inside its run; later the staging area of the batch's run ordering (its own buffer, so
+  // that the ordering of one batch can overlap the dedupe of the next)
+  DevBuf rank;
   std::vector<size_t> seg;         // [n+1] first unique of each owner
   std::vector<size_t> query_send;  // [n] unique keys addressed to each owner
   std::vector<size_t> query_recv;  // [n] keys each requester sends to me
@@ -144,7 +148,15 @@ class HetuTable {
   // it are dropped, so the next push_pull behaves like the first one of a fresh table.
   void exportState(const std::string &path);
   void importState(const std::string &path);
-  const StepStats &stats() const { return stats_; }
+  // (A single-rank table learns the unique count of its current batch only when the dedupe, which runs behind the
+  // step, has finished: asking waits for it.)
+  const StepStats &stats() {
+    if (cur_batch_.pending) {
+      quiesce();
+      stats_.unique = cur_batch_.unique_size;
+    }
+    return stats_;
+  }
   // "none" (single rank), "nccl", "inproc" or "p2p"
   const char *exchangeName() const;
   // Per-phase device time.  While enabled, every phase is bracketed by two events on the table's
@@ -170,6 +182,7 @@ class HetuTable {
                  const float *recv_val, const float *embedding, float *dst, uint32_t *err, cudaStream_t stream);
   void launchPushDecide(BatchDesc &b);
   void flushOrdering(BatchDesc &b);  // enqueues a batch's deferred run ordering
+  void flushDedupe(BatchDesc &b);    // enqueues a batch's deferred dedupe pipeline (single-rank tables)
   void quiesce();  // every stream drained, pending batch sizes read back
   void exchangeP2P(embed_t *dst_dev);
   const void *stageIn(const void *ptr, size_t bytes, DevBuf &buf, cudaStream_t s);
@@ -205,7 +218,7 @@ class HetuTable {
   size_t length_pad_ = 0;
 
   // dedupe scratch (persistent, all-zero between calls) and per-step scratch
-  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_ret_row_, d_ent_row_, d_row_mask_, d_src_off_, d_src_cnt_, d_word_base_, d_scan_, d_sk_, d_rank_, d_cnt_;
+  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_ret_row_, d_ent_row_, d_row_mask_, d_src_off_, d_src_cnt_, d_word_base_, d_scan_, d_sk_, d_cnt_;
   DevBuf d_push_count_, d_push_base_, d_recv_idx_, d_err_;
   size_t shared_capacity_ = 0;
   uint32_t dedupe_epoch_ = 0;

@@ -192,13 +192,13 @@ __global__ void __launch_bounds__(kThreads) dedupe_scatter(hctr_dedupe_args a) {
   const size_t i = mapped_pos(t, a.batch, a.stride);
   const u64 sk = a.sk[i];
   if (sk == ~0ull) {
-    a.pos_row[i] = HCTR_INVALID_ROW;
+    if (a.pos_row) a.pos_row[i] = HCTR_INVALID_ROW;
     return;
   }
   const u32 u = (u32)a.idx_map[i];
   const u32 rk = a.rank_in_run[i];
   a.sorted_pos[a.run_start[u] + rk] = (u32)i;
-  a.pos_row[i] = a.uniq_row[u];
+  if (a.pos_row) a.pos_row[i] = a.uniq_row[u];
   if (rk == 0) {
     // leave the persistent scratch all-zero for the next batch (once per unique key)
     a.bits[sk >> 6] = 0;
@@ -331,9 +331,40 @@ __global__ void __launch_bounds__(kThreads) ingest_keys(const long long *__restr
   if (i < n) dst[i] = src[i];
 }
 
+// The same, plus the local row of every batch position (pos_row[i] = row_of[key] or HCTR_INVALID_ROW): all the
+// row expansion needs to know about a batch whose keys are stored here, so that it does not have to wait for the
+// dedupe pipeline.  src may equal dst (keys already in place).  A key outside [0, length) sets bit
+// HCTR_ERR_KEY_RANGE in *err.
+__global__ void __launch_bounds__(kThreads) ingest_keys_rows(const long long *__restrict__ src,
+                                                             long long *__restrict__ dst, size_t n,
+                                                             u32 *__restrict__ meta, unsigned meta_words,
+                                                             const int32_t *__restrict__ row_of, size_t length,
+                                                             int32_t *__restrict__ pos_row, u32 *__restrict__ err) {
+  const size_t i = (size_t)blockIdx.x * kThreads + threadIdx.x;
+  if (i < meta_words) meta[i] = 0;
+  if (i < n) {
+    const long long k = src[i];
+    if (src != dst) dst[i] = k;
+    int32_t row = HCTR_INVALID_ROW;
+    if (k >= 0 && (size_t)k < length) row = row_of[k];
+    else atomicOr(err, HCTR_ERR_KEY_RANGE);
+    pos_row[i] = row;
+  }
+}
+
 }  // namespace hctr
 
 using namespace hctr;
+
+extern "C" int hctr_ingest_keys_rows(const int64_t *src, int64_t *dst, size_t n, uint32_t *meta, unsigned meta_words,
+                                     const int32_t *row_of, size_t length, int32_t *pos_row, uint32_t *err,
+                                     void *stream) {
+  const size_t items = n > meta_words ? n : meta_words;
+  ingest_keys_rows<<<grid_for(items ? items : 1, kThreads), kThreads, 0, (cudaStream_t)stream>>>(
+      (const long long *)src, (long long *)dst, n, meta, meta_words, row_of, length, pos_row, err);
+  count_launches(1);
+  return launch_status();
+}
 
 extern "C" int hctr_detect_key_stride(const int64_t *keys, size_t n, uint32_t *scores, void *stream) {
   key_stride_scores<<<64, kThreads, 0, (cudaStream_t)stream>>>((const long long *)keys, n, scores);

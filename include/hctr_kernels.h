@@ -149,7 +149,7 @@ typedef struct hctr_dedupe_args {
   uint32_t *run_start;      /* [B+1] first slot of each unique key's run in sorted_pos; entry U = batch */
   uint32_t *sorted_pos;     /* [B] batch positions grouped by unique, ascending inside a group */
   int32_t *idx_map;         /* [B] batch position -> unique index */
-  int32_t *pos_row;         /* [B] batch position -> local row or HCTR_INVALID_ROW */
+  int32_t *pos_row;         /* [B] batch position -> local row or HCTR_INVALID_ROW; null = not wanted (see hctr_ingest_keys_rows) */
   uint32_t *heavy_list;     /* [B/32 + 2] unique indices whose run is longer than HCTR_LIGHT_RUN */
   uint32_t *meta;           /* [HCTR_META_WORDS + nrank + 1]: see HCTR_META_* */
   /* optional: a second stream (cudaStream_t) and two events (cudaEvent_t).  When given, the two
@@ -188,6 +188,12 @@ int hctr_detect_key_stride(const int64_t *keys, size_t n, uint32_t *scores, void
 /* Front of the pipeline for keys that already live in device memory: dst[0..n) = src[0..n) (the table's private
  * copy, so that the caller may reuse its buffer) and meta[0..meta_words) = 0, in one launch. */
 int hctr_ingest_keys(const int64_t *src, int64_t *dst, size_t n, uint32_t *meta, unsigned meta_words, void *stream);
+/* hctr_ingest_keys plus pos_row[i] = row_of[keys[i]] (HCTR_INVALID_ROW for a key that is not stored here or lies
+ * outside [0, length); the latter also sets HCTR_ERR_KEY_RANGE in *err).  With pos_row known this early the row
+ * expansion of a batch whose keys are all stored locally does not depend on the dedupe pipeline at all.  src may
+ * equal dst.  Part of what cvt_embedding_idx_2_offset did, csrc/core/preprocess.cu:62-76. */
+int hctr_ingest_keys_rows(const int64_t *src, int64_t *dst, size_t n, uint32_t *meta, unsigned meta_words,
+                          const int32_t *row_of, size_t length, int32_t *pos_row, uint32_t *err, void *stream);
 
 /* The run-ordering half of the pipeline alone (positions of every unique key's run in ascending batch order
  * inside sorted_pos), for callers that deferred it: same args as the hctr_dedupe_map call it completes, on a

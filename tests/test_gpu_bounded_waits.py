@@ -20,14 +20,7 @@ import hetuctr_b200 as hb  # noqa: E402
 HCTR_ERR_TIMEOUT = 8
 
 
-class Box(ctypes.Structure):  # hctr_p2p_box, include/hctr_kernels.h
-    _fields_ = [(n, ctypes.c_void_p) for n in ("hdr", "qkey", "qver", "pkey", "pupd", "pval", "flag", "rver", "rval")]
-
-
-class Ctx(ctypes.Structure):  # hctr_p2p_ctx
-    _fields_ = [("nrank", ctypes.c_int), ("rank", ctypes.c_int), ("cap", ctypes.c_uint32), ("width", ctypes.c_size_t),
-                ("box", ctypes.c_void_p), ("cnt_in", ctypes.c_void_p), ("err", ctypes.c_void_p),
-                ("timeout_ns", ctypes.c_ulonglong)]
+from hetuctr_b200.owner_replay import Box, Ctx  # noqa: E402  (ctypes mirrors of hctr_p2p_box / hctr_p2p_ctx)
 
 
 def _mailbox(nrank, timeout_ms):

@@ -179,3 +179,15 @@ def test_ingest_keys_and_deferred_ordering():
     torch.cuda.synchronize()
     idx_map = t["idx_map"].cpu().numpy()
     assert np.array_equal(t["sorted_pos"].cpu().numpy().astype(np.int64), np.argsort(idx_map, kind="stable"))
+
+
+@pytest.mark.parametrize("sources,width,rows", [(8, 128, 5000), (4, 32, 3000), (32, 8, 800), (3, 132, 2000), (2, 64, 1000)])
+def test_owner_side_kernels_on_synthetic_mailbox(sources, width, rows):
+    """hctr_p2p_owner_mark / _apply / _stale_scan / _gather on a mailbox filled the way `sources - 1` peers would
+    fill it (hot rows pushed by many of them), against numpy applying the sources one after the other."""
+    from hetuctr_b200.owner_replay import OwnerReplay
+    r = OwnerReplay(sources, rows, width, pushed=rows * 2, queries=rows * 3, alpha=1.05, seed=sources)
+    distinct = len(np.unique(np.concatenate(r.push_keys)))
+    assert sum(len(k) for k in r.push_keys) > distinct  # several pushers per row do occur
+    assert r.check()
+    assert r.check()  # a second step on the same scratch: epochs, tickets and sequence numbers move on
