@@ -146,8 +146,12 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
       b->push_recv.assign(nrank_, 0);
       b->ret_send.assign(nrank_, 0);
       b->ret_recv.assign(nrank_, 0);
+      HCTR_CUDA(cudaMallocHost(&b->h_meta, (HCTR_META_WORDS + (size_t)nrank_ + 1) * sizeof(uint32_t)));
       reserveBatch(*b, 1);
     }
+    HCTR_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&h_ingest_err_), 64, cudaHostAllocMapped));
+    *h_ingest_err_ = 0;
+    HCTR_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&d_ingest_err_), h_ingest_err_, 0));
     reserveShared(1);
     h_pinned_words_ = HCTR_META_WORDS + (size_t)nrank_ + 1 + 12 * (size_t)nrank_ + 16;
     HCTR_CUDA(cudaMallocHost(&h_pinned_, h_pinned_words_ * sizeof(uint32_t)));
@@ -321,7 +325,9 @@ void HetuTable::reserveShared(size_t batch) {
 // ------------------------------------------------------------------------------------------------
 void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   HCTR_CUDA(cudaSetDevice(device_id_));
-  finalizePending();
+  // A single-rank table never waits for its dedupe here: the next reduction reads the batch's sizes on the device.
+  if (nrank_ == 1) flushDedupe(cur_batch_);  // two preprocess calls in a row: the first one's dedupe is still due
+  else finalizePending();
   batch_open_ = true;
   profile_ = profile_every_ > 0 && (profile_step_++ % (size_t)profile_every_) == 0;
   flushOrdering(cur_batch_);  // normally done by push_pull already; two preprocess calls in a row get here
@@ -353,7 +359,7 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   }
   HCTR_LAUNCH(hctr_ingest_keys_rows(key_src, cur.keys.as<int64_t>(), batch_size, cur.meta.as<uint32_t>(),
                                     (unsigned)meta_words, d_row_of_.as<int32_t>(), kEmbeddingIDMax,
-                                    cur.pos_row.as<int32_t>(), d_err_.as<uint32_t>() + 9, stream_main_));
+                                    cur.pos_row.as<int32_t>(), d_ingest_err_, stream_main_));
   HCTR_CUDA(cudaEventRecord(ev_keys_, stream_main_));
 
   if (!key_stride_known_ && batch_size >= 4096) detectKeyStride(cur);  // once per table
@@ -414,8 +420,16 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
     // ingest), so its launches are left to push_pull, AFTER the reduction and the expansion have been enqueued: the
     // host reaches those sooner.  Wait only until the caller's key buffer has been consumed.
     HCTR_CUDA(cudaEventSynchronize(ev_keys_));
+    if (*h_ingest_err_) {
+      // a key outside the table: drop the batch (its dedupe is not enqueued yet) and report right away
+      *h_ingest_err_ = 0;
+      cur.dedupe_pending = cur.order_pending = cur.pending = false;
+      cur.batch_size = cur.unique_size = cur.n_heavy = 0;
+      throw std::runtime_error("preprocess: a key is outside [0, length)");
+    }
     return;
   }
+  *h_ingest_err_ = 0;  // multi-rank tables learn about bad keys from the dedupe (which also checks the owners)
   flushDedupe(cur);
   int sp;
   uint32_t *h_cnt_s = h_pinned_ + meta_words;
@@ -506,7 +520,7 @@ void HetuTable::flushDedupe(BatchDesc &b) {
   HCTR_LAUNCH(hctr_dedupe_map(&b.order_args, stream_main_));
   toc(sp);
   const size_t meta_words = HCTR_META_WORDS + nrank_ + 1;
-  HCTR_CUDA(cudaMemcpyAsync(h_pinned_, b.meta.p, meta_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
+  HCTR_CUDA(cudaMemcpyAsync(b.h_meta, b.meta.p, meta_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
 }
 
 void HetuTable::flushOrdering(BatchDesc &b) {
@@ -520,27 +534,33 @@ void HetuTable::flushOrdering(BatchDesc &b) {
 
 // Reads the counts the preprocess pipeline copied to pinned memory into the batch descriptors.
 // The stream must have drained.
+uint32_t HetuTable::readSizes(BatchDesc &b) {
+  const int n = nrank_;
+  const uint32_t *h_meta = b.h_meta;
+  b.pending = false;
+  b.unique_size = h_meta[HCTR_META_UNIQUE];
+  b.n_heavy = h_meta[HCTR_META_NHEAVY];
+  for (int p = 0; p <= n; p++) b.seg[p] = h_meta[HCTR_META_SEG + p];
+  for (int p = 0; p < n; p++) b.query_send[p] = b.seg[p + 1] - b.seg[p];
+  return h_meta[HCTR_META_ERR];
+}
+
 void HetuTable::finalizeBatch() {
   BatchDesc &cur = cur_batch_, &prev = prev_batch_;
   const int n = nrank_;
   const size_t meta_words = HCTR_META_WORDS + n + 1;
-  const uint32_t *h_meta = h_pinned_;
   const uint32_t *h_cnt_s = h_pinned_ + meta_words;
   const uint32_t *h_cnt_r = h_cnt_s + 2 * n;
-  cur.pending = false;
-  cur.unique_size = h_meta[HCTR_META_UNIQUE];
-  cur.n_heavy = h_meta[HCTR_META_NHEAVY];
-  for (int p = 0; p <= n; p++) cur.seg[p] = h_meta[HCTR_META_SEG + p];
+  const uint32_t err = readSizes(cur);
   for (int p = 0; p < n; p++) {
-    cur.query_send[p] = cur.seg[p + 1] - cur.seg[p];
     const bool host_counts = n > 1 && !use_p2p_;  // the device-driven exchange keeps counts on the device
     cur.query_recv[p] = host_counts ? h_cnt_r[2 * p] : cur.query_send[p];
     prev.push_send[p] = host_counts ? h_cnt_s[2 * p + 1] : 0;
     prev.push_recv[p] = host_counts ? h_cnt_r[2 * p + 1] : 0;
   }
-  if (h_meta[HCTR_META_ERR] & HCTR_ERR_TIMEOUT)
+  if (err & HCTR_ERR_TIMEOUT)
     throw std::runtime_error("preprocess: a chained scan gave up waiting for an earlier thread block");
-  if (h_meta[HCTR_META_ERR] & HCTR_ERR_KEY_RANGE) {
+  if (err & HCTR_ERR_KEY_RANGE) {
     // leave a consistent (empty) batch behind, then report
     cur.batch_size = 0;
     cur.unique_size = 0;
@@ -549,12 +569,22 @@ void HetuTable::finalizeBatch() {
   }
 }
 
+// Single-rank tables hand a batch on to the next step without ever reading its sizes on the host; whoever wants
+// them for the previous batch (dump, stats) gets them here.  stream_main_ must have drained.
+void HetuTable::finalizePrev() {
+  if (!prev_batch_.pending) return;
+  const uint32_t err = readSizes(prev_batch_);
+  if (err & HCTR_ERR_TIMEOUT)
+    throw std::runtime_error("preprocess: a chained scan gave up waiting for an earlier thread block");
+}
+
 void HetuTable::finalizePending() {
-  if (!cur_batch_.pending) return;
+  if (!cur_batch_.pending && !prev_batch_.pending) return;
   flushDedupe(cur_batch_);
   HCTR_CUDA(cudaStreamSynchronize(stream_main_));
   collectSpans();
-  finalizeBatch();
+  finalizePrev();  // (the dedupe of the previous batch sits in front of this one's on the same stream)
+  if (cur_batch_.pending) finalizeBatch();
 }
 
 const void *HetuTable::stageIn(const void *ptr, size_t bytes, DevBuf &buf, cudaStream_t st) {
@@ -625,9 +655,13 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   stats_.queried_keys = q_recv;
 
   // A. duplicate-gradient reduction + local apply + pack (generateGradient)
-  if (prev.unique_size > 0) {
+  // A single-rank table has not read the previous batch's sizes (that would mean waiting for its dedupe on the
+  // host): the kernels take them from the batch's meta words on the device, the host passes upper bounds.
+  const bool sizes_on_device = n == 1 && prev.pending;
+  if (sizes_on_device ? prev.batch_size > 0 : prev.unique_size > 0) {
     hctr_reduce_args r;
-    r.n_unique = prev.unique_size;
+    r.meta = sizes_on_device ? prev.meta.as<uint32_t>() : nullptr;
+    r.n_unique = sizes_on_device ? prev.batch_size : prev.unique_size;
     r.width = W;
     r.n_cached = kNonLocalStorageMax;
     r.neg_lr = -learning_rate_;
@@ -635,7 +669,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     r.run_start = prev.run_start.as<uint32_t>();
     r.sorted_pos = prev.sorted_pos.as<uint32_t>();
     r.heavy_list = prev.heavy.as<uint32_t>();
-    r.n_heavy = prev.n_heavy;
+    r.n_heavy = sizes_on_device ? prev.batch_size / (HCTR_LIGHT_RUN + 1) + 1 : prev.n_heavy;
     r.uniq = prev.uniq.as<int64_t>();
     r.uniq_row = prev.uniq_row.as<int32_t>();
     r.need_push = n > 1 ? prev.need_push.as<uint32_t>() : nullptr;
@@ -869,9 +903,8 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
 
   if (dst_staged)
     HCTR_CUDA(cudaMemcpyAsync(dst, dst_dev, cur.batch_size * W * sizeof(embed_t), cudaMemcpyDeviceToHost, tail));
-  // two error words: bounded waits of the expand kernel, key range check of the key ingest
-  uint32_t *h_expand_err = h_pinned_ + h_pinned_words_ - 2;
-  HCTR_CUDA(cudaMemcpyAsync(h_expand_err, d_err_.as<uint32_t>() + 8, 2 * sizeof(uint32_t), cudaMemcpyDeviceToHost, tail));
+  uint32_t *h_expand_err = h_pinned_ + h_pinned_words_ - 1;  // bounded waits of the expand kernel
+  HCTR_CUDA(cudaMemcpyAsync(h_expand_err, d_err_.as<uint32_t>() + 8, sizeof(uint32_t), cudaMemcpyDeviceToHost, tail));
   HCTR_CUDA(cudaStreamSynchronize(tail));
   collectSpans();
   if (h_expand_err[0]) {
@@ -882,12 +915,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     finalizeBatch();
     stats_.unique = cur.unique_size;
   }
-  if (n == 1 && h_expand_err[1]) {
-    // a key outside the table: the dedupe has seen it too; wait for it and report from here
-    HCTR_CUDA(cudaMemsetAsync(d_err_.as<uint32_t>() + 9, 0, sizeof(uint32_t), tail));
-    HCTR_CUDA(cudaStreamSynchronize(tail));
-    finalizePending();
-  }
+
   uint32_t p2p_err = 0;
   if (p2p_counts_pending_) {
     p2p_counts_pending_ = false;
@@ -1230,7 +1258,11 @@ void HetuTable::releaseAll() {
   for (BatchDesc *b : {&cur_batch_, &prev_batch_}) {
     if (b->ev_order) cudaEventDestroy(b->ev_order);
     b->ev_order = nullptr;
+    if (b->h_meta) cudaFreeHost(b->h_meta);
+    b->h_meta = nullptr;
   }
+  if (h_ingest_err_) cudaFreeHost(h_ingest_err_);
+  h_ingest_err_ = d_ingest_err_ = nullptr;
   for (BatchDesc *b : {&cur_batch_, &prev_batch_})
     for (DevBuf *d : {&b->keys, &b->idx_map, &b->sorted_pos, &b->uniq, &b->uniq_owner, &b->uniq_row,
                       &b->run_start, &b->meta, &b->pos_row, &b->heavy, &b->need_push, &b->push_slot, &b->rank})

@@ -73,6 +73,7 @@ struct BatchDesc {
   // rank of every position inside its run; later the staging area of the batch's run ordering (its own buffer, so
   // that the ordering of one batch can overlap the dedupe of the next)
   DevBuf rank;
+  uint32_t *h_meta = nullptr;      // pinned: the batch's meta words (sizes, segment starts, error bits) as read back
   std::vector<size_t> seg;         // [n+1] first unique of each owner
   std::vector<size_t> query_send;  // [n] unique keys addressed to each owner
   std::vector<size_t> query_recv;  // [n] keys each requester sends to me
@@ -151,9 +152,10 @@ class HetuTable {
   // (A single-rank table learns the unique count of its current batch only when the dedupe, which runs behind the
   // step, has finished: asking waits for it.)
   const StepStats &stats() {
-    if (cur_batch_.pending) {
+    if (cur_batch_.pending || prev_batch_.pending) {
       quiesce();
       stats_.unique = cur_batch_.unique_size;
+      stats_.prev_unique = prev_batch_.unique_size;
     }
     return stats_;
   }
@@ -178,6 +180,8 @@ class HetuTable {
   void releaseAll();
   void finalizeBatch();
   void finalizePending();
+  void finalizePrev();   // single-rank tables: sizes of the previous batch, read back on demand
+  uint32_t readSizes(BatchDesc &b);  // copies b's meta words into the descriptor; returns the error bits
   int expandRows(size_t batch, size_t width, const int32_t *pos_row, const int32_t *idx_map, const uint32_t *recv_slot,
                  const float *recv_val, const float *embedding, float *dst, uint32_t *err, cudaStream_t stream);
   void launchPushDecide(BatchDesc &b);
@@ -236,6 +240,9 @@ class HetuTable {
   void *h_src_ = nullptr;         // pinned staging of the per-source list descriptors
   size_t p2p_off_cap_ = 0;        // mailbox capacity d_src_off_ was filled for
   uint32_t *h_pinned_ = nullptr;  // pinned mirror for counts read back from the device
+  // Mapped pinned word the key ingest reports an out-of-range key through: the host reads it right after the
+  // ingest without a copy.
+  uint32_t *h_ingest_err_ = nullptr, *d_ingest_err_ = nullptr;
   size_t h_pinned_words_ = 0;
 
   BatchDesc cur_batch_, prev_batch_;

@@ -114,6 +114,11 @@ __global__ void push_counts(const u32 *__restrict__ meta, int nrank, const u32 *
 //   type 2  cached, push    -> emb += s, pending += s, push pending, clear it, version += pending count
 //   type 3  cached, hold    -> emb += s, pending += s, pending count += count
 
+// number of unique keys / of long runs of the batch: from the batch's meta words when the host passed them
+__device__ __forceinline__ size_t unique_count(const hctr_reduce_args &a) {
+  return a.meta ? (size_t)a.meta[HCTR_META_UNIQUE] : a.n_unique;
+}
+
 struct RowTarget {
   int type;
   size_t slot;
@@ -214,7 +219,7 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short(ReduceKernelArgs k
   typedef typename R::T T;
   const size_t u = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES;
   const unsigned gl = threadIdx.x % LANES;
-  if (u >= a.n_unique) return;
+  if (u >= unique_count(a)) return;
   const u32 l = a.run_start[u], r = a.run_start[u + 1];
   if (r - l > HCTR_LIGHT_RUN) return;  // handled by grad_reduce_long
   PushDest dest;
@@ -278,12 +283,13 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_wide(ReduceKernelA
   T *emb_base = reinterpret_cast<T *>(a.embedding);
   T *pend_base = reinterpret_cast<T *>(a.pending);
   // (A one-wave grid with chunks drawn from a shared counter was measured and was slower: 105 us vs 92 us.)
-  for (size_t u0 = warp * kWideChunk; u0 < a.n_unique; u0 += n_warps * kWideChunk) {
+  const size_t n_unique = unique_count(a);
+  for (size_t u0 = warp * kWideChunk; u0 < n_unique; u0 += n_warps * kWideChunk) {
     const size_t my_u = u0 + lane;
     u32 l = 0, len = 0, p0 = 0;
     unsigned long long outp = 0;  // destination of this lane's key if it is pushed
     int row = 0, type = -1;       // type -1: nothing to do for this lane's key
-    if (lane < kWideChunk && my_u < a.n_unique) {
+    if (lane < kWideChunk && my_u < n_unique) {
       l = a.run_start[my_u];
       len = a.run_start[my_u + 1] - l;
       if (len > 0 && len <= HCTR_LIGHT_RUN) {
@@ -439,7 +445,7 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKerne
   const u64 warp = (u64)(threadIdx.x >> 5) * gridDim.x + blockIdx.x;
   const u64 n_warps = ((u64)gridDim.x * kThreads) >> 5;
   const size_t E = a.width / 4;
-  const u32 U = (u32)a.n_unique;
+  const u32 U = (u32)unique_count(a);
   const T *grad = reinterpret_cast<const T *>(a.grad);
   T *emb_base = reinterpret_cast<T *>(a.embedding);
   T *pend_base = reinterpret_cast<T *>(a.pending);
@@ -582,8 +588,9 @@ __device__ __forceinline__ void cp_async_elem(void *smem_dst, const void *gsrc) 
 }
 
 template <bool VEC>
-__global__ void __launch_bounds__(kLongThreads) grad_reduce_long(ReduceKernelArgs ka, u32 n_heavy, u32 *work_counter) {
+__global__ void __launch_bounds__(kLongThreads) grad_reduce_long(ReduceKernelArgs ka, u32 n_heavy_host, u32 *work_counter) {
   const hctr_reduce_args &a = ka.a;
+  const u32 n_heavy = a.meta ? a.meta[HCTR_META_NHEAVY] : n_heavy_host;
   typedef RowT<VEC> R;
   typedef typename R::T T;
   extern __shared__ __align__(16) unsigned char smem_raw[];

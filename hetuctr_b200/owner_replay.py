@@ -1,7 +1,7 @@
 """Replays the OWNER side of one step of the peer-to-peer exchange on a single GPU, from synthetic traffic.
 
   python -m hetuctr_b200.owner_replay [--sources 8] [--rows 4200000] [--width 128] [--pushed 68000]
-                                      [--queries 77000] [--iters 20] [--check]
+                                      [--queries 77000] [--iters 20] [--check | --cap 212992]
 
 In a job of several GPUs the owner-side kernels (source marking + versions, row apply, staleness scan, row gather)
 run once per step on what the peers stored into this rank's mailbox.  To time or profile them in isolation this
@@ -36,7 +36,7 @@ def cnt_words(n):
 
 class OwnerReplay:
     def __init__(self, sources=8, rows=4_200_000, width=128, pushed=68_000, queries=77_000, alpha=1.05, seed=0,
-                 device=0):
+                 device=0, cap=0, shared_peer=False):
         import torch
 
         import hetuctr_b200 as hb
@@ -59,17 +59,21 @@ class OwnerReplay:
 
         # traffic of the peers: key-sorted unique keys per source, drawn from a bounded Zipf over this rank's rows
         def draw(m):
-            ranks = np.minimum(rng.zipf(alpha, size=int(m * 1.6)) - 1, S - 1).astype(np.int64)
-            ks = np.unique(ranks * 2654435761 % S) * n  # the same hot rows for every source, spread over the shard
+            m = min(m, S)
+            ks = np.zeros(0, np.int64)
+            while len(ks) < m:  # m distinct rows, the hot ones (low Zipf ranks) in nearly every source's list
+                ranks = np.minimum(rng.zipf(alpha, size=2 * m) - 1, S - 1).astype(np.int64)
+                ks = np.unique(np.concatenate([ks, ranks * 2654435761 % S]))
             if len(ks) > m:
                 ks = np.sort(rng.choice(ks, m, replace=False))
-            return ks.astype(np.int64)
+            return ks * n  # this rank's keys
 
         per_push = max(pushed // max(n - 1, 1), 1)
         per_query = max(queries // n, 1)
         self.push_keys = [np.zeros(0, np.int64) if s == self.rank else draw(per_push) for s in range(n)]
         self.query_keys = [draw(per_query) for _ in range(n)]
-        self.cap = cap = int(max(max(len(k) for k in self.push_keys), max(len(k) for k in self.query_keys), 1))
+        # rows per (mailbox, source) sub-region: a table uses its batch size, which also sizes the kernels' grids
+        self.cap = cap = int(max(cap, max(len(k) for k in self.push_keys), max(len(k) for k in self.query_keys), 1))
 
         def z(shape, dt):
             return torch.zeros(shape, dtype=dt, device=dev)
@@ -80,7 +84,9 @@ class OwnerReplay:
                         flag=z(n * cap, torch.uint8), rver=z(n * cap, torch.int64), rval=z((n * cap, W), torch.float32))
 
         self.mine = region_set()
-        self.peers = [self.mine if s == self.rank else region_set() for s in range(n)]
+        # one stand-in mailbox per peer; `shared_peer` lets all peers share one (timing runs with a large cap)
+        shared = region_set() if shared_peer else None
+        self.peers = [self.mine if s == self.rank else (shared or region_set()) for s in range(n)]
         self.push_upd, self.push_val, self.query_ver = [], [], []
         for s in range(n):
             k = self.push_keys[s]
@@ -236,8 +242,12 @@ def main():
     ap.add_argument("--queries", type=int, default=77_000)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--check", action="store_true")
+    ap.add_argument("--cap", type=int, default=0,
+                    help="rows per mailbox sub-region (a table uses its batch size; it sizes the grids); with a cap "
+                         "the peers' stand-in mailboxes are one shared allocation and --check is not available")
     a = ap.parse_args()
-    r = OwnerReplay(a.sources, a.rows, a.width, a.pushed, a.queries)
+    assert not (a.cap and a.check), "--check needs one stand-in mailbox per peer: leave --cap out"
+    r = OwnerReplay(a.sources, a.rows, a.width, a.pushed, a.queries, cap=a.cap, shared_peer=a.cap > 0)
     if a.check:
         r.check()
         print("check ok: versions and rows equal a source-by-source numpy evaluation")

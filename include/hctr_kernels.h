@@ -373,6 +373,10 @@ typedef struct hctr_reduce_args {
   void *side_stream;
   void *fork_event;
   void *join_event;
+  /* optional: the batch's meta words on the device.  When non-null the kernels read the number of unique keys and
+   * of long runs from meta[HCTR_META_UNIQUE] / meta[HCTR_META_NHEAVY] - the host need not have seen them - and
+   * n_unique / n_heavy are only upper bounds that size the grids. */
+  const uint32_t *meta;
 } hctr_reduce_args;
 
 int hctr_grad_reduce_apply_pack(const hctr_reduce_args *a, void *stream);

@@ -127,14 +127,13 @@ def test_out_of_range_key_raises_and_table_recovers(oracle_mod):
     N, W = 300, 4
     root = np.zeros(N, dtype=np.uint8)
     gw, ow = make_worlds(oracle_mod, 1, N, W, 0, 0, 0.1, root, [np.arange(N)])
-    # A single-rank table reports a bad key from the first call that synchronises with the device
-    # (push_pull, or the next preprocess); multi-rank tables report it from preprocess itself.
+    # the key ingest checks the range and preprocess reports it; the batch is dropped
     with pytest.raises(RuntimeError, match="outside"):
         gw.preprocess([[1, 2, N, 5]])
-        gw.push_pull(None)
+    gw.push_pull(None)
     with pytest.raises(RuntimeError, match="outside"):
         gw.preprocess([[-1]])
-        gw.preprocess([[1]])
+    gw.preprocess([[1]])
     gw.push_pull(None)
     rng = np.random.RandomState(6)
     batches = [[rng.randint(N, size=64)] for _ in range(3)]
