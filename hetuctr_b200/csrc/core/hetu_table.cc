@@ -396,12 +396,15 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   // recycled (two batches old) must be out of use.
   if (cur.order_recorded) HCTR_CUDA(cudaStreamWaitEvent(stream_main_, cur.ev_order, 0));
   if (!cur.ev_order) HCTR_CUDA(cudaEventCreateWithFlags(&cur.ev_order, cudaEventDisableTiming));
+  if (!cur.ev_scatter) HCTR_CUDA(cudaEventCreateWithFlags(&cur.ev_scatter, cudaEventDisableTiming));
   a.side_stream = stream_side_;
-  a.fork_event = ev_fork_;
+  a.fork_event = cur.ev_scatter;
   // The ordering kernels are not even enqueued here: push_pull enqueues them after the gradient reduction,
   // which brings the reduction (it only starts once push_pull is called) several launches forward.
   a.join_event = nullptr;
   cur.order_recorded = false;
+  cur.scatter_recorded = false;
+  cur.light_ordered = false;
   cur.order_pending = true;
   cur.order_args = a;
   // The push decision for the previous batch goes first: the gradient reduction (on its own stream, started
@@ -517,19 +520,30 @@ void HetuTable::flushDedupe(BatchDesc &b) {
   if (!b.dedupe_pending) return;
   b.dedupe_pending = false;
   int sp = tic(kPhDedupe);
-  HCTR_LAUNCH(hctr_dedupe_map(&b.order_args, stream_main_));
+  HCTR_LAUNCH(hctr_dedupe_map(&b.order_args, stream_main_));  // records b.ev_scatter behind its last kernel
+  b.scatter_recorded = true;
   toc(sp);
   const size_t meta_words = HCTR_META_WORDS + nrank_ + 1;
   HCTR_CUDA(cudaMemcpyAsync(b.h_meta, b.meta.p, meta_words * sizeof(uint32_t), cudaMemcpyDeviceToHost, stream_main_));
 }
 
+// The long runs (hot keys) are ordered on stream_side_; only the long-run kernel of the next reduction waits for
+// that.  The short runs are ordered by the reduction itself where its kernel can (orderLightRuns otherwise).
 void HetuTable::flushOrdering(BatchDesc &b) {
   if (!b.order_pending) return;
   b.order_pending = false;
-  HCTR_CUDA(cudaStreamWaitEvent(stream_side_, ev_fork_, 0));  // recorded after this batch's scatter
-  HCTR_LAUNCH(hctr_dedupe_order(&b.order_args, stream_side_));
+  flushDedupe(b);
+  HCTR_CUDA(cudaStreamWaitEvent(stream_side_, b.ev_scatter, 0));
+  HCTR_LAUNCH(hctr_dedupe_order_heavy(&b.order_args, stream_side_));
   HCTR_CUDA(cudaEventRecord(b.ev_order, stream_side_));
   b.order_recorded = true;
+}
+
+void HetuTable::orderLightRuns(BatchDesc &b, cudaStream_t s) {
+  if (b.light_ordered || !b.scatter_recorded) return;
+  HCTR_CUDA(cudaStreamWaitEvent(s, b.ev_scatter, 0));
+  HCTR_LAUNCH(hctr_dedupe_order_light(&b.order_args, s));
+  b.light_ordered = true;
 }
 
 // Reads the counts the preprocess pipeline copied to pinned memory into the batch descriptors.
@@ -691,7 +705,13 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     // Own stream: overlaps the (still running) dedupe of the current batch.  It needs the push decision of
     // the previous batch (ev_decide_) and nothing else from stream_main_.
     HCTR_CUDA(cudaStreamWaitEvent(stream_reduce_, ev_decide_, 0));
-    if (prev.order_recorded) HCTR_CUDA(cudaStreamWaitEvent(stream_reduce_, prev.ev_order, 0));
+    // the batch's runs must exist (end of its dedupe); the ordering of its long runs only concerns the long-run
+    // kernel, and the short runs are ordered by the streaming kernel as it loads them (or here, for the row
+    // widths and gradient buffers that kernel does not take)
+    if (prev.scatter_recorded) HCTR_CUDA(cudaStreamWaitEvent(stream_reduce_, prev.ev_scatter, 0));
+    if (!prev.light_ordered && !hctr_reduce_orders_short_runs(W, grad_dev)) orderLightRuns(prev, stream_reduce_);
+    r.short_runs_unordered = prev.light_ordered ? 0 : 1;
+    r.long_wait_event = prev.order_recorded ? prev.ev_order : nullptr;
     int sp = tic(kPhReduce, stream_reduce_);
     HCTR_LAUNCH(hctr_grad_reduce_apply_pack(&r, stream_reduce_));
     toc(sp, stream_reduce_);
@@ -1258,6 +1278,8 @@ void HetuTable::releaseAll() {
   for (BatchDesc *b : {&cur_batch_, &prev_batch_}) {
     if (b->ev_order) cudaEventDestroy(b->ev_order);
     b->ev_order = nullptr;
+    if (b->ev_scatter) cudaEventDestroy(b->ev_scatter);
+    b->ev_scatter = nullptr;
     if (b->h_meta) cudaFreeHost(b->h_meta);
     b->h_meta = nullptr;
   }

@@ -59,8 +59,11 @@ struct BatchDesc {
   size_t capacity = 0;
   size_t n_heavy = 0;  // runs longer than HCTR_LIGHT_RUN
   bool pending = false;  // sizes not yet read back from the device (single-rank tables defer this)
-  cudaEvent_t ev_order = nullptr;  // completion of this batch's run ordering (on the ordering stream)
+  cudaEvent_t ev_order = nullptr;  // completion of the ordering of this batch's long runs (on the ordering stream)
   bool order_recorded = false;
+  cudaEvent_t ev_scatter = nullptr;  // this batch's positions are in their runs (end of the dedupe pipeline)
+  bool scatter_recorded = false;
+  bool light_ordered = false;        // runs of up to HCTR_LIGHT_RUN positions have been put in ascending order
   bool decided = false;            // the push decision for this batch has been enqueued
   bool order_pending = false;      // the run-ordering kernels of this batch are not enqueued yet
   bool dedupe_pending = false;     // single-rank tables: the dedupe pipeline of this batch is not enqueued yet
@@ -187,6 +190,7 @@ class HetuTable {
   void launchPushDecide(BatchDesc &b);
   void flushOrdering(BatchDesc &b);  // enqueues a batch's deferred run ordering
   void flushDedupe(BatchDesc &b);    // enqueues a batch's deferred dedupe pipeline (single-rank tables)
+  void orderLightRuns(BatchDesc &b, cudaStream_t s);  // the short-run half of the ordering, where somebody needs it
   void quiesce();  // every stream drained, pending batch sizes read back
   void exchangeP2P(embed_t *dst_dev);
   const void *stageIn(const void *ptr, size_t bytes, DevBuf &buf, cudaStream_t s);

@@ -71,6 +71,9 @@ void HetuTable::quiesce() {
   HCTR_CUDA(cudaSetDevice(device_id_));
   finalizePending();
   flushOrdering(cur_batch_);
+  // whoever looks at a batch's position lists expects every run in ascending order
+  for (BatchDesc *b : {&cur_batch_, &prev_batch_})
+    if (b->batch_size > 0) orderLightRuns(*b, stream_side_);
   for (cudaStream_t s : {stream_main_, stream_side_, stream_reduce_, stream_reduce_side_, stream_apply_})
     if (s) HCTR_CUDA(cudaStreamSynchronize(s));
 }

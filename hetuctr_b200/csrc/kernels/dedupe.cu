@@ -421,8 +421,17 @@ extern "C" int hctr_dedupe_map(const hctr_dedupe_args *ap, void *stream) {
   return hctr_dedupe_order(ap, stream);
 }
 
-extern "C" int hctr_dedupe_order(const hctr_dedupe_args *ap, void *stream) {
-  cudaStream_t os = (cudaStream_t)stream;
+extern "C" int hctr_dedupe_order_light(const hctr_dedupe_args *ap, void *stream) {
+  const hctr_dedupe_args a = *ap;
+  size_t ctas = ((a.batch + 31) / 32 * 32 + kThreads - 1) / kThreads;  // one warp per 32 unique keys
+  if (ctas > (size_t)kSMs * 8) ctas = (size_t)kSMs * 8;
+  if (ctas == 0) ctas = 1;
+  dedupe_order_light<<<(unsigned)ctas, kThreads, 0, (cudaStream_t)stream>>>(a);
+  count_launches(1);
+  return launch_status();
+}
+
+extern "C" int hctr_dedupe_order_heavy(const hctr_dedupe_args *ap, void *stream) {
   const hctr_dedupe_args a = *ap;
   static bool attr_set = false;
   if (!attr_set) {
@@ -431,23 +440,20 @@ extern "C" int hctr_dedupe_order(const hctr_dedupe_args *ap, void *stream) {
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  {
-    size_t ctas = ((a.batch + 31) / 32 * 32 + kThreads - 1) / kThreads;  // one warp per 32 unique keys
-    if (ctas > (size_t)kSMs * 8) ctas = (size_t)kSMs * 8;
-    if (ctas == 0) ctas = 1;
-    dedupe_order_light<<<(unsigned)ctas, kThreads, 0, os>>>(a);
-  }
-  {
-    // window = the batch when it fits (small windows let several CTAs share an SM)
-    size_t wbits = (a.batch + 1023) / 1024 * 1024;
-    if (wbits > (size_t)kHeavyWindowBits) wbits = kHeavyWindowBits;
-    if (wbits < 1024) wbits = 1024;
-    const size_t smem = wbits / 8;
-    size_t per_sm = (200 * 1024) / (smem + 1024);
-    if (per_sm > 2) per_sm = 2;  // 1024-thread CTAs: at most 2 per SM
-    if (per_sm < 1) per_sm = 1;
-    dedupe_order_heavy<<<(unsigned)(kSMs * per_sm), 1024, smem, os>>>(a, (u32)wbits);
-  }
-  count_launches(2);
+  // window = the batch when it fits (small windows let several CTAs share an SM)
+  size_t wbits = (a.batch + 1023) / 1024 * 1024;
+  if (wbits > (size_t)kHeavyWindowBits) wbits = kHeavyWindowBits;
+  if (wbits < 1024) wbits = 1024;
+  const size_t smem = wbits / 8;
+  size_t per_sm = (200 * 1024) / (smem + 1024);
+  if (per_sm > 2) per_sm = 2;  // 1024-thread CTAs: at most 2 per SM
+  if (per_sm < 1) per_sm = 1;
+  dedupe_order_heavy<<<(unsigned)(kSMs * per_sm), 1024, smem, (cudaStream_t)stream>>>(a, (u32)wbits);
+  count_launches(1);
   return launch_status();
+}
+
+extern "C" int hctr_dedupe_order(const hctr_dedupe_args *ap, void *stream) {
+  const int rc = hctr_dedupe_order_light(ap, stream);
+  return rc ? rc : hctr_dedupe_order_heavy(ap, stream);
 }

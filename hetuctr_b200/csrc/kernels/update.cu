@@ -450,6 +450,9 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKerne
   T *emb_base = reinterpret_cast<T *>(a.embedding);
   T *pend_base = reinterpret_cast<T *>(a.pending);
   T *ring = ring_all + (size_t)(threadIdx.x >> 5) * D * E;
+  __shared__ u32 sort_all[kThreads];  // 32 words per warp
+  u32 *sort_buf = sort_all + (threadIdx.x & ~31u);
+  const bool unordered = a.short_runs_unordered != 0;
   const u32 n_pos = a.run_start[U];
   const u64 total = (u64)n_pos + 2ull * U;
   const u64 per_warp = (total + n_warps - 1) / n_warps;
@@ -493,6 +496,24 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKerne
           src = emb_base + (size_t)P.row * E;
         } else {
           const u32 q = P.l + (u32)P.j;
+          if (unordered && P.j == 0 && P.len >= 2) {
+            // First gradient row of a key whose run is still in arrival order: bring the whole run (at most 32
+            // positions) into the window, then put it in ascending order - a lane's place is the number of smaller
+            // positions in the run (positions are distinct).  Sums stay in batch order without a separate pass.
+            if (!have_window || q - q_base + P.len > 32u) {
+              q_base = q;
+              have_window = true;
+              sp = q_base + lane < n_pos ? a.sorted_pos[q_base + lane] : 0u;
+            }
+            const u32 s0 = q - q_base;
+            const bool in_run = lane - s0 < P.len;
+            u32 place = 0;
+            for (u32 k2 = 0; k2 < P.len; k2++) place += __shfl_sync(0xffffffffu, sp, (int)(s0 + k2)) < sp ? 1u : 0u;
+            if (in_run) sort_buf[place] = sp;
+            __syncwarp();
+            if (in_run) sp = sort_buf[lane - s0];
+            __syncwarp();
+          }
           if (!have_window || q - q_base >= 32u) {
             q_base = q;
             have_window = true;
@@ -1044,6 +1065,13 @@ extern "C" int hctr_push_decide_fused(const uint32_t *meta, int nrank, int rank,
   return launch_status();
 }
 
+// the streaming short-run kernel is the variant that can order its runs itself
+static bool streaming_shape(size_t width, bool aligned) { return aligned && width % 4 == 0 && width >= 128 && width <= 512; }
+
+extern "C" int hctr_reduce_orders_short_runs(size_t width, const float *grad) {
+  return streaming_shape(width, host_aligned16(grad)) ? 1 : 0;
+}
+
 extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *stream) {
   cudaStream_t s = (cudaStream_t)stream;
   const hctr_reduce_args a = *ap;
@@ -1058,7 +1086,8 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
     cudaError_t e = cudaEventRecord((cudaEvent_t)a.fork_event, s);
     if (e != cudaSuccess) return (int)e;
   }
-  if (al && a.width % 4 == 0 && a.width >= 128 && a.width <= 512 && a.n_unique < 0x7fffffffu) {
+  if (a.short_runs_unordered && !streaming_shape(a.width, al)) return (int)cudaErrorInvalidValue;
+  if (streaming_shape(a.width, al) && a.n_unique < 0x7fffffffu) {
     const size_t E = a.width / 4;
     const int variant = E <= 32 ? 0 : E <= 64 ? 1 : 2;
     void (*kernel)(ReduceKernelArgs) = variant == 0   ? grad_reduce_short_stream<8, 1>
@@ -1111,6 +1140,10 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
     if (a.side_stream && a.fork_event && a.join_event) {
       ls = (cudaStream_t)a.side_stream;
       cudaError_t e = cudaStreamWaitEvent(ls, (cudaEvent_t)a.fork_event, 0);
+      if (e != cudaSuccess) return (int)e;
+    }
+    if (a.long_wait_event) {  // ordering of the long runs, done on another stream
+      cudaError_t e = cudaStreamWaitEvent(ls, (cudaEvent_t)a.long_wait_event, 0);
       if (e != cudaSuccess) return (int)e;
     }
     cudaError_t em = cudaMemsetAsync(a.work_counter, 0, 2 * sizeof(u32), ls);

@@ -200,6 +200,11 @@ int hctr_ingest_keys_rows(const int64_t *src, int64_t *dst, size_t n, uint32_t *
  * stream that has waited for that call's fork_event.  Nothing but the next gradient reduction (and a reader
  * of sorted_pos) needs it. */
 int hctr_dedupe_order(const hctr_dedupe_args *a, void *stream);
+/* The two halves of hctr_dedupe_order: runs of 2..HCTR_LIGHT_RUN positions (one warp per run) and longer runs
+ * (a thread block per run).  The short-run half is not needed when the consumer orders short runs itself, see
+ * hctr_reduce_orders_short_runs. */
+int hctr_dedupe_order_light(const hctr_dedupe_args *a, void *stream);
+int hctr_dedupe_order_heavy(const hctr_dedupe_args *a, void *stream);
 
 /* ---------------------------------------------------------------------------------------------
  * Gradient push decision (previous batch).  Replaces decide_update_kernel + scan,
@@ -377,9 +382,19 @@ typedef struct hctr_reduce_args {
    * of long runs from meta[HCTR_META_UNIQUE] / meta[HCTR_META_NHEAVY] - the host need not have seen them - and
    * n_unique / n_heavy are only upper bounds that size the grids. */
   const uint32_t *meta;
+  /* runs of up to HCTR_LIGHT_RUN positions are in arbitrary order in sorted_pos (hctr_dedupe_order_light has not
+   * run): the kernel puts each of them in ascending order as it loads them.  Only legal when
+   * hctr_reduce_orders_short_runs(width, grad) is non-zero. */
+  int short_runs_unordered;
+  /* optional cudaEvent_t the long-run kernel waits for before it starts (the ordering of the long runs, when that
+   * runs on another stream); the short-run kernel does not wait for it */
+  void *long_wait_event;
 } hctr_reduce_args;
 
 int hctr_grad_reduce_apply_pack(const hctr_reduce_args *a, void *stream);
+/* Non-zero when, for rows of `width` floats and this gradient buffer, the short-run kernel is the one that can
+ * order its runs itself (short_runs_unordered). */
+int hctr_reduce_orders_short_runs(size_t width, const float *grad);
 
 /* ---------------------------------------------------------------------------------------------
  * Query generation.  Replaces lookup_version_kernel, csrc/core/generate_query.cu:91-106.
