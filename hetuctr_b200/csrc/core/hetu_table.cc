@@ -150,7 +150,7 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
       reserveBatch(*b, 1);
     }
     HCTR_CUDA(cudaHostAlloc(reinterpret_cast<void **>(&h_ingest_err_), 64, cudaHostAllocMapped));
-    *h_ingest_err_ = 0;
+    h_ingest_err_[0] = h_ingest_err_[1] = 0;
     HCTR_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void **>(&d_ingest_err_), h_ingest_err_, 0));
     reserveShared(1);
     h_pinned_words_ = HCTR_META_WORDS + (size_t)nrank_ + 1 + 12 * (size_t)nrank_ + 16;
@@ -352,15 +352,19 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
   // One launch in front of the pipeline: private copy of the keys (host keys are copied first, then taken in place),
   // cleared meta words, and the local row of every batch position - which is all the row expansion needs for keys
   // that are stored here, so a single-rank table starts it without waiting for the dedupe.
+  // A single-rank table ingests on the (idle) stream of its reduction: stream_main_ may still hold the previous
+  // batch's dedupe, which nothing here has to wait for.  The dedupe of this batch waits for ev_keys_.
+  cudaStream_t ks = n == 1 ? stream_reduce_ : stream_main_;
   const int64_t *key_src = reinterpret_cast<const int64_t *>(data_ptr);
   if (!keys_on_device) {
-    HCTR_CUDA(cudaMemcpyAsync(cur.keys.p, data_ptr, sizeof(index_t) * batch_size, cudaMemcpyDefault, stream_main_));
+    HCTR_CUDA(cudaMemcpyAsync(cur.keys.p, data_ptr, sizeof(index_t) * batch_size, cudaMemcpyDefault, ks));
     key_src = cur.keys.as<int64_t>();
   }
   HCTR_LAUNCH(hctr_ingest_keys_rows(key_src, cur.keys.as<int64_t>(), batch_size, cur.meta.as<uint32_t>(),
                                     (unsigned)meta_words, d_row_of_.as<int32_t>(), kEmbeddingIDMax,
-                                    cur.pos_row.as<int32_t>(), d_ingest_err_, stream_main_));
-  HCTR_CUDA(cudaEventRecord(ev_keys_, stream_main_));
+                                    cur.pos_row.as<int32_t>(), d_ingest_err_, ks));
+  HCTR_CUDA(cudaEventRecord(ev_keys_, ks));
+  if (n == 1) HCTR_CUDA(cudaStreamWaitEvent(stream_main_, ev_keys_, 0));
 
   if (!key_stride_known_ && batch_size >= 4096) detectKeyStride(cur);  // once per table
   hctr_dedupe_args a;
@@ -731,9 +735,12 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     HCTR_CUDA(cudaStreamWaitEvent(tail, ev_keys_, 0));
     int sp = tic(kPhExpand, tail);
     HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
-                                 nullptr, d_embedding_.as<float>(), dst_dev, d_err_.as<uint32_t>() + 8, tail));
+                                 nullptr, d_embedding_.as<float>(), dst_dev, d_ingest_err_ + 1, tail));
     toc(sp, tail);
-    flushDedupe(cur);    // behind the step's critical path on stream_main_: only the next step's reduction needs it
+    // The dedupe of this batch goes behind the step's critical path on stream_main_ (low priority): only the next
+    // step's reduction needs it.  (Holding it back until the reduction has ended was measured and is slower: the
+    // dedupe then ends after the expansion and the next reduction waits for it.)
+    flushDedupe(cur);
     flushOrdering(cur);
   } else if (use_p2p_) {
     exchangeP2P(dst_dev);
@@ -913,7 +920,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     sp = tic(kPhExpand);
     HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
                                  d_recv_slot_.as<uint32_t>(), d_rval_r_.as<float>(), d_embedding_.as<float>(), dst_dev,
-                                 d_err_.as<uint32_t>() + 8, stream_main_));
+                                 d_ingest_err_ + 1, stream_main_));
     toc(sp);
     if (*h_err) {
       HCTR_CUDA(cudaStreamSynchronize(stream_main_));
@@ -923,12 +930,11 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
 
   if (dst_staged)
     HCTR_CUDA(cudaMemcpyAsync(dst, dst_dev, cur.batch_size * W * sizeof(embed_t), cudaMemcpyDeviceToHost, tail));
-  uint32_t *h_expand_err = h_pinned_ + h_pinned_words_ - 1;  // bounded waits of the expand kernel
-  HCTR_CUDA(cudaMemcpyAsync(h_expand_err, d_err_.as<uint32_t>() + 8, sizeof(uint32_t), cudaMemcpyDeviceToHost, tail));
+  // the expand kernel reports a bounded wait that ran out through a mapped pinned word: nothing to copy back
   HCTR_CUDA(cudaStreamSynchronize(tail));
   collectSpans();
-  if (h_expand_err[0]) {
-    HCTR_CUDA(cudaMemsetAsync(d_err_.as<uint32_t>() + 8, 0, sizeof(uint32_t), tail));
+  if (h_ingest_err_[1]) {
+    h_ingest_err_[1] = 0;
     throw std::runtime_error("push_pull: the row expansion gave up waiting for a bulk copy");
   }
   if (cur.pending && n > 1) {
@@ -1063,7 +1069,7 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
   toc(sp);
   sp = tic(kPhExpand);
   HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
-                               d_recv_idx_.as<uint32_t>(), mine.rval, d_embedding_.as<float>(), dst_dev, d_err_.as<uint32_t>() + 8, stream_main_));
+                               d_recv_idx_.as<uint32_t>(), mine.rval, d_embedding_.as<float>(), dst_dev, d_ingest_err_ + 1, stream_main_));
   toc(sp);
 
   // counts, wait times and the error word come back with the step's final synchronisation

@@ -406,6 +406,19 @@ __device__ __forceinline__ void cp_async16(void *smem, const void *gmem) {
   const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(sa), "l"(gmem) : "memory");
 }
+// Gradient rows are read exactly once: their copies carry an evict-first L2 policy so that 100+ MB of them per
+// step do not push the table rows and the (L2-resident) dedupe structures of the concurrently running
+// preprocess out of the cache.
+__device__ __forceinline__ u64 l2_evict_first_policy() {
+  u64 p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void cp_async16_once(void *smem, const void *gmem, u64 policy) {
+  const unsigned sa = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(sa), "l"(gmem), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
@@ -453,6 +466,7 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKerne
   __shared__ u32 sort_all[kThreads];  // 32 words per warp
   u32 *sort_buf = sort_all + (threadIdx.x & ~31u);
   const bool unordered = a.short_runs_unordered != 0;
+  const u64 once = l2_evict_first_policy();
   const u32 n_pos = a.run_start[U];
   const u64 total = (u64)n_pos + 2ull * U;
   const u64 per_warp = (total + n_warps - 1) / n_warps;
@@ -523,10 +537,14 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKerne
           src = grad + (size_t)pos * E;
         }
         T *dst = ring + (size_t)slot_p * E;
+        const bool is_grad = P.j >= 0;  // a gradient row (read once), not the key's table row
 #pragma unroll
         for (int i = 0; i < EPL; i++) {
           const size_t c = lane + 32u * i;
-          if (c < E) cp_async16(dst + c, src + c);
+          if (c < E) {
+            if (is_grad) cp_async16_once(dst + c, src + c, once);
+            else cp_async16(dst + c, src + c);
+          }
         }
         if (++P.j == (int)P.len) cursor_next_key(P, l, len, type, row);
       }
@@ -602,16 +620,21 @@ constexpr int kLongPosChunk = 2048;  // positions staged in shared memory at a t
 constexpr u32 kVeryLongRun = 256;     // runs at least this long are started first
 
 template <bool VEC>
-__device__ __forceinline__ void cp_async_elem(void *smem_dst, const void *gsrc) {
+__device__ __forceinline__ void cp_async_elem(void *smem_dst, const void *gsrc, u64 policy) {
   const unsigned s = (unsigned)__cvta_generic_to_shared(smem_dst);
-  if (VEC) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gsrc) : "memory");
-  else asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gsrc) : "memory");
+  if (VEC)
+    asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gsrc), "l"(policy)
+                 : "memory");
+  else
+    asm volatile("cp.async.ca.shared.global.L2::cache_hint [%0], [%1], 4, %2;\n" ::"r"(s), "l"(gsrc), "l"(policy)
+                 : "memory");
 }
 
 template <bool VEC>
 __global__ void __launch_bounds__(kLongThreads) grad_reduce_long(ReduceKernelArgs ka, u32 n_heavy_host, u32 *work_counter) {
   const hctr_reduce_args &a = ka.a;
   const u32 n_heavy = a.meta ? a.meta[HCTR_META_NHEAVY] : n_heavy_host;
+  const u64 once = l2_evict_first_policy();
   typedef RowT<VEC> R;
   typedef typename R::T T;
   extern __shared__ __align__(16) unsigned char smem_raw[];
@@ -665,7 +688,7 @@ __global__ void __launch_bounds__(kLongThreads) grad_reduce_long(ReduceKernelArg
             for (u32 rr = warp * rows_per_warp_iter + sub; rr < nr; rr += kLongWarps * rows_per_warp_iter) {
               const T *src = grad + (size_t)pos_s[r0 + rr] * E;
               T *d = dst + rr * E32;
-              for (u32 cc = sl; cc < E32; cc += lpr) cp_async_elem<VEC>(d + cc, src + cc);
+              for (u32 cc = sl; cc < E32; cc += lpr) cp_async_elem<VEC>(d + cc, src + cc, once);
             }
           }
           asm volatile("cp.async.commit_group;\n" ::: "memory");  // one group per tile slot, even if empty
