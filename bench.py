@@ -134,13 +134,30 @@ def make_workload(cfg, nrank, rank, rows=0, width=0):
 
 
 def algorithmic_bytes(c, st):
-    """Algorithmic HBM bytes per launch of the two row-moving kernels (D = 4*width bytes per row):
+    """Algorithmic HBM bytes per step of each phase (D = 4*width bytes per row):
+       dedupe            : 8B (keys) + B (owner lookups) + 4B (batch->unique map) + 17 per unique key
        reduce+apply+pack : B*D (gradients) + 2*D per locally stored unique row + (D+16) per pushed row
+       owner update      : G*(D+16) (message) + G*2D (row read+write) + G*16 (version read+write)
+       stale check+gather: Q*24 + R_s*(2D+8)
        expand            : D per unique row + B*D (dst) + 4*B (batch->unique map)"""
     D = 4 * c["width"]
     B, U = st["batch"], st["unique"]
     Bp, Up, P = st["prev_batch"], st["prev_unique"], st["pushed_rows"]
-    return {"reduce": Bp * D + Up * 2 * D + P * (D + 16), "expand": U * D + B * D + 4 * B}
+    G, Q, Rs = st["received_push_rows"], st["queried_keys"], st["returned_rows"]
+    stored = max(Up - P, 0) + min(P, Up)  # every unique row is either applied locally, pushed, or both (cached)
+    return {"dedupe": 13 * B + 17 * U, "reduce": Bp * D + stored * 2 * D + P * (D + 16),
+            "owner_update": G * (3 * D + 32), "stale_gather": Q * 24 + Rs * (2 * D + 8),
+            "expand": U * D + B * D + 4 * B}
+
+
+def nvlink_bytes(c, st, world):
+    """Algorithmic bytes ONE GPU stores into its peers' memory per step: queries (key + version, 16 B) for the keys
+    other ranks own, pushed rows (row + key + count), one flag byte per remote query answered, returned rows
+    (row + version).  Keys addressed to the rank itself stay local: with random owners that is 1/world of them."""
+    D = 4 * c["width"]
+    remote = (world - 1) / world
+    return {"queries": 16 * st["unique"] * remote, "pushed_rows": st["pushed_rows"] * (D + 16),
+            "flags": st["queried_keys"] * remote, "returned_rows": st["returned_rows"] * (D + 8)}
 
 
 def run_ours(args):
@@ -193,9 +210,23 @@ def run_ours(args):
     table.push_pull(None, dst)
     clocks = ClockSampler(local)
     if rank == 0:
-        clocks.start()  # sampling covers warm-up + timed region, both under the same load
+        # sampling covers warm-up, timed region and the end-to-end region, all under the same load; a short run
+        # (the timed region of 20 steps lasts milliseconds) keeps stepping until the sampler has delivered
+        clocks.start()
     for i in range(args.warmup):
         step(i)
+    # every rank takes the same number of steps (a step is collective): rank 0 decides, the others follow
+    t_wait, i = time.perf_counter(), 0
+    while True:
+        more = torch.tensor([1 if rank == 0 and len(clocks.lines) < 3 and time.perf_counter() - t_wait < 3.0 else 0],
+                            device=dev)
+        if world > 1:
+            dist.broadcast(more, 0)
+        if int(more.item()) == 0:
+            break
+        for _ in range(50):
+            step(i)
+            i += 1
 
     # phase timers on every 8th step: their events cost a timed step ~15 us, sampling keeps `value` honest
     PROFILE_EVERY = 8
@@ -213,7 +244,6 @@ def run_ours(args):
     wall = time.perf_counter() - t0
     ms = e0.elapsed_time(e1)
     launches = hb.lib().hctr_launch_count() - launches0
-    clk = clocks.stop() if rank == 0 else None
     phases = table.phase_times(reset=True)
     table.profile(False)
     stats = table.stats()
@@ -233,6 +263,7 @@ def run_ours(args):
     f1.record(stream)
     barrier()
     e2e_ms = f0.elapsed_time(f1)
+    clk = clocks.stop() if rank == 0 else None
 
     if args.timeline:
         table.profile(1)
@@ -264,15 +295,46 @@ def run_ours(args):
         alg = algorithmic_bytes(c, stats)
         per_phase = {p: (v[0] / v[1] if v[1] else 0.0) for p, v in phases.items()}
         timed_steps = (args.steps + PROFILE_EVERY - 1) // PROFILE_EVERY
-        dom = max(("reduce", "expand"), key=lambda p: per_phase[p])
+        # the row-moving kernels; the dominant one (longest launch) is the line's `roofline`, all of them (and the
+        # latency-bound dedupe pipeline, whose working set lives in L2) are listed under `roofline_phases`
+        kernels = {"reduce": "grad_reduce_apply_pack", "expand": "expand_rows", "owner_update": "owner_mark + owner_apply",
+                   "stale_gather": "p2p_stale_scan + p2p_gather", "dedupe": "dedupe pipeline (5 launches)"}
+        # the owner's row pass runs on a second stream next to the staleness scan: charge it to owner_update
+        per_phase["owner_update"] = per_phase.get("owner_update", 0.0) + per_phase.get("owner_apply", 0.0)
+        movers = [p for p in ("reduce", "expand", "owner_update", "stale_gather") if per_phase.get(p, 0.0) > 0]
+        dom = max(movers, key=lambda p: per_phase[p])
         achieved = alg[dom] / (per_phase[dom] * 1e-3) / 1e9 if per_phase[dom] > 0 else 0.0
-        traffic = None
+        roofline_phases = {p: {"kernel": kernels[p], "avg_launch_ms": per_phase[p], "algorithmic_bytes": alg[p],
+                               "achieved_gbs": alg[p] / (per_phase[p] * 1e-3) / 1e9,
+                               "frac": alg[p] / (per_phase[p] * 1e-3) / 1e9 / peak}
+                           for p in movers + ["dedupe"] if per_phase.get(p, 0.0) > 0}
+        traffic, traffic_note = None, None
         tfile = os.path.join(ROOT, "profiles", "traffic.json")
         if os.path.exists(tfile):
             tj = json.load(open(tfile))
             key = f"{args.config}:n{world}:{dom}"
             if key in tj:
                 traffic = tj[key]["bytes_per_launch"]
+                traffic_note = tj[key].get("source")
+        nvlink = None
+        if world > 1:
+            nb = nvlink_bytes(c, stats, world)
+            sent = sum(nb.values())
+            store_ms = per_phase["reduce"] + per_phase.get("query", 0.0) + per_phase.get("stale_gather", 0.0)
+            gather_ms = per_phase.get("stale_gather", 0.0)
+            nvlink = {"bytes_sent_per_gpu_per_step": sent, "parts": nb, "peak": 900.0, "unit": "GB/s per direction",
+                      "step_gbs": sent / (ms / args.steps * 1e-3) / 1e9,
+                      "step_frac": sent / (ms / args.steps * 1e-3) / 1e9 / 900.0,
+                      "store_kernels_ms": store_ms,
+                      "store_kernels_gbs": sent / (store_ms * 1e-3) / 1e9 if store_ms > 0 else 0.0,
+                      "store_kernels_frac": sent / (store_ms * 1e-3) / 1e9 / 900.0 if store_ms > 0 else 0.0,
+                      "gather_gbs": nb["returned_rows"] / (gather_ms * 1e-3) / 1e9 if gather_ms > 0 else 0.0,
+                      "gather_frac": nb["returned_rows"] / (gather_ms * 1e-3) / 1e9 / 900.0 if gather_ms > 0 else 0.0,
+                      "how": "algorithmic bytes this GPU stores into peer memory per step (counts of the last step) "
+                             "over (a) the step, (b) the CUDA-event time of the kernels that issue the stores "
+                             "(reduce: pushed rows; query: keys+versions; stale_gather: flags + returned rows), "
+                             "(c) returned rows over the staleness scan + gather alone",
+                      "wait_for_peers_us": {"queries": stats["wait_queries_us"], "returned_rows": stats["wait_returns_us"]}}
         out = {
             "metric": METRIC, "value": world * B * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True,
@@ -292,15 +354,18 @@ def run_ours(args):
                     "h2d_bytes_per_step": B * 8 + B * W * 4, "d2h_bytes_per_step": B * W * 4,
                     "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps},
             "gpu_launches": int(launches),
-            "roofline": {"bound": "hbm", "kernel": {"reduce": "grad_reduce_apply_pack", "expand": "expand_rows"}[dom],
+            "roofline": {"bound": "hbm", "kernel": kernels[dom],
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "algorithmic_bytes_per_launch": alg[dom],
-                         "avg_launch_ms": per_phase[dom], "traffic": traffic},
+                         "avg_launch_ms": per_phase[dom], "traffic": traffic, "traffic_source": traffic_note},
+            "roofline_phases": roofline_phases,
             "phase_ms_per_step": {p: phases[p][0] / timed_steps for p in phases},
             "phase_timers": f"CUDA events on every {PROFILE_EVERY}th step of the timed region ({timed_steps} steps)",
             "wall_ms_per_step": wall * 1e3 / args.steps,
             "clocks": clk,
         }
+        if nvlink:
+            out["nvlink"] = nvlink
         # the CPU baseline is a single-GPU-run item (a multi-rank launcher also pins OpenMP to one thread)
         if not args.no_cpu_baseline and world == 1:
             out["cpu_baseline"] = cpu_baseline(args, world)
