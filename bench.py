@@ -301,6 +301,8 @@ def run_ours(args):
                    "stale_gather": "p2p_stale_scan + p2p_gather", "dedupe": "dedupe pipeline (5 launches)"}
         # the owner's row pass runs on a second stream next to the staleness scan: charge it to owner_update
         per_phase["owner_update"] = per_phase.get("owner_update", 0.0) + per_phase.get("owner_apply", 0.0)
+        gather_only_ms = per_phase.get("stale_gather", 0.0)  # the peer-to-peer exchange times scan and gather apart
+        per_phase["stale_gather"] = gather_only_ms + per_phase.get("stale_scan", 0.0)
         movers = [p for p in ("reduce", "expand", "owner_update", "stale_gather") if per_phase.get(p, 0.0) > 0]
         dom = max(movers, key=lambda p: per_phase[p])
         achieved = alg[dom] / (per_phase[dom] * 1e-3) / 1e9 if per_phase[dom] > 0 else 0.0
@@ -321,7 +323,7 @@ def run_ours(args):
             nb = nvlink_bytes(c, stats, world)
             sent = sum(nb.values())
             store_ms = per_phase["reduce"] + per_phase.get("query", 0.0) + per_phase.get("stale_gather", 0.0)
-            gather_ms = per_phase.get("stale_gather", 0.0)
+            gather_ms = gather_only_ms if per_phase.get("stale_scan", 0.0) > 0 else per_phase.get("stale_gather", 0.0)
             nvlink = {"bytes_sent_per_gpu_per_step": sent, "parts": nb, "peak": 900.0, "unit": "GB/s per direction",
                       "step_gbs": sent / (ms / args.steps * 1e-3) / 1e9,
                       "step_frac": sent / (ms / args.steps * 1e-3) / 1e9 / 900.0,
@@ -333,7 +335,7 @@ def run_ours(args):
                       "how": "algorithmic bytes this GPU stores into peer memory per step (counts of the last step) "
                              "over (a) the step, (b) the CUDA-event time of the kernels that issue the stores "
                              "(reduce: pushed rows; query: keys+versions; stale_gather: flags + returned rows), "
-                             "(c) returned rows over the staleness scan + gather alone",
+                             "(c) returned rows over the gather kernel alone",
                       "wait_for_peers_us": {"queries": stats["wait_queries_us"], "returned_rows": stats["wait_returns_us"]}}
         out = {
             "metric": METRIC, "value": world * B * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world,

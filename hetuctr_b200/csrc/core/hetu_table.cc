@@ -247,6 +247,8 @@ void HetuTable::initTable(const worker_t *root, const index_t *storage) {
     // owner-side apply: one source-mask word per owned row, and the per-source list descriptors
     d_row_mask_.ensure(std::max<size_t>(S - kNonLocalStorageMax, 1) * sizeof(unsigned long long));
     HCTR_CUDA(cudaMemsetAsync(d_row_mask_.p, 0, d_row_mask_.bytes, stream_main_));
+    d_row_head_.ensure(std::max<size_t>(S - kNonLocalStorageMax, 1) * sizeof(unsigned long long));
+    HCTR_CUDA(cudaMemsetAsync(d_row_head_.p, 0, d_row_head_.bytes, stream_main_));
     d_src_off_.ensure((size_t)nrank_ * sizeof(unsigned long long));
     d_src_cnt_.ensure(((size_t)nrank_ + 1) * sizeof(uint32_t));
   }
@@ -800,12 +802,14 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
         HCTR_CUDA(cudaMemcpyAsync(d_src_off_.p, h_off, n * sizeof(unsigned long long), cudaMemcpyHostToDevice, stream_main_));
         HCTR_CUDA(cudaMemcpyAsync(d_src_cnt_.p, h_start, (n + 1) * sizeof(uint32_t), cudaMemcpyHostToDevice, stream_main_));
         d_ent_row_.ensure((push_recv + 1) * sizeof(int32_t));
+        d_ent_next_.ensure((push_recv + 1) * sizeof(uint32_t));
         HCTR_LAUNCH(hctr_owner_update_merged(n, push_recv, W, d_pkey_r_.as<int64_t>(),
                                              d_pupd_r_.as<int64_t>(), d_pval_r_.as<float>(),
                                              d_src_off_.as<unsigned long long>(), d_src_cnt_.as<uint32_t>(),
                                              d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
-                                             d_row_mask_.as<unsigned long long>(), nextEpoch(),
-                                             d_ent_row_.as<int32_t>(), d_embedding_.as<float>(),
+                                             d_row_mask_.as<unsigned long long>(),
+                                             d_row_head_.as<unsigned long long>(), nextEpoch(),
+                                             d_ent_row_.as<int32_t>(), d_ent_next_.as<uint32_t>(), d_embedding_.as<float>(),
                                              d_version_.as<int64_t>(), d_err_.as<uint32_t>(), stream_main_));
       } else {
         size_t off = 0;
@@ -993,6 +997,8 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
   d_ret_q_.ensure((slots + 1) * sizeof(uint32_t));
   d_ret_row_.ensure((slots + 1) * sizeof(int32_t));
   d_ent_row_.ensure((slots + 1) * sizeof(int32_t));
+  d_ent_next_.ensure((slots + 1) * sizeof(uint32_t));
+  d_recv_list_.ensure((u_max + 1) * sizeof(uint32_t));
   d_flag_r_.ensure(u_max + 16);
   {
     const size_t before = d_chain2_.bytes;
@@ -1026,14 +1032,16 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
     // pass A waits for the peers' counts, then marks sources and finishes the versions; pass B (the rows) goes to a
     // second stream and overlaps the staleness scan, which only reads versions
     HCTR_LAUNCH(hctr_p2p_owner_mark(c, &mine, seq, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
-                                    d_row_mask_.as<unsigned long long>(), nextEpoch(), d_ent_row_.as<int32_t>(),
+                                    d_row_mask_.as<unsigned long long>(), d_row_head_.as<unsigned long long>(),
+                                    nextEpoch(), d_ent_row_.as<int32_t>(), d_ent_next_.as<uint32_t>(),
                                     d_version_.as<int64_t>(), stream_main_));
     toc(sp);
     HCTR_CUDA(cudaEventRecord(ev_afork_, stream_main_));
     HCTR_CUDA(cudaStreamWaitEvent(stream_apply_, ev_afork_, 0));
     sp = tic(kPhOwnerApply, stream_apply_);
     HCTR_LAUNCH(hctr_p2p_owner_apply(c, &mine, kNonLocalStorageMax, d_ent_row_.as<int32_t>(),
-                                     d_row_mask_.as<unsigned long long>(), d_embedding_.as<float>(), stream_apply_));
+                                     d_row_mask_.as<unsigned long long>(), d_row_head_.as<unsigned long long>(),
+                                     d_ent_next_.as<uint32_t>(), d_embedding_.as<float>(), stream_apply_));
     toc(sp, stream_apply_);
     HCTR_CUDA(cudaEventRecord(ev_ajoin_, stream_apply_));
     rows_forked = true;
@@ -1048,24 +1056,30 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
   // D. staleness, per-requester counts, rows gathered into the requesters' mailboxes
   // flat index space: Q = all received queries (device value), at most `slots`; flags, slots and the list of
   // returned queries come out of one launch
-  sp = tic(kPhStaleGather);
+  sp = tic(kPhStaleScan);
   HCTR_LAUNCH(hctr_p2p_stale_scan(c, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
                                   d_version_.as<int64_t>(), pull_bound_, d_ret_slot_.as<uint32_t>(),
                                   d_ret_q_.as<uint32_t>(), d_ret_row_.as<int32_t>(), d_chain2_.as<uint32_t>(),
                                   nextEpoch(), stream_main_));
+  toc(sp);
   if (rows_forked) HCTR_CUDA(cudaStreamWaitEvent(stream_main_, ev_ajoin_, 0));  // the gather reads updated rows
+  sp = tic(kPhStaleGather);
   HCTR_LAUNCH(hctr_p2p_gather(c, seq, d_ret_q_.as<uint32_t>(), d_ret_row_.as<int32_t>(), d_ret_slot_.as<uint32_t>(),
                               d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
   toc(sp);
   meet();
 
   // E. requester: wait for the owners, flags -> row indices in its own mailbox, cache refresh, expand
-  sp = tic(kPhRefresh);
+  sp = tic(kPhRecvScan);
   HCTR_LAUNCH(hctr_p2p_recv_scan(c, seq, meta, u_max, cur.uniq_owner.as<uint8_t>(), d_flag_r_.as<uint8_t>(),
-                                 d_recv_idx_.as<uint32_t>(), d_chain2_.as<uint32_t>(), nextEpoch(), stream_main_));
-  HCTR_LAUNCH(hctr_cache_refresh(u_max, W, d_flag_r_.as<uint8_t>(), d_recv_idx_.as<uint32_t>(),
-                                 cur.uniq_row.as<int32_t>(), mine.rval, mine.rver, d_gradient_.as<float>(),
-                                 d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
+                                 d_recv_idx_.as<uint32_t>(), d_recv_list_.as<uint32_t>(), d_chain2_.as<uint32_t>(),
+                                 nextEpoch(), stream_main_));
+  toc(sp);
+  sp = tic(kPhRefresh);
+  HCTR_LAUNCH(hctr_cache_refresh_listed(c->cnt_in + 2 * n, n, u_max, W, d_recv_list_.as<uint32_t>(),
+                                        d_recv_idx_.as<uint32_t>(), cur.uniq_row.as<int32_t>(), mine.rval, mine.rver,
+                                        d_gradient_.as<float>(), d_embedding_.as<float>(), d_version_.as<int64_t>(),
+                                        stream_main_));
   toc(sp);
   sp = tic(kPhExpand);
   HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
@@ -1275,7 +1289,7 @@ void HetuTable::releaseAll() {
   p2p_.reset();
   transport_.reset();
   DevBuf *all[] = {&d_embedding_, &d_gradient_, &d_updates_, &d_version_, &d_root_, &d_row_of_, &d_stored_keys_,
-                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_chain_, &d_chain2_, &d_chain3_, &d_ret_q_, &d_ret_row_, &d_ent_row_, &d_row_mask_, &d_src_off_, &d_src_cnt_, &d_word_base_, &d_scan_, &d_sk_, &d_cnt_,
+                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_chain_, &d_chain2_, &d_chain3_, &d_ret_q_, &d_ret_row_, &d_ent_row_, &d_ent_next_, &d_recv_list_, &d_row_mask_, &d_row_head_, &d_src_off_, &d_src_cnt_, &d_word_base_, &d_scan_, &d_sk_, &d_cnt_,
                    &d_push_count_, &d_push_base_, &d_recv_idx_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
                    &d_qkey_r_, &d_qver_r_, &d_pkey_s_, &d_pupd_s_, &d_pval_s_, &d_pkey_r_, &d_pupd_r_, &d_pval_r_,
                    &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,

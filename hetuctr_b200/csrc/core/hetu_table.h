@@ -105,6 +105,8 @@ enum Phase {
   kPhRefresh,         // hctr_recv_slots + hctr_cache_refresh
   kPhExpand,          // hctr_expand_rows
   kPhOwnerApply,      // peer-to-peer: row pass of the owner update (second stream, overlaps the staleness scan)
+  kPhStaleScan,       // peer-to-peer: hctr_p2p_stale_scan alone (kPhStaleGather is then the gather alone)
+  kPhRecvScan,        // peer-to-peer: wait for the owners + hctr_p2p_recv_scan (kPhRefresh is then the refresh alone)
   kPhCount
 };
 
@@ -226,7 +228,7 @@ class HetuTable {
   size_t length_pad_ = 0;
 
   // dedupe scratch (persistent, all-zero between calls) and per-step scratch
-  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_ret_row_, d_ent_row_, d_row_mask_, d_src_off_, d_src_cnt_, d_word_base_, d_scan_, d_sk_, d_cnt_;
+  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_ret_row_, d_ent_row_, d_ent_next_, d_recv_list_, d_row_mask_, d_row_head_, d_src_off_, d_src_cnt_, d_word_base_, d_scan_, d_sk_, d_cnt_;
   DevBuf d_push_count_, d_push_base_, d_recv_idx_, d_err_;
   size_t shared_capacity_ = 0;
   uint32_t dedupe_epoch_ = 0;

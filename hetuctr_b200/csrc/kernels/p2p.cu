@@ -71,14 +71,15 @@ __global__ void __launch_bounds__(kMaxRanks) p2p_wait(hctr_p2p_ctx c, int phase,
   else wait_returns(c, seq, a, true);
 }
 
-// One group of LANES lanes per returned row, rows written straight into the requester's mailbox.  A group takes
-// kGatherRows rows per iteration and issues the loads of all of them stage by stage (list entries, then the rows),
-// so that the chains of dependent accesses of several rows overlap.  ret_q[r] is the flat query index of returned
-// row r and ret_row[r] its local row (both written by p2p_stale_scan).  The thread block that finishes last
-// publishes the per-requester row counts and releases `seq` (phase 1) to every peer.
-constexpr int kGatherRows = 4;
+// Returned rows go straight into the requesters' mailboxes.  A warp takes 32 consecutive returned rows: lane i
+// fetches the list entries of row i (ret_q[r] = flat query index of returned row r, ret_row[r] = its local row,
+// both written by p2p_stale_scan; coalesced, one load per 32 rows) and works out where the row goes; then all
+// lanes move the elements of the 32 rows as one flat range, several independent loads in flight per lane.  The
+// thread block that finishes last publishes the per-requester row counts and releases `seq` (phase 1) to every
+// peer.
+constexpr int kGatherUnroll = 4;
 
-template <int LANES, bool VEC>
+template <bool VEC>
 __global__ void __launch_bounds__(kThreads) p2p_gather(hctr_p2p_ctx c, u32 seq, const u32 *__restrict__ ret_q,
                                                        const int32_t *__restrict__ ret_row,
                                                        const u32 *__restrict__ ret_slot,
@@ -91,39 +92,44 @@ __global__ void __launch_bounds__(kThreads) p2p_gather(hctr_p2p_ctx c, u32 seq, 
   __syncthreads();
   const u32 Q = qstart[c.nrank];
   const u32 n_ret = ret_slot[Q];
-  const unsigned gl = threadIdx.x % LANES;
-  const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
-  const size_t E = R::elems(c.width);
-  for (size_t r0 = (((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES) * kGatherRows; r0 < n_ret;
-       r0 += groups * kGatherRows) {
-    u32 qq[kGatherRows];
-    unsigned src[kGatherRows];
-    int32_t row[kGatherRows];
-    size_t dst[kGatherRows];
-#pragma unroll
-    for (int k = 0; k < kGatherRows; k++) {
-      const bool in = r0 + k < n_ret;
-      qq[k] = in ? ret_q[r0 + k] : 0u;
-      row[k] = in ? ret_row[r0 + k] : -1;
+  const unsigned lane = threadIdx.x & 31;
+  const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
+  const size_t n_warps = ((size_t)gridDim.x * kThreads) >> 5;
+  const u32 E = (u32)R::elems(c.width);
+  for (size_t r0 = warp * 32; r0 < n_ret; r0 += n_warps * 32) {
+    const u32 cnt = (u32)min((size_t)32, (size_t)n_ret - r0);
+    const T *src_row = nullptr;
+    T *dst_row = nullptr;
+    if (lane < cnt) {
+      const u32 qq = ret_q[r0 + lane];
+      const int32_t row = ret_row[r0 + lane];
+      const unsigned s = segment_of(qstart, c.nrank, qq);
+      const size_t dst = (size_t)c.rank * c.cap + ((u32)(r0 + lane) - ret_slot[qstart[s]]);
+      const hctr_p2p_box b = c.box[s];
+      b.rver[dst] = version[row];
+      src_row = reinterpret_cast<const T *>(embedding) + (size_t)row * E;
+      dst_row = reinterpret_cast<T *>(b.rval) + dst * E;
     }
+    const u32 total = cnt * E;  // elements of the block's rows, as one flat range
+    for (u32 t0 = 0; t0 < total; t0 += 32 * kGatherUnroll) {
+      T v[kGatherUnroll];
+      T *d[kGatherUnroll];
+      u32 ee[kGatherUnroll];
 #pragma unroll
-    for (int k = 0; k < kGatherRows; k++) {
-      src[k] = segment_of(qstart, c.nrank, qq[k]);
-      dst[k] = (size_t)c.rank * c.cap + ((u32)(r0 + k) - ret_slot[qstart[src[k]]]);
-    }
-    if (gl == 0) {
+      for (int k = 0; k < kGatherUnroll; k++) {
+        const u32 t = t0 + 32u * k + lane;
+        const u32 j = t / E, e = t - j * E;
+        ee[k] = e;
+        const bool act = t < total;
+        // (shuffles are executed by all lanes; rows beyond the block read lane 0's pointers and are not used)
+        const T *sp = reinterpret_cast<const T *>(__shfl_sync(0xffffffffu, (unsigned long long)src_row, act ? j : 0));
+        d[k] = reinterpret_cast<T *>(__shfl_sync(0xffffffffu, (unsigned long long)dst_row, act ? j : 0));
+        if (act) v[k] = sp[e];
+        else d[k] = nullptr;
+      }
 #pragma unroll
-      for (int k = 0; k < kGatherRows; k++)
-        if (row[k] >= 0) c.box[src[k]].rver[dst[k]] = version[row[k]];
-    }
-    for (size_t e = gl; e < E; e += LANES) {
-      T v[kGatherRows];
-#pragma unroll
-      for (int k = 0; k < kGatherRows; k++)
-        if (row[k] >= 0) v[k] = reinterpret_cast<const T *>(embedding)[(size_t)row[k] * E + e];
-#pragma unroll
-      for (int k = 0; k < kGatherRows; k++)
-        if (row[k] >= 0) reinterpret_cast<T *>(c.box[src[k]].rval)[dst[k] * E + e] = v[k];
+      for (int k = 0; k < kGatherUnroll; k++)
+        if (d[k]) d[k][ee[k]] = v[k];
     }
   }
   if (!last_block_of_launch(c.cnt_in + HCTR_P2P_TICKET1(c.nrank))) return;
@@ -246,7 +252,8 @@ __global__ void __launch_bounds__(kTileThreads) p2p_stale_scan(hctr_p2p_ctx c, c
 __global__ void __launch_bounds__(kTileThreads) p2p_recv_scan(hctr_p2p_ctx c, u32 seq, const u32 *__restrict__ meta,
                                                               size_t u_max, const uint8_t *__restrict__ uniq_owner,
                                                               uint8_t *__restrict__ flags,
-                                                              u32 *__restrict__ recv_index, u64 *agg, u32 epoch) {
+                                                              u32 *__restrict__ recv_index,
+                                                              u32 *__restrict__ recv_list, u64 *agg, u32 epoch) {
   __shared__ u32 owner_base[kMaxRanks + 1];
   const size_t U = meta[HCTR_META_UNIQUE];
   const u32 *seg = meta + HCTR_META_SEG;
@@ -284,6 +291,7 @@ __global__ void __launch_bounds__(kTileThreads) p2p_recv_scan(hctr_p2p_ctx c, u3
   for (int k = 0; k < kTileItems; k++) {
     const size_t u = base + k;
     if (u < u_max) recv_index[u] = u < U ? owner[k] * (u32)c.cap + (ex - owner_base[owner[k]]) : 0u;
+    if (v[k]) recv_list[ex] = (u32)u;  // the ex-th key (in unique order) a row came back for
     ex += v[k];
   }
 }
@@ -345,24 +353,24 @@ extern "C" int hctr_p2p_gather(const hctr_p2p_ctx *c, uint32_t seq, const uint32
                                void *stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (c->nrank > kMaxRanks) return (int)cudaErrorInvalidValue;
-  const bool al = host_aligned16(embedding);
-  const size_t width = c->width;
-#define CALL(L, V)                                                                                               \
-  p2p_gather<L, V><<<(unsigned)((size_t)kSMs * 8), kThreads, 0, st>>>(*c, seq, ret_q, ret_row, ret_slot, embedding, \
-                                                                      (const long long *)version)
-  HCTR_DISPATCH_ROWS(width, al, CALL);
-#undef CALL
+  // one warp per 32 returned rows; at most nrank * cap rows exist, a few resident rounds of blocks cover them
+  size_t g = ((size_t)c->nrank * c->cap / 32 + 1 + kThreads / 32 - 1) / (kThreads / 32);
+  if (g > (size_t)kSMs * 4) g = (size_t)kSMs * 4;
+  if (g == 0) g = 1;
+  const bool vec = host_aligned16(embedding) && c->width % 4 == 0;
+  if (vec) p2p_gather<true><<<(unsigned)g, kThreads, 0, st>>>(*c, seq, ret_q, ret_row, ret_slot, embedding, (const long long *)version);
+  else p2p_gather<false><<<(unsigned)g, kThreads, 0, st>>>(*c, seq, ret_q, ret_row, ret_slot, embedding, (const long long *)version);
   count_launches(1);
   return launch_status();
 }
 
 extern "C" int hctr_p2p_recv_scan(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *meta, size_t u_max,
-                                  const uint8_t *uniq_owner, uint8_t *flags, uint32_t *recv_index, uint32_t *scratch,
-                                  uint32_t epoch, void *stream) {
+                                  const uint8_t *uniq_owner, uint8_t *flags, uint32_t *recv_index,
+                                  uint32_t *recv_list, uint32_t *scratch, uint32_t epoch, void *stream) {
   if (c->nrank > kMaxRanks || epoch == 0) return (int)cudaErrorInvalidValue;
   const unsigned grid = (unsigned)((u_max + kTile - 1) / kTile);
   p2p_recv_scan<<<grid ? grid : 1, kTileThreads, 0, (cudaStream_t)stream>>>(*c, seq, meta, u_max, uniq_owner, flags,
-                                                                            recv_index,
+                                                                            recv_index, recv_list,
                                                                             reinterpret_cast<u64 *>(scratch), epoch);
   count_launches(1);
   return launch_status();

@@ -785,7 +785,12 @@ struct PushLists {  // where every source's pushed rows are, as seen by the owne
   size_t src_stride;
   const u32 *flat_start;              // device [nsrc+1]: exclusive prefix of the per-source row counts
   int nsrc;
+  // chain of the entries that push the same row, built by pass A and walked by pass B: head[row] =
+  // [epoch:32 | flat entry:32] of the entry marked last, next[f] = the entry marked before f (kNoEntry: none)
+  u64 *head;
+  u32 *next;
 };
+constexpr u32 kNoEntry = 0xffffffffu;
 
 __device__ __forceinline__ size_t push_list_base(const PushLists &p, int s) {
   return p.src_off ? (size_t)p.src_off[s] : (size_t)s * p.src_stride;
@@ -826,6 +831,8 @@ __global__ void __launch_bounds__(kThreads) owner_mark_sources(PushLists p, hctr
       continue;
     }
     atomicAdd(reinterpret_cast<u64 *>(version) + row, (u64)p.upd[ent]);
+    const u64 before = atomicExch(&p.head[(size_t)row - n_cached], ((u64)epoch << 32) | (u32)f);
+    p.next[f] = (u32)(before >> 32) == epoch ? (u32)before : kNoEntry;
     u64 *w = &mask[(size_t)row - n_cached];
     u64 old = *w;
     for (;;) {  // terminates: at most nsrc writers per word, each CAS failure means another one got through
@@ -880,6 +887,53 @@ __global__ void __launch_bounds__(kThreads) owner_apply_sources(PushLists p, siz
       for (size_t e = gl; e < E; e += LANES) emb[e] = R::add(emb[e], R::ld_once(val + ent * E + e));
       continue;
     }
+    const int others = __popc(rest);
+    if (others < LANES) {
+      // Walk the row's chain (all of its entries, this one included, in the order pass A happened to mark them):
+      // lane i keeps the i-th entry, then the lanes rank their entries by flat index - which ascends with the
+      // source - and the group adds the rows in that order.  One dependent load per pusher, nothing to search.
+      const int total_e = others + 1;
+      u32 cur = (u32)p.head[(size_t)row - n_cached], mine_f = kNoEntry;
+      for (int i = 0; i < total_e && cur != kNoEntry; i++) {
+        if (i == (int)gl) mine_f = cur;
+        cur = p.next[cur];
+      }
+      int place = 0;
+      for (int i = 0; i < total_e; i++) place += __shfl_sync(gmask, mine_f, i, LANES) < mine_f ? 1 : 0;
+      size_t mine_ent = 0;
+      if ((int)gl < total_e && mine_f != kNoEntry) {
+        const int s2 = (int)segment_of(start, p.nsrc, mine_f);
+        mine_ent = push_list_base(p, s2) + (mine_f - start[s2]);
+      }
+      // lane q of the group ends up with the entry of place q
+      size_t ordered = 0;
+      for (int i = 0; i < total_e; i++) {
+        const int pl = __shfl_sync(gmask, place, i, LANES);
+        const size_t en = __shfl_sync(gmask, mine_ent, i, LANES);
+        if (pl == (int)gl) ordered = en;
+      }
+      for (size_t e0 = 0; e0 < E; e0 += LANES) {  // same trip count in every lane: the loop body shuffles
+        const size_t e = e0 + gl;
+        const bool act = e < E;
+        T acc = R::zero();
+        if (act) acc = emb[e];
+        for (int j0 = 0; j0 < total_e; j0 += 4) {  // ascending source order, as source-by-source launches would
+          T v[4];
+#pragma unroll
+          for (int j = 0; j < 4; j++) {
+            const size_t ej = __shfl_sync(gmask, ordered, (j0 + j) % LANES, LANES);
+            if (act && j0 + j < total_e) v[j] = R::ld_once(val + ej * E + e);
+          }
+#pragma unroll
+          for (int j = 0; j < 4; j++)
+            if (act && j0 + j < total_e) acc = R::add(acc, v[j]);
+        }
+        if (act) emb[e] = acc;
+      }
+      continue;
+    }
+    // more pushers than the group has lanes (narrow rows, many ranks): find the other sources' entries by binary
+    // search in their key-sorted lists, LANES of them per round
     const long long key = p.key[ent];
     bool first = true;
     while (rest) {
@@ -983,8 +1037,9 @@ static unsigned mark_grid(size_t rows_hint) {
 extern "C" int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width, const int64_t *key,
                                         const int64_t *updates, const float *val, const unsigned long long *src_off,
                                         const uint32_t *flat_start, const int32_t *row_of, size_t length,
-                                        size_t n_cached, unsigned long long *row_mask, uint32_t epoch,
-                                        int32_t *ent_row, float *embedding, int64_t *version, uint32_t *err,
+                                        size_t n_cached, unsigned long long *row_mask,
+                                        unsigned long long *row_head, uint32_t epoch, int32_t *ent_row,
+                                        uint32_t *ent_next, float *embedding, int64_t *version, uint32_t *err,
                                         void *stream) {
   cudaStream_t st = (cudaStream_t)stream;
   if (nsrc > 32 || epoch == 0) return (int)cudaErrorInvalidValue;
@@ -997,6 +1052,8 @@ extern "C" int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width
   p.src_stride = 0;
   p.flat_start = flat_start;
   p.nsrc = nsrc;
+  p.head = row_head;
+  p.next = ent_next;
   hctr_p2p_ctx none;
   memset(&none, 0, sizeof(none));
   owner_mark_sources<false><<<mark_grid(rows_hint), kThreads, 0, st>>>(p, none, 0u, row_of, length, n_cached, row_mask,
@@ -1005,7 +1062,8 @@ extern "C" int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width
   return launch_owner_apply(p, rows_hint, width, n_cached, ent_row, row_mask, embedding, st);
 }
 
-static PushLists mailbox_lists(const hctr_p2p_ctx *c, const hctr_p2p_box *mine) {
+static PushLists mailbox_lists(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, unsigned long long *row_head,
+                               uint32_t *ent_next) {
   PushLists p;
   p.key = (const long long *)mine->pkey;
   p.upd = (const long long *)mine->pupd;
@@ -1014,15 +1072,17 @@ static PushLists mailbox_lists(const hctr_p2p_ctx *c, const hctr_p2p_box *mine) 
   p.src_stride = c->cap;
   p.flat_start = c->cnt_in + 4 * c->nrank + 1;
   p.nsrc = c->nrank;
+  p.head = row_head;
+  p.next = ent_next;
   return p;
 }
 
 extern "C" int hctr_p2p_owner_mark(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, uint32_t seq,
                                    const int32_t *row_of, size_t length, size_t n_cached,
-                                   unsigned long long *row_mask, uint32_t epoch, int32_t *ent_row, int64_t *version,
-                                   void *stream) {
+                                   unsigned long long *row_mask, unsigned long long *row_head, uint32_t epoch,
+                                   int32_t *ent_row, uint32_t *ent_next, int64_t *version, void *stream) {
   if (c->nrank > 32 || epoch == 0) return (int)cudaErrorInvalidValue;
-  const PushLists p = mailbox_lists(c, mine);
+  const PushLists p = mailbox_lists(c, mine, row_head, ent_next);
   owner_mark_sources<true><<<mark_grid(c->cap), kThreads, 0, (cudaStream_t)stream>>>(
       p, *c, seq, row_of, length, n_cached, row_mask, epoch, ent_row, (long long *)version, c->err);
   count_launches(1);
@@ -1030,11 +1090,12 @@ extern "C" int hctr_p2p_owner_mark(const hctr_p2p_ctx *c, const hctr_p2p_box *mi
 }
 
 extern "C" int hctr_p2p_owner_apply(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, size_t n_cached,
-                                    const int32_t *ent_row, const unsigned long long *row_mask, float *embedding,
+                                    const int32_t *ent_row, const unsigned long long *row_mask,
+                                    unsigned long long *row_head, uint32_t *ent_next, float *embedding,
                                     void *stream) {
   if (c->nrank > 32) return (int)cudaErrorInvalidValue;
-  return launch_owner_apply(mailbox_lists(c, mine), c->cap, c->width, n_cached, ent_row, row_mask, embedding,
-                            (cudaStream_t)stream);
+  return launch_owner_apply(mailbox_lists(c, mine, row_head, ent_next), c->cap, c->width, n_cached, ent_row, row_mask,
+                            embedding, (cudaStream_t)stream);
 }
 
 extern "C" int hctr_p2p_owner_update(const hctr_p2p_ctx *cp, const int32_t *row_of, size_t length, size_t n_cached,

@@ -56,6 +56,7 @@ class OwnerReplay:
         self.emb = torch.randn(S, W, device=dev) * 0.1
         self.version = torch.randint(0, 50, (S,), dtype=torch.int64, device=dev)
         self.mask = torch.zeros(S, dtype=torch.int64, device=dev)
+        self.head = torch.zeros(S, dtype=torch.int64, device=dev)
 
         # traffic of the peers: key-sorted unique keys per source, drawn from a bounded Zipf over this rank's rows
         def draw(m):
@@ -118,6 +119,7 @@ class OwnerReplay:
                        int(50e6))
         slots = n * cap
         self.ent_row = z(slots + 1, torch.int32)
+        self.ent_next = z(slots + 1, torch.int32)
         self.ret_slot = z(slots + 1, torch.int32)
         self.ret_q = z(slots + 1, torch.int32)
         self.ret_row = z(slots + 1, torch.int32)
@@ -127,8 +129,8 @@ class OwnerReplay:
         self.seq = 0
         self.epoch = 0
         i64, u32, sz = ctypes.c_int64, ctypes.c_uint32, ctypes.c_size_t
-        self.L.hctr_p2p_owner_mark.argtypes = [vp, vp, u32, vp, sz, sz, vp, u32, vp, vp, vp]
-        self.L.hctr_p2p_owner_apply.argtypes = [vp, vp, sz, vp, vp, vp, vp]
+        self.L.hctr_p2p_owner_mark.argtypes = [vp, vp, u32, vp, sz, sz, vp, vp, u32, vp, vp, vp, vp]
+        self.L.hctr_p2p_owner_apply.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, vp]
         self.L.hctr_p2p_stale_scan.argtypes = [vp, vp, sz, sz, vp, i64, vp, vp, vp, vp, u32, vp]
         self.L.hctr_p2p_gather.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp]
 
@@ -149,9 +151,11 @@ class OwnerReplay:
         self.epoch += 2
         rec(0)
         rc = L.hctr_p2p_owner_mark(c, mb, self.seq, self.row_of.data_ptr(), self.length, 0, self.mask.data_ptr(),
-                                   self.epoch, self.ent_row.data_ptr(), self.version.data_ptr(), None)
+                                   self.head.data_ptr(), self.epoch, self.ent_row.data_ptr(),
+                                   self.ent_next.data_ptr(), self.version.data_ptr(), None)
         rec(1)
-        rc |= L.hctr_p2p_owner_apply(c, mb, 0, self.ent_row.data_ptr(), self.mask.data_ptr(), self.emb.data_ptr(), None)
+        rc |= L.hctr_p2p_owner_apply(c, mb, 0, self.ent_row.data_ptr(), self.mask.data_ptr(), self.head.data_ptr(),
+                                     self.ent_next.data_ptr(), self.emb.data_ptr(), None)
         rec(2)
         rc |= L.hctr_p2p_stale_scan(c, self.row_of.data_ptr(), self.length, 0, self.version.data_ptr(), pull_bound,
                                     self.ret_slot.data_ptr(), self.ret_q.data_ptr(), self.ret_row.data_ptr(),

@@ -315,10 +315,11 @@ int hctr_p2p_owner_update(const hctr_p2p_ctx *c, const int32_t *row_of, size_t l
  * entries) and adds the update counts to the versions: versions are final when it ends.  hctr_p2p_owner_apply adds
  * the rows; it may run on another stream, concurrently with hctr_p2p_stale_scan. */
 int hctr_p2p_owner_mark(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, uint32_t seq, const int32_t *row_of,
-                        size_t length, size_t n_cached, unsigned long long *row_mask, uint32_t epoch,
-                        int32_t *ent_row, int64_t *version, void *stream);
+                        size_t length, size_t n_cached, unsigned long long *row_mask, unsigned long long *row_head,
+                        uint32_t epoch, int32_t *ent_row, uint32_t *ent_next, int64_t *version, void *stream);
 int hctr_p2p_owner_apply(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, size_t n_cached, const int32_t *ent_row,
-                         const unsigned long long *row_mask, float *embedding, void *stream);
+                         const unsigned long long *row_mask, unsigned long long *row_head, uint32_t *ent_next,
+                         float *embedding, void *stream);
 
 /* Fused flag + scan steps of the owner and of the requester.
  * scratch: hctr_p2p_scan_scratch_words(entries) words, 8-byte aligned, zero-initialised ONCE; epoch non-zero and
@@ -334,7 +335,8 @@ int hctr_p2p_owner_apply(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, size_t
  * csrc/core/all2all.cu:89-130.
  * hctr_p2p_recv_scan (entries = u_max): waits (bounded) for the owners' phase-1 release of `seq`, then collects the
  * flags of this rank's unique keys from its mailbox (flags[u]; zeros for u >= U up to u_max) and computes
- * recv_index[u] = row index (relative to box[rank].rval / rver) of the row returned for unique key u. */
+ * recv_index[u] = row index (relative to box[rank].rval / rver) of the row returned for unique key u, and
+ * recv_list = the unique keys a row came back for, in order (u_max entries at most). */
 size_t hctr_p2p_scan_scratch_words(size_t entries);
 int hctr_p2p_stale_scan(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
                         const int64_t *version, int64_t pull_bound, uint32_t *ret_slot, uint32_t *ret_q,
@@ -342,8 +344,8 @@ int hctr_p2p_stale_scan(const hctr_p2p_ctx *c, const int32_t *row_of, size_t len
 int hctr_p2p_gather(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *ret_q, const int32_t *ret_row,
                     const uint32_t *ret_slot, const float *embedding, const int64_t *version, void *stream);
 int hctr_p2p_recv_scan(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *meta, size_t u_max,
-                       const uint8_t *uniq_owner, uint8_t *flags, uint32_t *recv_index, uint32_t *scratch,
-                       uint32_t epoch, void *stream);
+                       const uint8_t *uniq_owner, uint8_t *flags, uint32_t *recv_index, uint32_t *recv_list,
+                       uint32_t *scratch, uint32_t epoch, void *stream);
 
 typedef struct hctr_reduce_args {
   size_t n_unique;            /* U of the previous batch (host value) */
@@ -414,8 +416,10 @@ int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int
                       const float *val, const int32_t *row_of, size_t length, size_t n_cached,
                       float *embedding, int64_t *version, uint32_t *err, void *stream);
 /* All sources at once, in two launches (mark sources + versions, then rows), with the same per-row apply order
- * (ascending source rank) and therefore the same bits as calling hctr_owner_update once per source.  ent_row is
- * scratch for one 32-bit word per pushed row.  Source s's rows start at entry
+ * (ascending source rank) and therefore the same bits as calling hctr_owner_update once per source.  ent_row and
+ * ent_next are scratch for one 32-bit word per pushed row; row_head is a second array like row_mask (one 64-bit
+ * word per owned row, zero-initialised once, epoch-tagged): the mark pass chains the entries that push the same
+ * row through row_head / ent_next, the row pass walks the chain instead of searching the sources' lists.  Source s's rows start at entry
  * src_off[s] of key/updates/val and number flat_start[s+1] - flat_start[s] (device arrays of nsrc and nsrc+1
  * entries; the counts may only exist on the device); every source's list must be sorted by key, as the
  * slices of a unique list are.  row_mask: one 64-bit word per OWNED row (row - n_cached), zero-initialised once; `epoch` must be
@@ -424,8 +428,9 @@ int hctr_owner_update(size_t n_rows, size_t width, const int64_t *key, const int
 int hctr_owner_update_merged(int nsrc, size_t rows_hint, size_t width, const int64_t *key,
                              const int64_t *updates, const float *val, const unsigned long long *src_off,
                              const uint32_t *flat_start, const int32_t *row_of, size_t length, size_t n_cached,
-                             unsigned long long *row_mask, uint32_t epoch, int32_t *ent_row, float *embedding,
-                             int64_t *version, uint32_t *err, void *stream);
+                             unsigned long long *row_mask, unsigned long long *row_head, uint32_t epoch,
+                             int32_t *ent_row, uint32_t *ent_next, float *embedding, int64_t *version, uint32_t *err,
+                             void *stream);
 
 /* Same, with the row count read from device memory (at most n_rows_max). */
 int hctr_owner_update_dev(size_t n_rows_max, const uint32_t *n_rows_dev, size_t width, const int64_t *key,
@@ -462,6 +467,13 @@ int hctr_recv_slots(size_t n_unique, const uint8_t *flags, uint32_t *flags32, ui
 int hctr_cache_refresh(size_t n_unique, size_t width, const uint8_t *flags, const uint32_t *recv_slot,
                        const int32_t *uniq_row, const float *recv_val, const int64_t *recv_version,
                        const float *pending, float *embedding, int64_t *version, void *stream);
+
+/* hctr_cache_refresh over a list of unique keys whose length only the device knows: the sum of
+ * n_listed[0..n_counts) (at most max_listed, which sizes the grid). */
+int hctr_cache_refresh_listed(const uint32_t *n_listed, int n_counts, size_t max_listed, size_t width,
+                              const uint32_t *list, const uint32_t *recv_slot, const int32_t *uniq_row,
+                              const float *recv_val, const int64_t *recv_version, const float *pending,
+                              float *embedding, int64_t *version, void *stream);
 
 /* dst[i] = row of keys[i]: from the local table when stored (pos_row[i] >= 0), else from the receive
  * buffer at recv_slot[idx_map[i]].  recv_slot / recv_val may be null when every key is stored locally
