@@ -14,7 +14,12 @@ constexpr long long kInvalidVersion = INT64_MIN;
 // finishes last then publishes this rank's counts (queries per owner from the batch's segment starts, pushed rows
 // per owner from `push_counts`, null = none) and releases sequence number `seq` to every peer.  The pushed rows
 // themselves were written by the gradient reduction, an earlier kernel.
-__global__ void __launch_bounds__(kThreads) p2p_query_send(hctr_p2p_ctx c, const u32 *__restrict__ meta,
+// (Publishing kernels run at most one thread block per SM: every block ends with a system-scope fence, and an SM
+// works through the fences of its resident blocks one after the other - with 832 small blocks this kernel took 25 us
+// for 77 k keys, most of it fences.)
+constexpr int kPubThreads = 1024;
+
+__global__ void __launch_bounds__(kPubThreads) p2p_query_send(hctr_p2p_ctx c, const u32 *__restrict__ meta,
                                                            const long long *__restrict__ uniq,
                                                            const uint8_t *__restrict__ uniq_owner,
                                                            const int32_t *__restrict__ uniq_row,
@@ -22,7 +27,7 @@ __global__ void __launch_bounds__(kThreads) p2p_query_send(hctr_p2p_ctx c, const
                                                            const u32 *__restrict__ push_counts) {
   const size_t U = meta[HCTR_META_UNIQUE];
   const u32 *seg = meta + HCTR_META_SEG;
-  for (size_t u = (size_t)blockIdx.x * kThreads + threadIdx.x; u < U; u += (size_t)gridDim.x * kThreads) {
+  for (size_t u = (size_t)blockIdx.x * kPubThreads + threadIdx.x; u < U; u += (size_t)gridDim.x * kPubThreads) {
     const unsigned p = uniq_owner[u];
     const u32 j = (u32)u - seg[p];
     if (j >= c.cap) {
@@ -36,7 +41,7 @@ __global__ void __launch_bounds__(kThreads) p2p_query_send(hctr_p2p_ctx c, const
     b.qver[slot] = row >= 0 ? version[row] : kInvalidVersion;
   }
   if (!last_block_of_launch(c.cnt_in + HCTR_P2P_TICKET0(c.nrank))) return;
-  for (int p = threadIdx.x; p < c.nrank; p += kThreads) {
+  for (int p = threadIdx.x; p < c.nrank; p += kPubThreads) {
     __threadfence_system();
     u32 *hdr = c.box[p].hdr + (size_t)c.rank * kHdrWords;
     hdr[1] = seg[p + 1] - seg[p];
@@ -80,7 +85,7 @@ __global__ void __launch_bounds__(kMaxRanks) p2p_wait(hctr_p2p_ctx c, int phase,
 constexpr int kGatherUnroll = 4;
 
 template <bool VEC>
-__global__ void __launch_bounds__(kThreads) p2p_gather(hctr_p2p_ctx c, u32 seq, const u32 *__restrict__ ret_q,
+__global__ void __launch_bounds__(kPubThreads) p2p_gather(hctr_p2p_ctx c, u32 seq, const u32 *__restrict__ ret_q,
                                                        const int32_t *__restrict__ ret_row,
                                                        const u32 *__restrict__ ret_slot,
                                                        const float *__restrict__ embedding,
@@ -88,13 +93,13 @@ __global__ void __launch_bounds__(kThreads) p2p_gather(hctr_p2p_ctx c, u32 seq, 
   typedef RowT<VEC> R;
   typedef typename R::T T;
   __shared__ u32 qstart[kMaxRanks + 1];
-  for (int i = threadIdx.x; i <= c.nrank; i += kThreads) qstart[i] = c.cnt_in[3 * c.nrank + i];
+  for (int i = threadIdx.x; i <= c.nrank; i += kPubThreads) qstart[i] = c.cnt_in[3 * c.nrank + i];
   __syncthreads();
   const u32 Q = qstart[c.nrank];
   const u32 n_ret = ret_slot[Q];
   const unsigned lane = threadIdx.x & 31;
-  const size_t warp = ((size_t)blockIdx.x * kThreads + threadIdx.x) >> 5;
-  const size_t n_warps = ((size_t)gridDim.x * kThreads) >> 5;
+  const size_t warp = ((size_t)blockIdx.x * kPubThreads + threadIdx.x) >> 5;
+  const size_t n_warps = ((size_t)gridDim.x * kPubThreads) >> 5;
   const u32 E = (u32)R::elems(c.width);
   for (size_t r0 = warp * 32; r0 < n_ret; r0 += n_warps * 32) {
     const u32 cnt = (u32)min((size_t)32, (size_t)n_ret - r0);
@@ -133,7 +138,7 @@ __global__ void __launch_bounds__(kThreads) p2p_gather(hctr_p2p_ctx c, u32 seq, 
     }
   }
   if (!last_block_of_launch(c.cnt_in + HCTR_P2P_TICKET1(c.nrank))) return;
-  for (int p = threadIdx.x; p < c.nrank; p += kThreads) {
+  for (int p = threadIdx.x; p < c.nrank; p += kPubThreads) {
     __threadfence_system();
     u32 *hdr = c.box[p].hdr + (size_t)c.rank * kHdrWords;
     hdr[9] = ret_slot[qstart[p + 1]] - ret_slot[qstart[p]];
@@ -311,7 +316,9 @@ extern "C" int hctr_p2p_query_send(const hctr_p2p_ctx *c, const uint32_t *meta, 
                                    const uint8_t *uniq_owner, const int32_t *uniq_row, const int64_t *version,
                                    uint32_t seq, const uint32_t *push_counts, void *stream) {
   if (c->nrank > kMaxRanks) return (int)cudaErrorInvalidValue;
-  p2p_query_send<<<persistent_grid(u_max), kThreads, 0, (cudaStream_t)stream>>>(
+  size_t g = (u_max + kPubThreads - 1) / kPubThreads;
+  if (g > (size_t)kSMs) g = kSMs;
+  p2p_query_send<<<(unsigned)(g ? g : 1), kPubThreads, 0, (cudaStream_t)stream>>>(
       *c, meta, (const long long *)uniq, uniq_owner, uniq_row, (const long long *)version, seq, push_counts);
   count_launches(1);
   return launch_status();
@@ -354,12 +361,12 @@ extern "C" int hctr_p2p_gather(const hctr_p2p_ctx *c, uint32_t seq, const uint32
   cudaStream_t st = (cudaStream_t)stream;
   if (c->nrank > kMaxRanks) return (int)cudaErrorInvalidValue;
   // one warp per 32 returned rows; at most nrank * cap rows exist, a few resident rounds of blocks cover them
-  size_t g = ((size_t)c->nrank * c->cap / 32 + 1 + kThreads / 32 - 1) / (kThreads / 32);
-  if (g > (size_t)kSMs * 4) g = (size_t)kSMs * 4;
+  size_t g = ((size_t)c->nrank * c->cap / 32 + 1 + kPubThreads / 32 - 1) / (kPubThreads / 32);
+  if (g > (size_t)kSMs) g = kSMs;  // a publishing kernel: one block per SM at most
   if (g == 0) g = 1;
   const bool vec = host_aligned16(embedding) && c->width % 4 == 0;
-  if (vec) p2p_gather<true><<<(unsigned)g, kThreads, 0, st>>>(*c, seq, ret_q, ret_row, ret_slot, embedding, (const long long *)version);
-  else p2p_gather<false><<<(unsigned)g, kThreads, 0, st>>>(*c, seq, ret_q, ret_row, ret_slot, embedding, (const long long *)version);
+  if (vec) p2p_gather<true><<<(unsigned)g, kPubThreads, 0, st>>>(*c, seq, ret_q, ret_row, ret_slot, embedding, (const long long *)version);
+  else p2p_gather<false><<<(unsigned)g, kPubThreads, 0, st>>>(*c, seq, ret_q, ret_row, ret_slot, embedding, (const long long *)version);
   count_launches(1);
   return launch_status();
 }

@@ -1029,8 +1029,9 @@ static int launch_owner_apply(const PushLists &p, size_t rows_hint, size_t width
 }
 
 static unsigned mark_grid(size_t rows_hint) {
+  // at most two blocks per SM: in the peer-to-peer exchange every block starts by polling the mailbox headers
   size_t g = (rows_hint + kThreads - 1) / kThreads;
-  if (g > (size_t)kSMs * 8) g = (size_t)kSMs * 8;
+  if (g > (size_t)kSMs * 2) g = (size_t)kSMs * 2;
   return (unsigned)(g ? g : 1);
 }
 
