@@ -221,7 +221,7 @@ class Table:
         return dict(zip(self._STATS, list(out)))
 
     PHASES = ("dedupe", "push_decide", "reduce", "query", "exchange", "owner_update", "stale_gather", "refresh",
-              "expand", "owner_apply", "stale_scan", "recv_scan")
+              "expand", "owner_apply")
 
     def profile(self, enable=True):
         """False/0: off; True/1: time every step; k > 1: time every k-th step."""

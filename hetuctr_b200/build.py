@@ -23,7 +23,7 @@ CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
 CU_SOURCES = ["kernels/scan.cu", "kernels/dedupe.cu", "kernels/update.cu", "kernels/query.cu", "kernels/table.cu",
-              "kernels/p2p.cu"]
+              "kernels/p2p.cu", "kernels/p2p_pull.cu"]
 CC_SOURCES = ["core/hetu_table.cc", "core/table_state.cc", "core/c_api.cc", "core/transport.cc", "core/p2p.cc", "utils/rendezvous.cc"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC]

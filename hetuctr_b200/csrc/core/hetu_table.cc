@@ -104,13 +104,6 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
     HCTR_CUDA(cudaStreamCreateWithPriority(&stream_reduce_, cudaStreamNonBlocking, single ? hi : lo));
     HCTR_CUDA(cudaStreamCreateWithPriority(&stream_reduce_side_, cudaStreamNonBlocking, hi));
   }
-  {
-    int lo = 0, hi = 0;
-    HCTR_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
-    HCTR_CUDA(cudaStreamCreateWithPriority(&stream_apply_, cudaStreamNonBlocking, hi));
-  }
-  HCTR_CUDA(cudaEventCreateWithFlags(&ev_afork_, cudaEventDisableTiming));
-  HCTR_CUDA(cudaEventCreateWithFlags(&ev_ajoin_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_rfork_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_rjoin_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_decide_, cudaEventDisableTiming));
@@ -993,19 +986,9 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
   const size_t u_max = cur.batch_size;  // U is only known on the device here
   const uint32_t *meta = cur.meta.as<uint32_t>();
   const bool split = p2p_->sameContext();  // thread ranks on one GPU: no kernel may wait for a peer's kernel
-  d_ret_slot_.ensure((slots + 1) * sizeof(uint32_t));
-  d_ret_q_.ensure((slots + 1) * sizeof(uint32_t));
-  d_ret_row_.ensure((slots + 1) * sizeof(int32_t));
   d_ent_row_.ensure((slots + 1) * sizeof(int32_t));
   d_ent_next_.ensure((slots + 1) * sizeof(uint32_t));
-  d_recv_list_.ensure((u_max + 1) * sizeof(uint32_t));
   d_flag_r_.ensure(u_max + 16);
-  {
-    const size_t before = d_chain2_.bytes;
-    d_chain2_.ensure(hctr_p2p_scan_scratch_words(std::max(slots, u_max) + 1) * sizeof(uint32_t));
-    if (d_chain2_.bytes != before)  // epoch tags must not match leftovers of an earlier allocation
-      HCTR_CUDA(cudaMemsetAsync(d_chain2_.p, 0, d_chain2_.bytes, stream_main_));
-  }
   // In split mode every rank drains its stream after publishing and meets the others at a host barrier, so the
   // kernel that consumes finds every sequence number in place and never polls.
   auto meet = [&] {
@@ -1027,24 +1010,19 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
   // C. owner applies the pushed rows of each source in rank order
   const hctr_p2p_box mine = p2p_->mine();
   sp = tic(kPhOwnerUpdate);
-  bool rows_forked = false;
   if (n <= 32) {
-    // pass A waits for the peers' counts, then marks sources and finishes the versions; pass B (the rows) goes to a
-    // second stream and overlaps the staleness scan, which only reads versions
+    // pass A waits for the peers' counts, then marks sources, chains the entries of every row and finishes the
+    // versions; pass B adds the rows
     HCTR_LAUNCH(hctr_p2p_owner_mark(c, &mine, seq, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
                                     d_row_mask_.as<unsigned long long>(), d_row_head_.as<unsigned long long>(),
                                     nextEpoch(), d_ent_row_.as<int32_t>(), d_ent_next_.as<uint32_t>(),
                                     d_version_.as<int64_t>(), stream_main_));
     toc(sp);
-    HCTR_CUDA(cudaEventRecord(ev_afork_, stream_main_));
-    HCTR_CUDA(cudaStreamWaitEvent(stream_apply_, ev_afork_, 0));
-    sp = tic(kPhOwnerApply, stream_apply_);
+    sp = tic(kPhOwnerApply);
     HCTR_LAUNCH(hctr_p2p_owner_apply(c, &mine, kNonLocalStorageMax, d_ent_row_.as<int32_t>(),
                                      d_row_mask_.as<unsigned long long>(), d_row_head_.as<unsigned long long>(),
-                                     d_ent_next_.as<uint32_t>(), d_embedding_.as<float>(), stream_apply_));
-    toc(sp, stream_apply_);
-    HCTR_CUDA(cudaEventRecord(ev_ajoin_, stream_apply_));
-    rows_forked = true;
+                                     d_ent_next_.as<uint32_t>(), d_embedding_.as<float>(), stream_main_));
+    toc(sp);
   } else {
     // more sources than a mask word holds: one cooperative launch with a grid-wide barrier between sources
     HCTR_LAUNCH(hctr_p2p_wait(c, 0, seq, stream_main_));
@@ -1053,33 +1031,20 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
     toc(sp);
   }
 
-  // D. staleness, per-requester counts, rows gathered into the requesters' mailboxes
-  // flat index space: Q = all received queries (device value), at most `slots`; flags, slots and the list of
-  // returned queries come out of one launch
-  sp = tic(kPhStaleScan);
-  HCTR_LAUNCH(hctr_p2p_stale_scan(c, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
-                                  d_version_.as<int64_t>(), pull_bound_, d_ret_slot_.as<uint32_t>(),
-                                  d_ret_q_.as<uint32_t>(), d_ret_row_.as<int32_t>(), d_chain2_.as<uint32_t>(),
-                                  nextEpoch(), stream_main_));
-  toc(sp);
-  if (rows_forked) HCTR_CUDA(cudaStreamWaitEvent(stream_main_, ev_ajoin_, 0));  // the gather reads updated rows
+  // D. staleness test and rows of the stale keys, straight into the requesters' mailboxes (one launch, no scan:
+  // the row for a requester's j-th query goes to row j of this rank's sub-region in its mailbox)
   sp = tic(kPhStaleGather);
-  HCTR_LAUNCH(hctr_p2p_gather(c, seq, d_ret_q_.as<uint32_t>(), d_ret_row_.as<int32_t>(), d_ret_slot_.as<uint32_t>(),
-                              d_embedding_.as<float>(), d_version_.as<int64_t>(), stream_main_));
+  HCTR_LAUNCH(hctr_p2p_stale_gather(c, seq, d_row_of_.as<int32_t>(), kEmbeddingIDMax, kNonLocalStorageMax,
+                                    d_embedding_.as<float>(), d_version_.as<int64_t>(), pull_bound_, stream_main_));
   toc(sp);
   meet();
 
-  // E. requester: wait for the owners, flags -> row indices in its own mailbox, cache refresh, expand
-  sp = tic(kPhRecvScan);
-  HCTR_LAUNCH(hctr_p2p_recv_scan(c, seq, meta, u_max, cur.uniq_owner.as<uint8_t>(), d_flag_r_.as<uint8_t>(),
-                                 d_recv_idx_.as<uint32_t>(), d_recv_list_.as<uint32_t>(), d_chain2_.as<uint32_t>(),
-                                 nextEpoch(), stream_main_));
-  toc(sp);
+  // E. requester: wait for the owners, row index + flag of every unique key, cache refresh; then expand
   sp = tic(kPhRefresh);
-  HCTR_LAUNCH(hctr_cache_refresh_listed(c->cnt_in + 2 * n, n, u_max, W, d_recv_list_.as<uint32_t>(),
-                                        d_recv_idx_.as<uint32_t>(), cur.uniq_row.as<int32_t>(), mine.rval, mine.rver,
-                                        d_gradient_.as<float>(), d_embedding_.as<float>(), d_version_.as<int64_t>(),
-                                        stream_main_));
+  HCTR_LAUNCH(hctr_p2p_refresh_index(c, seq, meta, u_max, cur.uniq_owner.as<uint8_t>(), cur.uniq_row.as<int32_t>(),
+                                     kNonLocalStorageMax, d_gradient_.as<float>(), d_embedding_.as<float>(),
+                                     d_version_.as<int64_t>(), d_flag_r_.as<uint8_t>(), d_recv_idx_.as<uint32_t>(),
+                                     stream_main_));
   toc(sp);
   sp = tic(kPhExpand);
   HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
@@ -1283,13 +1248,12 @@ void HetuTable::releaseAll() {
   cudaSetDevice(device_id_);
   if (stream_side_) cudaStreamSynchronize(stream_side_);
   if (stream_reduce_side_) cudaStreamSynchronize(stream_reduce_side_);
-  if (stream_apply_) cudaStreamSynchronize(stream_apply_);
   if (stream_reduce_) cudaStreamSynchronize(stream_reduce_);
   if (stream_main_) cudaStreamSynchronize(stream_main_);
   p2p_.reset();
   transport_.reset();
   DevBuf *all[] = {&d_embedding_, &d_gradient_, &d_updates_, &d_version_, &d_root_, &d_row_of_, &d_stored_keys_,
-                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_chain_, &d_chain2_, &d_chain3_, &d_ret_q_, &d_ret_row_, &d_ent_row_, &d_ent_next_, &d_recv_list_, &d_row_mask_, &d_row_head_, &d_src_off_, &d_src_cnt_, &d_word_base_, &d_scan_, &d_sk_, &d_cnt_,
+                   &d_bits_, &d_blk_cnt_, &d_blk_flag_, &d_chain_, &d_chain3_, &d_ent_row_, &d_ent_next_, &d_row_mask_, &d_row_head_, &d_src_off_, &d_src_cnt_, &d_word_base_, &d_scan_, &d_sk_, &d_cnt_,
                    &d_push_count_, &d_push_base_, &d_recv_idx_, &d_err_, &d_cnt_s_, &d_cnt_r_, &d_qver_s_,
                    &d_qkey_r_, &d_qver_r_, &d_pkey_s_, &d_pupd_s_, &d_pval_s_, &d_pkey_r_, &d_pupd_r_, &d_pval_r_,
                    &d_flag_s_, &d_flag_r_, &d_flag32_, &d_ret_slot_, &d_recv_slot_, &d_seg_r_, &d_retcnt_s_,
@@ -1328,11 +1292,6 @@ void HetuTable::releaseAll() {
   if (ev_rfork_) cudaEventDestroy(ev_rfork_);
   if (ev_rjoin_) cudaEventDestroy(ev_rjoin_);
   ev_decide_ = ev_reduce_ = ev_rfork_ = ev_rjoin_ = nullptr;
-  if (ev_afork_) cudaEventDestroy(ev_afork_);
-  if (ev_ajoin_) cudaEventDestroy(ev_ajoin_);
-  ev_afork_ = ev_ajoin_ = nullptr;
-  if (stream_apply_) cudaStreamDestroy(stream_apply_);
-  stream_apply_ = nullptr;
   if (stream_reduce_side_) cudaStreamDestroy(stream_reduce_side_);
   stream_reduce_side_ = nullptr;
   if (stream_reduce_) cudaStreamDestroy(stream_reduce_);

@@ -101,12 +101,10 @@ enum Phase {
   kPhQuery,           // hctr_query_versions
   kPhExchange,        // transport groups (all of a step)
   kPhOwnerUpdate,     // hctr_owner_update (all sources); peer-to-peer: wait for the peers + sources and versions
-  kPhStaleGather,     // hctr_stale_check + hctr_gather_rows
-  kPhRefresh,         // hctr_recv_slots + hctr_cache_refresh
+  kPhStaleGather,     // hctr_stale_check + hctr_gather_rows; peer-to-peer: hctr_p2p_stale_gather
+  kPhRefresh,         // hctr_recv_slots + hctr_cache_refresh; peer-to-peer: wait for the owners + hctr_p2p_refresh_index
   kPhExpand,          // hctr_expand_rows
-  kPhOwnerApply,      // peer-to-peer: row pass of the owner update (second stream, overlaps the staleness scan)
-  kPhStaleScan,       // peer-to-peer: hctr_p2p_stale_scan alone (kPhStaleGather is then the gather alone)
-  kPhRecvScan,        // peer-to-peer: wait for the owners + hctr_p2p_recv_scan (kPhRefresh is then the refresh alone)
+  kPhOwnerApply,      // peer-to-peer: row pass of the owner update
   kPhCount
 };
 
@@ -204,8 +202,6 @@ class HetuTable {
   // reads updated rows or versions.
   cudaStream_t stream_reduce_ = nullptr;
   cudaStream_t stream_reduce_side_ = nullptr;  // long-run reduce kernel, forked from stream_reduce_
-  cudaStream_t stream_apply_ = nullptr;        // row pass of the owner update (peer-to-peer exchange)
-  cudaEvent_t ev_afork_ = nullptr, ev_ajoin_ = nullptr;
   cudaEvent_t ev_decide_ = nullptr, ev_reduce_ = nullptr, ev_rfork_ = nullptr, ev_rjoin_ = nullptr;
   cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr, ev_keys_ = nullptr;
   std::unique_ptr<Transport> transport_;
@@ -228,7 +224,7 @@ class HetuTable {
   size_t length_pad_ = 0;
 
   // dedupe scratch (persistent, all-zero between calls) and per-step scratch
-  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain2_, d_chain3_, d_ret_q_, d_ret_row_, d_ent_row_, d_ent_next_, d_recv_list_, d_row_mask_, d_row_head_, d_src_off_, d_src_cnt_, d_word_base_, d_scan_, d_sk_, d_cnt_;
+  DevBuf d_bits_, d_blk_cnt_, d_blk_flag_, d_chain_, d_chain3_, d_ent_row_, d_ent_next_, d_row_mask_, d_row_head_, d_src_off_, d_src_cnt_, d_word_base_, d_scan_, d_sk_, d_cnt_;
   DevBuf d_push_count_, d_push_base_, d_recv_idx_, d_err_;
   size_t shared_capacity_ = 0;
   uint32_t dedupe_epoch_ = 0;

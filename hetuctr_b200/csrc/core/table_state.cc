@@ -74,7 +74,7 @@ void HetuTable::quiesce() {
   // whoever looks at a batch's position lists expects every run in ascending order
   for (BatchDesc *b : {&cur_batch_, &prev_batch_})
     if (b->batch_size > 0) orderLightRuns(*b, stream_side_);
-  for (cudaStream_t s : {stream_main_, stream_side_, stream_reduce_, stream_reduce_side_, stream_apply_})
+  for (cudaStream_t s : {stream_main_, stream_side_, stream_reduce_, stream_reduce_side_})
     if (s) HCTR_CUDA(cudaStreamSynchronize(s));
 }
 

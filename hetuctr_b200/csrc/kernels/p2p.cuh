@@ -109,13 +109,20 @@ __device__ __forceinline__ void wait_queries(const hctr_p2p_ctx &c, u32 seq, u32
       c.cnt_in[3 * n + i] = qstart[i];      // flat index space [0, Q) over all received queries
       c.cnt_in[4 * n + 1 + i] = gstart[i];  // flat index space over all pushed rows
     }
-    if (s == 0) c.cnt_in[HCTR_P2P_WAIT0(n)] = s_wait;
+    if (s == 0) {
+      c.cnt_in[HCTR_P2P_WAIT0(n)] = s_wait;
+      // counters the pull kernels of this step add to
+      c.cnt_in[HCTR_P2P_SERVED(n)] = 0;
+      c.cnt_in[2 * n] = 0;
+    }
   }
 }
 
 // Phase 1, receiving side: thread s waits for owner s's return sequence number; ret_base (nrank + 1 entries, shared
-// memory) receives the exclusive prefix of the returned-row counts.
-__device__ __forceinline__ void wait_returns(const hctr_p2p_ctx &c, u32 seq, u32 *ret_base, bool publish) {
+// memory) receives the exclusive prefix of the row counts the owners announced.  `publish` stores the counts to
+// c.cnt_in, `publish_wait` the longest wait.
+__device__ __forceinline__ void wait_returns(const hctr_p2p_ctx &c, u32 seq, u32 *ret_base, bool publish,
+                                             bool publish_wait) {
   __shared__ u32 s_r[kMaxRanks];
   __shared__ u32 s_wait;
   const int s = threadIdx.x;
@@ -145,10 +152,8 @@ __device__ __forceinline__ void wait_returns(const hctr_p2p_ctx &c, u32 seq, u32
     ret_base[n] = acc;
   }
   __syncthreads();
-  if (publish) {
-    if (s < n) c.cnt_in[2 * n + s] = s_r[s];
-    if (s == 0) c.cnt_in[HCTR_P2P_WAIT1(n)] = s_wait;
-  }
+  if (publish && s < n) c.cnt_in[2 * n + s] = s_r[s];
+  if (publish_wait && s == 0) c.cnt_in[HCTR_P2P_WAIT1(n)] = s_wait;
 }
 
 // Flat index f in [0, start[n]) -> the segment it falls into (start: n + 1 ascending entries).

@@ -113,39 +113,6 @@ __global__ void __launch_bounds__(kThreads) cache_refresh(size_t n_unique, size_
   for (size_t c = gl; c < E; c += LANES) emb[c] = R::add(src[c], pend[c]);
 }
 
-// The same over a LIST of the unique keys a row came back for (n_listed[0..n_counts) summed = its length, known on
-// the device only): a table of the peer-to-peer exchange does not know the number of unique keys of its batch on
-// the host, and one thread block per 8 POSSIBLE keys would mostly launch blocks that have nothing to do.
-template <int LANES, bool VEC>
-__global__ void __launch_bounds__(kThreads) cache_refresh_listed(const u32 *__restrict__ n_listed, int n_counts,
-                                                                 size_t width, const u32 *__restrict__ list,
-                                                                 const u32 *__restrict__ recv_slot,
-                                                                 const int32_t *__restrict__ uniq_row,
-                                                                 const float *__restrict__ recv_val,
-                                                                 const long long *__restrict__ recv_version,
-                                                                 const float *__restrict__ pending,
-                                                                 float *__restrict__ embedding,
-                                                                 long long *__restrict__ version) {
-  typedef RowT<VEC> R;
-  typedef typename R::T T;
-  u32 total = 0;
-  for (int i = 0; i < n_counts; i++) total += n_listed[i];
-  const unsigned gl = threadIdx.x % LANES;
-  const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
-  const size_t E = R::elems(width);
-  for (size_t i = ((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES; i < total; i += groups) {
-    const u32 u = list[i];
-    const int32_t row = uniq_row[u];
-    if (row < 0) continue;  // not cached here: the expansion reads the returned row from the mailbox
-    const size_t slot = recv_slot[u];
-    if (gl == 0) version[row] = recv_version[slot];
-    const T *src = reinterpret_cast<const T *>(recv_val) + slot * E;
-    const T *pend = reinterpret_cast<const T *>(pending) + (size_t)row * E;
-    T *emb = reinterpret_cast<T *>(embedding) + (size_t)row * E;
-    for (size_t c = gl; c < E; c += LANES) emb[c] = R::add(src[c], pend[c]);
-  }
-}
-
 // dst[i] = row of batch key i.  Row reads use default caching (duplicates and the rows just updated
 // hit L2); dst is written once and never re-read by this path, so it is stored evict-first.
 // A group moves kExpandRows rows per iteration so that several independent row reads are in flight
@@ -387,28 +354,6 @@ extern "C" int hctr_cache_refresh(size_t n_unique, size_t width, const uint8_t *
   cache_refresh<L, V><<<grid_for(n_unique * L, kThreads), kThreads, 0, s>>>(                     \
       n_unique, width, flags, recv_slot, uniq_row, recv_val, (const long long *)recv_version, pending, \
       embedding, (long long *)version)
-  HCTR_DISPATCH_ROWS(width, al, CALL);
-#undef CALL
-  count_launches(1);
-  return launch_status();
-}
-
-extern "C" int hctr_cache_refresh_listed(const uint32_t *n_listed, int n_counts, size_t max_listed, size_t width,
-                                         const uint32_t *list, const uint32_t *recv_slot, const int32_t *uniq_row,
-                                         const float *recv_val, const int64_t *recv_version, const float *pending,
-                                         float *embedding, int64_t *version, void *stream) {
-  cudaStream_t s = (cudaStream_t)stream;
-  if (max_listed == 0) return 0;
-  const bool al = host_aligned16(recv_val) && host_aligned16(pending) && host_aligned16(embedding);
-#define CALL(L, V)                                                                                          \
-  do {                                                                                                      \
-    size_t g_ = (max_listed * L + kThreads - 1) / kThreads;                                                 \
-    if (g_ > (size_t)kSMs * 2) g_ = (size_t)kSMs * 2;                                                       \
-    cache_refresh_listed<L, V><<<(unsigned)g_, kThreads, 0, s>>>(n_listed, n_counts, width, list, recv_slot, \
-                                                                 uniq_row, recv_val,                        \
-                                                                 (const long long *)recv_version, pending,  \
-                                                                 embedding, (long long *)version);          \
-  } while (0)
   HCTR_DISPATCH_ROWS(width, al, CALL);
 #undef CALL
   count_launches(1);

@@ -3,7 +3,7 @@
   python -m hetuctr_b200.owner_replay [--sources 8] [--rows 4200000] [--width 128] [--pushed 68000]
                                       [--queries 77000] [--iters 20] [--check | --cap 212992]
 
-In a job of several GPUs the owner-side kernels (source marking + versions, row apply, staleness scan, row gather)
+In a job of several GPUs the owner-side kernels (source marking + versions, row apply, staleness test + row gather)
 run once per step on what the peers stored into this rank's mailbox.  To time or profile them in isolation this
 tool builds one rank's table shard and mailbox on one GPU, fills the mailbox the way `sources - 1` peers would
 (key-sorted push lists drawn from a Zipf distribution over the rank's own rows, so hot rows are pushed by several
@@ -120,19 +120,12 @@ class OwnerReplay:
         slots = n * cap
         self.ent_row = z(slots + 1, torch.int32)
         self.ent_next = z(slots + 1, torch.int32)
-        self.ret_slot = z(slots + 1, torch.int32)
-        self.ret_q = z(slots + 1, torch.int32)
-        self.ret_row = z(slots + 1, torch.int32)
-        self.L.hctr_p2p_scan_scratch_words.restype = ctypes.c_size_t
-        self.L.hctr_p2p_scan_scratch_words.argtypes = [ctypes.c_size_t]
-        self.scratch = z(int(self.L.hctr_p2p_scan_scratch_words(slots + 1)) + 2, torch.int32)
         self.seq = 0
         self.epoch = 0
         i64, u32, sz = ctypes.c_int64, ctypes.c_uint32, ctypes.c_size_t
         self.L.hctr_p2p_owner_mark.argtypes = [vp, vp, u32, vp, sz, sz, vp, vp, u32, vp, vp, vp, vp]
         self.L.hctr_p2p_owner_apply.argtypes = [vp, vp, sz, vp, vp, vp, vp, vp, vp]
-        self.L.hctr_p2p_stale_scan.argtypes = [vp, vp, sz, sz, vp, i64, vp, vp, vp, vp, u32, vp]
-        self.L.hctr_p2p_gather.argtypes = [vp, u32, vp, vp, vp, vp, vp, vp]
+        self.L.hctr_p2p_stale_gather.argtypes = [vp, u32, vp, sz, sz, vp, vp, i64, vp]
 
     def publish(self):
         """What the peers' last thread blocks do: counts + sequence number into this rank's headers."""
@@ -145,7 +138,7 @@ class OwnerReplay:
         self.torch.cuda.synchronize()
 
     def step(self, pull_bound=0, events=None):
-        """One owner-side step; with `events` (5 CUDA events) the four kernels are bracketed for timing."""
+        """One owner-side step; with `events` (4 CUDA events) the three kernels are bracketed for timing."""
         L, c, mb = self.L, ctypes.byref(self.ctx), ctypes.byref(self.mine_box)
         rec = (lambda i: events[i].record()) if events else (lambda i: None)
         self.epoch += 2
@@ -157,13 +150,9 @@ class OwnerReplay:
         rc |= L.hctr_p2p_owner_apply(c, mb, 0, self.ent_row.data_ptr(), self.mask.data_ptr(), self.head.data_ptr(),
                                      self.ent_next.data_ptr(), self.emb.data_ptr(), None)
         rec(2)
-        rc |= L.hctr_p2p_stale_scan(c, self.row_of.data_ptr(), self.length, 0, self.version.data_ptr(), pull_bound,
-                                    self.ret_slot.data_ptr(), self.ret_q.data_ptr(), self.ret_row.data_ptr(),
-                                    self.scratch.data_ptr(), self.epoch + 1, None)
+        rc |= L.hctr_p2p_stale_gather(c, self.seq, self.row_of.data_ptr(), self.length, 0, self.emb.data_ptr(),
+                                      self.version.data_ptr(), pull_bound, None)
         rec(3)
-        rc |= L.hctr_p2p_gather(c, self.seq, self.ret_q.data_ptr(), self.ret_row.data_ptr(), self.ret_slot.data_ptr(),
-                                self.emb.data_ptr(), self.version.data_ptr(), None)
-        rec(4)
         assert rc == 0, "launch failed"
 
     # -- numpy evaluation of the same step: sources one after the other (csrc/core/handle_query.cu:106-116, 7-40) --
@@ -201,17 +190,20 @@ class OwnerReplay:
             if s == self.rank:
                 continue
             box = self.peers[s]
-            k, q = len(ret_rows[s]), len(self.query_keys[s])
+            q = len(self.query_keys[s])
             hdr = box["hdr"].cpu().numpy().reshape(n, 16)[self.rank]
-            assert hdr[8] == self.seq and hdr[9] == k, f"source {s}: announced return count"
-            assert np.array_equal(box["flag"].cpu().numpy()[base:base + q], flags[s].astype(np.uint8)), "flags"
-            assert np.array_equal(box["rval"].cpu().numpy()[base:base + k], emb[ret_rows[s]]), "returned rows differ"
-            assert np.array_equal(box["rver"].cpu().numpy()[base:base + k], ver[ret_rows[s]]), "returned versions"
+            assert hdr[8] == self.seq, f"source {s}: phase-1 sequence number"
+            f = flags[s]
+            assert np.array_equal(box["flag"].cpu().numpy()[base:base + q], f.astype(np.uint8)), "flags"
+            # the row for the j-th query sits at row j of this rank's sub-region, when the key was stale
+            rows = self.row_of_h[self.query_keys[s]]
+            assert np.array_equal(box["rval"].cpu().numpy()[base:base + q][f], emb[rows[f]]), "returned rows differ"
+            assert np.array_equal(box["rver"].cpu().numpy()[base:base + q][f], ver[rows[f]]), "returned versions"
         return True
 
     def time(self, iters=20):
         torch = self.torch
-        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(iters)]
+        ev = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(iters)]
         flush = torch.empty(256 << 20, dtype=torch.uint8, device=self.dev)
         for i in range(3):
             self.publish()
@@ -222,7 +214,7 @@ class OwnerReplay:
             torch.cuda.synchronize()
             self.step(events=ev[i])
         torch.cuda.synchronize()
-        names = ["owner_mark", "owner_apply", "stale_scan", "gather"]
+        names = ["owner_mark", "owner_apply", "stale_gather"]
         us = {nm: 1e3 * float(np.median([ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(iters)]))
               for j, nm in enumerate(names)}
         G = sum(len(k) for k in self.push_keys)
@@ -230,8 +222,8 @@ class OwnerReplay:
         R = int(self.cnt_in[5 * self.n + 6])
         D = 4 * self.W
         rows_touched = len(np.unique(np.concatenate(self.push_keys))) if G else 0
-        alg = {"owner_mark": G * (8 + 8 + 4 + 4 + 16 + 16), "owner_apply": G * D + rows_touched * 2 * D + G * 12,
-               "stale_scan": Q * (16 + 4 + 8 + 1 + 4), "gather": R * (2 * D + 16 + 8)}
+        alg = {"owner_mark": G * (8 + 8 + 4 + 4 + 16 + 16 + 12), "owner_apply": G * D + rows_touched * 2 * D + G * 16,
+               "stale_gather": Q * (16 + 4 + 8 + 1) + R * (2 * D + 8)}
         return {"pushed_rows": G, "distinct_pushed_rows": rows_touched, "queries": Q, "returned_rows": R,
                 "us": us, "algorithmic_bytes": alg,
                 "gbs": {k: (alg[k] / (us[k] * 1e-6) / 1e9 if us[k] > 0 else 0.0) for k in names}}

@@ -270,7 +270,8 @@ typedef struct hctr_p2p_ctx {
   const hctr_p2p_box *box;  /* device array [nrank]; box[rank] is this rank's own mailbox */
   uint32_t *cnt_in;         /* device [HCTR_P2P_CNT_WORDS(nrank)], zero-initialised once: query, push and return counts
                                received from each peer ([0,n), [n,2n), [2n,3n)), the exclusive prefixes of the query
-                               counts ([3n,4n]) and of the push counts ([4n+1,5n+1]), the longest wait of the last step
+                               counts ([3n,4n]) and of the push counts ([4n+1,5n+1]; word 2n is reused as the number
+                               of keys the owners flagged for this rank), the longest wait of the last step
                                for a peer's queries and for a peer's returned rows in microseconds (5n+2, 5n+3), and
                                two arrival counters of the publishing kernels */
   uint32_t *err;            /* device error word */
@@ -293,14 +294,14 @@ int hctr_p2p_query_send(const hctr_p2p_ctx *c, const uint32_t *meta, size_t u_ma
                         const uint32_t *push_counts, void *stream);
 
 /* Publishes this rank's counts to every peer and releases sequence number `seq` (what the last thread block of
- * hctr_p2p_query_send / hctr_p2p_gather does, as a launch of its own).
+ * hctr_p2p_query_send / hctr_p2p_stale_gather does, as a launch of its own).
  * phase 0: query count (from meta's segments) + push_count (null = zeros); phase 1: ret_count. */
 int hctr_p2p_signal(const hctr_p2p_ctx *c, int phase, uint32_t seq, const uint32_t *meta,
                     const uint32_t *counts, void *stream);
 
 /* Waits (bounded by c->timeout_ns) until every peer has released `seq` for `phase`; copies the announced counts
  * into c->cnt_in.  On timeout sets HCTR_ERR_TIMEOUT in *c->err, records zero counts for the silent peers and
- * returns normally.  hctr_p2p_owner_mark (phase 0) and hctr_p2p_recv_scan (phase 1) do the same wait in their
+ * returns normally.  hctr_p2p_owner_mark (phase 0) and hctr_p2p_refresh_index (phase 1) do the same wait in their
  * first instructions; this launch is for the paths that do not use them. */
 int hctr_p2p_wait(const hctr_p2p_ctx *c, int phase, uint32_t seq, void *stream);
 
@@ -313,7 +314,7 @@ int hctr_p2p_owner_update(const hctr_p2p_ctx *c, const int32_t *row_of, size_t l
  * mailbox (`mine` = host copy of box[rank]).  hctr_p2p_owner_mark first waits (bounded) for the peers' phase-0
  * counts of step `seq` and records them in c->cnt_in, then marks sources, resolves rows (ent_row, nrank * cap
  * entries) and adds the update counts to the versions: versions are final when it ends.  hctr_p2p_owner_apply adds
- * the rows; it may run on another stream, concurrently with hctr_p2p_stale_scan. */
+ * the rows. */
 int hctr_p2p_owner_mark(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, uint32_t seq, const int32_t *row_of,
                         size_t length, size_t n_cached, unsigned long long *row_mask, unsigned long long *row_head,
                         uint32_t epoch, int32_t *ent_row, uint32_t *ent_next, int64_t *version, void *stream);
@@ -321,31 +322,25 @@ int hctr_p2p_owner_apply(const hctr_p2p_ctx *c, const hctr_p2p_box *mine, size_t
                          const unsigned long long *row_mask, unsigned long long *row_head, uint32_t *ent_next,
                          float *embedding, void *stream);
 
-/* Fused flag + scan steps of the owner and of the requester.
- * scratch: hctr_p2p_scan_scratch_words(entries) words, 8-byte aligned, zero-initialised ONCE; epoch non-zero and
- * different from every earlier launch on the same scratch.
- * hctr_p2p_stale_scan (entries = nrank * cap): staleness flag of every received query, indexed FLAT (q in [0, Q)
- * runs over the queries of source 0, then source 1, ...; Q and the per-source starts are in c->cnt_in).  Flag
- * bytes go to the requesters' mailboxes, ret_slot[q] (Q + 1 entries) is the slot of query q's row among the
- * returned rows, ret_q[slot] the flat query index and ret_row[slot] the local row of the row in that slot.
- * Replaces decide_outdated_kernel, the scan, the segmented reduce and the select of csrc/core/handle_query.cu:7-73.
- * hctr_p2p_gather: the listed rows (+ versions) go straight into the requesters' mailboxes; the thread block that
- * finishes last publishes the per-requester row counts and releases `seq` (phase 1).  Replaces
- * write_return_value_kernel + all2allReturnOutdated / all2allReturnValue, csrc/core/handle_query.cu:24-40,
- * csrc/core/all2all.cu:89-130.
- * hctr_p2p_recv_scan (entries = u_max): waits (bounded) for the owners' phase-1 release of `seq`, then collects the
- * flags of this rank's unique keys from its mailbox (flags[u]; zeros for u >= U up to u_max) and computes
- * recv_index[u] = row index (relative to box[rank].rval / rver) of the row returned for unique key u, and
- * recv_list = the unique keys a row came back for, in order (u_max entries at most). */
-size_t hctr_p2p_scan_scratch_words(size_t entries);
-int hctr_p2p_stale_scan(const hctr_p2p_ctx *c, const int32_t *row_of, size_t length, size_t n_cached,
-                        const int64_t *version, int64_t pull_bound, uint32_t *ret_slot, uint32_t *ret_q,
-                        int32_t *ret_row, uint32_t *scratch, uint32_t epoch, void *stream);
-int hctr_p2p_gather(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *ret_q, const int32_t *ret_row,
-                    const uint32_t *ret_slot, const float *embedding, const int64_t *version, void *stream);
-int hctr_p2p_recv_scan(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *meta, size_t u_max,
-                       const uint8_t *uniq_owner, uint8_t *flags, uint32_t *recv_index, uint32_t *recv_list,
-                       uint32_t *scratch, uint32_t epoch, void *stream);
+/* Pull side.  Nothing is compacted: the row returned for the j-th query requester s sent to this owner goes to row
+ * (owner * cap + j) of s's mailbox - a place s can compute for each of its unique keys without knowing what the
+ * owner decided - so neither side scans flags.
+ * hctr_p2p_stale_gather (owner; after the pushed rows have been applied): for every received query, indexed FLAT
+ * (q in [0, Q) runs over the queries of source 0, then source 1, ...; Q and the per-source starts are in c->cnt_in),
+ * stale = (requester's version is INT64_MIN or version + pull_bound < owner's version) and the requester is not
+ * this rank.  Flag bytes, and rows + versions of the stale keys, go straight into the requesters' mailboxes; the
+ * thread block that finishes last releases `seq` (phase 1).  Replaces decide_outdated_kernel, the scan, the
+ * segmented reduce, the select and write_return_value_kernel of csrc/core/handle_query.cu:7-78 and
+ * all2allReturnOutdated / all2allReturnValue, csrc/core/all2all.cu:89-130.
+ * hctr_p2p_refresh_index (requester): waits (bounded) for the owners' phase-1 release of `seq`; then for every
+ * unique key u: recv_index[u] = its row in box[rank].rval / rver, flags[u] = the owner's decision, and for a
+ * flagged key cached here embedding[row] = returned row + pending[row], version[row] = returned version.
+ * Replaces the scan and update_cache_kernel of csrc/core/writeback.cu:8-50. */
+int hctr_p2p_stale_gather(const hctr_p2p_ctx *c, uint32_t seq, const int32_t *row_of, size_t length, size_t n_cached,
+                          const float *embedding, const int64_t *version, int64_t pull_bound, void *stream);
+int hctr_p2p_refresh_index(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *meta, size_t u_max,
+                           const uint8_t *uniq_owner, const int32_t *uniq_row, size_t n_cached, const float *pending,
+                           float *embedding, int64_t *version, uint8_t *flags, uint32_t *recv_index, void *stream);
 
 typedef struct hctr_reduce_args {
   size_t n_unique;            /* U of the previous batch (host value) */
@@ -467,13 +462,6 @@ int hctr_recv_slots(size_t n_unique, const uint8_t *flags, uint32_t *flags32, ui
 int hctr_cache_refresh(size_t n_unique, size_t width, const uint8_t *flags, const uint32_t *recv_slot,
                        const int32_t *uniq_row, const float *recv_val, const int64_t *recv_version,
                        const float *pending, float *embedding, int64_t *version, void *stream);
-
-/* hctr_cache_refresh over a list of unique keys whose length only the device knows: the sum of
- * n_listed[0..n_counts) (at most max_listed, which sizes the grid). */
-int hctr_cache_refresh_listed(const uint32_t *n_listed, int n_counts, size_t max_listed, size_t width,
-                              const uint32_t *list, const uint32_t *recv_slot, const int32_t *uniq_row,
-                              const float *recv_val, const int64_t *recv_version, const float *pending,
-                              float *embedding, int64_t *version, void *stream);
 
 /* dst[i] = row of keys[i]: from the local table when stored (pos_row[i] >= 0), else from the receive
  * buffer at recv_slot[idx_map[i]].  recv_slot / recv_val may be null when every key is stored locally

@@ -94,10 +94,9 @@ int hctr_table_stats(hctr_table *t, long long out[13]);
  * timed step each phase of preprocess/push_pull is bracketed by two CUDA events on the stream it runs on; hctr_table_phase_times returns the accumulated milliseconds and
  * call counts per phase (and clears them when reset != 0).  Phase order: dedupe, push_decide, reduce,
  * query, exchange, owner_update, stale_gather, refresh, expand, owner_apply (the row pass of the owner update in
- * the peer-to-peer exchange: it runs on a second stream, concurrently with the staleness scan), stale_scan and
- * recv_scan (peer-to-peer exchange: the scan halves of stale_gather and refresh, timed on their own; recv_scan
- * includes the wait for the owners' rows). */
-#define HCTR_N_PHASES 12
+ * the peer-to-peer exchange; there owner_update is the wait for the peers' queries + source marking + versions, and
+ * refresh includes the wait for the owners' rows). */
+#define HCTR_N_PHASES 10
 int hctr_table_profile(hctr_table *t, int enable);
 int hctr_table_phase_times(hctr_table *t, double ms[HCTR_N_PHASES], long long calls[HCTR_N_PHASES], int reset);
 /* The most recent timed phases (up to 256 are kept) as triples {phase index, start ms, end ms}, oldest first,
