@@ -100,6 +100,34 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def bind_to_gpu_numa_node(gpu_index):
+    """Pins this process to the CPU cores of the NUMA node its GPU hangs off, BEFORE any pinned host buffer is
+    allocated, so that those buffers (first touch) and the threads that drive the copies are local to the GPU's PCIe
+    root.  A launcher such as torchrun binds nothing; with eight ranks moving 220 MB per step each, buffers on the
+    wrong socket make every copy cross the inter-socket link.  Used by both arms.  Returns a description."""
+    try:
+        bus = subprocess.run(["nvidia-smi", "--query-gpu=pci.bus_id", "--format=csv,noheader", "-i", str(gpu_index)],
+                             stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True).stdout.strip().lower()
+        if not bus:
+            return {"numa_node": None}
+        dom, rest = bus.split(":", 1)
+        path = f"/sys/bus/pci/devices/{dom[-4:]}:{rest}/numa_node"
+        node = int(open(path).read().strip())
+        if node < 0:
+            return {"numa_node": None}
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return {"numa_node": node, "cpus": 0}
+        os.sched_setaffinity(0, cpus)
+        return {"numa_node": node, "cpus": len(cpus)}
+    except (OSError, ValueError):
+        return {"numa_node": None}
+
+
 def make_job_workload(cfg, nrank, rank, layout, log_samples):
     """Batches of one shared clustered click log; owners, caches and the rank of every sample either from the
     offline partitioner ("graph") or dealt at random ("random")."""
@@ -170,6 +198,8 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", 1))
     local = int(os.environ.get("LOCAL_RANK", 0))
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    all_cpus = os.sched_getaffinity(0)
+    binding = bind_to_gpu_numa_node(local)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -354,7 +384,9 @@ def run_ours(args):
                        "transport": table.exchange_name()},
             "e2e": {"value": world * B * args.e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": B * 8 + B * W * 4, "d2h_bytes_per_step": B * W * 4,
-                    "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps},
+                    "ms_per_step": e2e_ms / args.e2e_steps, "steps": args.e2e_steps,
+                    "host_gbs_per_gpu": (B * 8 + 2 * B * W * 4) / (e2e_ms / args.e2e_steps * 1e-3) / 1e9,
+                    "host_binding": binding},
             "gpu_launches": int(launches),
             "roofline": {"bound": "hbm", "kernel": kernels[dom],
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -370,6 +402,7 @@ def run_ours(args):
             out["nvlink"] = nvlink
         # the CPU baseline is a single-GPU-run item (a multi-rank launcher also pins OpenMP to one thread)
         if not args.no_cpu_baseline and world == 1:
+            os.sched_setaffinity(0, all_cpus)  # the CPU baseline uses every host core
             out["cpu_baseline"] = cpu_baseline(args, world)
     table.close()
     if world > 1:
@@ -438,6 +471,7 @@ def run_reference(args):
     c = CONFIGS[args.config]
     B = c["samples"] * c["fields"]
     ref = _ref_module() if _gpu_present() else None
+    binding = bind_to_gpu_numa_node(local) if ref is not None else None
     if ref is None:
         if rank != 0:
             return None
@@ -506,7 +540,7 @@ def run_reference(args):
                                        f"(one driving host thread per rank; the reference has no CPU path)"},
             "e2e": {"value": world * B * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": B * 8 + B * W * 4, "d2h_bytes_per_step": B * W * 4,
-                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps}}
+                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps, "host_binding": binding}}
 
 
 def main():
