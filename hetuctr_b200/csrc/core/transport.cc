@@ -4,6 +4,7 @@
 
 #include <chrono>
 #include <condition_variable>
+#include <cstdlib>
 #include <cstring>
 #include <iostream>
 #include <map>
@@ -13,6 +14,8 @@
 #include "utils/rendezvous.h"
 
 namespace hetuCTR {
+
+void Transport::waitStream(cudaStream_t stream) { HCTR_CUDA(cudaStreamSynchronize(stream)); }
 
 namespace {
 
@@ -34,6 +37,30 @@ class NcclTransport : public Transport {
     tcp.broadcast(&uid, sizeof(uid));
     HCTR_NCCL(ncclCommInitRank(&comm_, nrank, uid, rank));
     nrank_ = nrank;
+    if (const char *e = std::getenv("HCTR_NCCL_TIMEOUT_MS")) {
+      char *end = nullptr;
+      const long ms = std::strtol(e, &end, 10);
+      HCTR_CHECK(end != e && *end == 0 && ms >= 100 && ms <= 3600000, "HCTR_NCCL_TIMEOUT_MS must be in [100, 3600000]");
+      timeout_ms_ = ms;
+    }
+  }
+  void waitStream(cudaStream_t stream) override {
+    const auto t0 = std::chrono::steady_clock::now();
+    for (unsigned spins = 0;; spins++) {
+      const cudaError_t q = cudaStreamQuery(stream);
+      if (q == cudaSuccess) return;
+      if (q != cudaErrorNotReady) HCTR_CUDA(q);
+      if ((spins & 1023u) != 1023u) continue;  // look at the clock and the communicator now and then only
+      ncclResult_t async = ncclSuccess;
+      HCTR_NCCL(ncclCommGetAsyncError(comm_, &async));
+      const bool late = std::chrono::steady_clock::now() - t0 > std::chrono::milliseconds(timeout_ms_);
+      if (async != ncclSuccess && async != ncclInProgress || late) {
+        ncclCommAbort(comm_);  // unblocks the kernels of the stuck group
+        comm_ = nullptr;
+        throw std::runtime_error(late ? "NCCL exchange did not finish in time (is every rank calling the same step?)"
+                                      : std::string("NCCL reported an asynchronous error: ") + ncclGetErrorString(async));
+      }
+    }
   }
   ~NcclTransport() override {
     if (comm_) ncclCommDestroy(comm_);
@@ -61,6 +88,7 @@ class NcclTransport : public Transport {
  private:
   ncclComm_t comm_ = nullptr;
   int nrank_ = 1;
+  long timeout_ms_ = 120000;
 };
 
 // ------------------------------------------------------------------------------------------------

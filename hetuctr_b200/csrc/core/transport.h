@@ -35,6 +35,10 @@ class Transport {
   virtual void allgatherHost(const void *mine, void *all, size_t bytes) = 0;
   // True when ranks are separate processes that each drive their own GPU.
   virtual bool multiProcess() const = 0;
+  // Waits until `stream` has drained.  The NCCL transport does not block inside the driver: it polls the stream
+  // and the communicator's asynchronous error state, and after HCTR_NCCL_TIMEOUT_MS (default 120 s; a peer that
+  // never joins a group leaves the stream stuck for ever) aborts the communicator and throws.
+  virtual void waitStream(cudaStream_t stream);
 };
 
 // ip == "inproc" selects the in-process transport (all ranks of the job must use the same port value,
