@@ -459,7 +459,7 @@ void HetuTable::preprocess(index_t *data_ptr, size_t batch_size) {
     HCTR_CUDA(cudaEventSynchronize(ev_keys_));
     return;
   }
-  HCTR_CUDA(cudaStreamSynchronize(stream_main_));
+  transport_->waitStream(stream_main_);  // an NCCL group is in the stream: wait with a deadline
   collectSpans();
   finalizeBatch();
 }
@@ -928,7 +928,8 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   if (dst_staged)
     HCTR_CUDA(cudaMemcpyAsync(dst, dst_dev, cur.batch_size * W * sizeof(embed_t), cudaMemcpyDeviceToHost, tail));
   // the expand kernel reports a bounded wait that ran out through a mapped pinned word: nothing to copy back
-  HCTR_CUDA(cudaStreamSynchronize(tail));
+  if (transport_ && !use_p2p_) transport_->waitStream(tail);
+  else HCTR_CUDA(cudaStreamSynchronize(tail));
   collectSpans();
   if (h_ingest_err_[1]) {
     h_ingest_err_[1] = 0;
