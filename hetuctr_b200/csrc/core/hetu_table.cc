@@ -871,7 +871,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     HCTR_LAUNCH(hctr_recv_slots(U, d_flag_r_.as<uint8_t>(), d_flag32_.as<uint32_t>(), d_recv_slot_.as<uint32_t>(),
                                 d_scan_.as<uint32_t>(), stream_main_));
     toc(sp);
-    HCTR_CUDA(cudaStreamSynchronize(stream_main_));  // the one mid-step host sync: NCCL needs the row counts
+    transport_->waitStream(stream_main_);  // the one mid-step host sync: NCCL needs the row counts
 
     if (*h_err) {
       HCTR_CUDA(cudaMemsetAsync(d_err_.p, 0, sizeof(uint32_t), stream_main_));
