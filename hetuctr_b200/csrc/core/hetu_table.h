@@ -155,11 +155,9 @@ class HetuTable {
   // (A single-rank table learns the unique count of its current batch only when the dedupe, which runs behind the
   // step, has finished: asking waits for it.)
   const StepStats &stats() {
-    if (cur_batch_.pending || prev_batch_.pending) {
-      quiesce();
-      stats_.unique = cur_batch_.unique_size;
-      stats_.prev_unique = prev_batch_.unique_size;
-    }
+    if (cur_batch_.pending || prev_batch_.pending) quiesce();
+    stats_.unique = stats_.batch ? cur_batch_.unique_size : 0;
+    stats_.prev_unique = stats_.prev_batch ? prev_batch_.unique_size : 0;
     return stats_;
   }
   // "none" (single rank), "nccl", "inproc" or "p2p"
