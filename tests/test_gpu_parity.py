@@ -61,7 +61,7 @@ def test_config1_plumbing(oracle_mod):
     gw.close()
 
 
-@pytest.mark.parametrize("width", [1, 3, 4, 8, 20, 32, 64, 100, 128, 132, 256, 512, 516, 1024])
+@pytest.mark.parametrize("width", [1, 3, 4, 8, 20, 32, 64, 100, 128, 132, 256, 512, 516, 1024, 1100])
 def test_single_rank_widths(oracle_mod, width):
     N, B = 5000, 3000
     root = np.zeros(N, dtype=np.uint8)
