@@ -446,7 +446,9 @@ __device__ __forceinline__ void cursor_next_key(RowCursor &c, u32 l, u32 len, in
   }
 }
 
-template <int D, int EPL>
+// EC: row size in float4 when known at compile time (32, 64 or 128 for rows of 128, 256 or 512 floats - the
+// bounds checks and multiplications by the row size then fold away), 0: taken from the arguments.
+template <int D, int EPL, int EC>
 __global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKernelArgs ka) {
   extern __shared__ float4 ring_all[];
   const hctr_reduce_args &a = ka.a;
@@ -458,7 +460,7 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKerne
   // would leave whole blocks - and with them whole SMs - without work.
   const u64 warp = (u64)(threadIdx.x >> 5) * gridDim.x + blockIdx.x;
   const u64 n_warps = ((u64)gridDim.x * kThreads) >> 5;
-  const size_t E = a.width / 4;
+  const size_t E = EC ? (size_t)EC : a.width / 4;
   const u32 U = (u32)unique_count(a);
   const T *grad = reinterpret_cast<const T *>(a.grad);
   T *emb_base = reinterpret_cast<T *>(a.embedding);
@@ -575,7 +577,8 @@ __global__ void __launch_bounds__(kThreads) grad_reduce_short_stream(ReduceKerne
       }
       if (++C.j == (int)C.len) {
         // the key is complete: scale once, then the update its storage class asks for
-        const unsigned long long outk = __shfl_sync(0xffffffffu, outp, C.k);
+        // (only a pushed key - not stored, or cached with its push due - has a destination to fetch)
+        const unsigned long long outk = (C.type == 0 || C.type == 2) ? __shfl_sync(0xffffffffu, outp, C.k) : 0ull;
         T *emb = emb_base + (C.type != 0 ? (size_t)C.row * E : 0);
         T *pend = pend_base + (C.type >= 2 ? (size_t)C.row * E : 0);
         T *out = reinterpret_cast<T *>(outk);
@@ -1219,9 +1222,12 @@ extern "C" int hctr_grad_reduce_apply_pack(const hctr_reduce_args *ap, void *str
   if (streaming_shape(a.width, al) && a.n_unique < 0x7fffffffu) {
     const size_t E = a.width / 4;
     const int variant = E <= 32 ? 0 : E <= 64 ? 1 : 2;
-    void (*kernel)(ReduceKernelArgs) = variant == 0   ? grad_reduce_short_stream<8, 1>
-                                       : variant == 1 ? grad_reduce_short_stream<4, 2>
-                                                      : grad_reduce_short_stream<2, 4>;
+    void (*kernel)(ReduceKernelArgs) = E == 32    ? grad_reduce_short_stream<8, 1, 32>
+                                       : E == 64    ? grad_reduce_short_stream<4, 2, 64>
+                                       : E == 128   ? grad_reduce_short_stream<2, 4, 128>
+                                       : variant == 0 ? grad_reduce_short_stream<8, 1, 0>
+                                       : variant == 1 ? grad_reduce_short_stream<4, 2, 0>
+                                                      : grad_reduce_short_stream<2, 4, 0>;
     const int depth = variant == 0 ? 8 : variant == 1 ? 4 : 2;
     const size_t smem = (size_t)(kThreads / 32) * depth * E * sizeof(float4);  // at most 32 KB
     static int per_sm_of[3][3] = {};  // resident thread blocks per SM, by kernel variant and ring size class
