@@ -111,6 +111,8 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_fork_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_join_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_keys_, cudaEventDisableTiming));
+  HCTR_CUDA(cudaEventCreateWithFlags(&ev_early_, cudaEventDisableTiming));
+  if (const char *e = std::getenv("HCTR_SPLIT_HOST_EXPAND")) split_host_expand_ = std::atoi(e) != 0;
 
   try {
     initComm(ip, port);
@@ -633,7 +635,7 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
   }
 
   // dst (and grad) are normally device memory; host buffers are staged
-  embed_t *dst_dev = dst;
+  embed_t *dst_dev = dst, *dst_mapped = nullptr;
   bool dst_staged = false;
   if (cur.batch_size > 0) {
     cudaPointerAttributes attr;
@@ -643,14 +645,34 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
       attr.type = cudaMemoryTypeUnregistered;
     }
     if (!(attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged)) {
-      d_stage_dst_.ensure(cur.batch_size * W * sizeof(embed_t));
-      dst_dev = d_stage_dst_.as<embed_t>();
+      dst_mapped = attr.type == cudaMemoryTypeHost ? static_cast<embed_t *>(attr.devicePointer) : nullptr;
       dst_staged = true;
     }
   }
   const embed_t *grad_dev = grad;
   if (grad != nullptr && prev.batch_size > 0)
     grad_dev = static_cast<const embed_t *>(stageIn(grad, prev.batch_size * W * sizeof(embed_t), d_stage_grad_, stream_reduce_));
+
+  // Single rank, gradients arriving from host memory and dst in pinned host memory: the step is two transfers over
+  // the host link with a short computation between them.  The rows of dst whose keys the previous batch did not
+  // contain do not depend on the gradients, so they are written (by the kernel, straight into dst) while the
+  // gradients are still coming in, and only the other rows after the update: the two directions of the link overlap.
+  const bool split_expand = n == 1 && dst_mapped != nullptr && grad_dev != grad && prev.scatter_recorded &&
+                            cur.batch_size > 0 && split_host_expand_;
+  if (split_expand) {
+    dst_dev = dst_mapped;
+    dst_staged = false;
+    // stream_main_ is idle here (the previous batch's dedupe ended long ago; this batch's is enqueued below) and
+    // already waits for the key ingest
+    HCTR_CUDA(cudaStreamWaitEvent(stream_main_, prev.ev_scatter, 0));
+    HCTR_LAUNCH(hctr_expand_rows_subset(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.keys.as<int64_t>(),
+                                        prev.uniq.as<int64_t>(), prev.meta.as<uint32_t>(), 0,
+                                        d_embedding_.as<float>(), dst_dev, stream_main_));
+    HCTR_CUDA(cudaEventRecord(ev_early_, stream_main_));
+  } else if (dst_staged) {
+    d_stage_dst_.ensure(cur.batch_size * W * sizeof(embed_t));
+    dst_dev = d_stage_dst_.as<embed_t>();
+  }
 
   size_t pushed = 0, push_recv = 0, q_recv = 0;
   for (int p = 0; p < n; p++) {
@@ -729,8 +751,15 @@ void HetuTable::pushPull(embed_t *grad, embed_t *dst) {
     // keeps running on stream_main_; nothing of this step reads its results.
     HCTR_CUDA(cudaStreamWaitEvent(tail, ev_keys_, 0));
     int sp = tic(kPhExpand, tail);
-    HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
-                                 nullptr, d_embedding_.as<float>(), dst_dev, d_ingest_err_ + 1, tail));
+    if (split_expand) {
+      HCTR_LAUNCH(hctr_expand_rows_subset(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.keys.as<int64_t>(),
+                                          prev.uniq.as<int64_t>(), prev.meta.as<uint32_t>(), 1,
+                                          d_embedding_.as<float>(), dst_dev, tail));
+      HCTR_CUDA(cudaStreamWaitEvent(tail, ev_early_, 0));  // the step ends when both halves are in dst
+    } else {
+      HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(), nullptr,
+                                   nullptr, d_embedding_.as<float>(), dst_dev, d_ingest_err_ + 1, tail));
+    }
     toc(sp, tail);
     // The dedupe of this batch goes behind the step's critical path on stream_main_ (low priority): only the next
     // step's reduction needs it.  (Holding it back until the reduction has ended was measured and is slower: the
@@ -1288,6 +1317,8 @@ void HetuTable::releaseAll() {
   if (ev_fork_) cudaEventDestroy(ev_fork_);
   if (ev_join_) cudaEventDestroy(ev_join_);
   if (ev_keys_) cudaEventDestroy(ev_keys_);
+  if (ev_early_) cudaEventDestroy(ev_early_);
+  ev_early_ = nullptr;
   if (ev_decide_) cudaEventDestroy(ev_decide_);
   if (ev_reduce_) cudaEventDestroy(ev_reduce_);
   if (ev_rfork_) cudaEventDestroy(ev_rfork_);

@@ -202,6 +202,8 @@ class HetuTable {
   cudaStream_t stream_reduce_side_ = nullptr;  // long-run reduce kernel, forked from stream_reduce_
   cudaEvent_t ev_decide_ = nullptr, ev_reduce_ = nullptr, ev_rfork_ = nullptr, ev_rjoin_ = nullptr;
   cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr, ev_keys_ = nullptr;
+  cudaEvent_t ev_early_ = nullptr;   // end of the gradient-independent half of a split row expansion
+  bool split_host_expand_ = true;    // HCTR_SPLIT_HOST_EXPAND=0 switches the split off
   std::unique_ptr<Transport> transport_;
   std::unique_ptr<P2PMailbox> p2p_;  // device-driven exchange (one process per GPU, peer access); else NCCL groups
   bool use_p2p_ = false;

@@ -159,6 +159,58 @@ __global__ void __launch_bounds__(kThreads) expand_rows(size_t batch, size_t wid
   }
 }
 
+// One half of the row expansion of a single-rank table: only the positions whose key is (in_prev != 0) or is not
+// (in_prev == 0) among the unique keys of the previous batch.  The gradients of the previous batch change exactly the
+// rows of those keys, so the "is not" half can run before they are applied - while they are still on their way from
+// host memory - and the "is" half after.  prev_uniq is ascending (single owner); every lane of a group searches it
+// for the same key, which the hardware serves as one broadcast access per step.
+template <int LANES, bool VEC>
+__global__ void __launch_bounds__(kThreads) expand_rows_subset(size_t batch, size_t width, const int32_t *__restrict__ pos_row,
+                                                               const long long *__restrict__ keys,
+                                                               const long long *__restrict__ prev_uniq,
+                                                               const u32 *__restrict__ prev_meta, int in_prev,
+                                                               const float *__restrict__ embedding,
+                                                               float *__restrict__ dst) {
+  typedef RowT<VEC> R;
+  typedef typename R::T T;
+  const size_t groups = ((size_t)gridDim.x * kThreads) / LANES;
+  const unsigned gl = threadIdx.x % LANES;
+  const size_t E = R::elems(width);
+  const size_t U = prev_meta[HCTR_META_UNIQUE];
+  for (size_t i0 = (((size_t)blockIdx.x * kThreads + threadIdx.x) / LANES) * kExpandRows; i0 < batch;
+       i0 += groups * kExpandRows) {
+    const T *src[kExpandRows];
+    bool mine[kExpandRows];
+#pragma unroll
+    for (int k = 0; k < kExpandRows; k++) {
+      src[k] = nullptr;
+      mine[k] = false;
+      const size_t i = i0 + k;
+      if (i < batch) {
+        const long long key = keys[i];
+        size_t lo = 0, hi = U;  // first entry >= key
+        while (lo < hi) {
+          const size_t mid = (lo + hi) >> 1;
+          if (prev_uniq[mid] < key) lo = mid + 1;
+          else hi = mid;
+        }
+        const bool found = lo < U && prev_uniq[lo] == key;
+        mine[k] = found == (in_prev != 0);
+        const int32_t row = pos_row[i];  // < 0: key was out of range (the host reports it); write zeros
+        if (mine[k] && row >= 0) src[k] = reinterpret_cast<const T *>(embedding) + (size_t)row * E;
+      }
+    }
+    for (size_t c = gl; c < E; c += LANES) {
+      T v[kExpandRows];
+#pragma unroll
+      for (int k = 0; k < kExpandRows; k++) v[k] = src[k] ? src[k][c] : R::zero();
+#pragma unroll
+      for (int k = 0; k < kExpandRows; k++)
+        if (mine[k]) R::st_once(reinterpret_cast<T *>(dst) + (i0 + k) * E + c, v[k]);
+    }
+  }
+}
+
 
 // ---- expand through the bulk-copy engine ---------------------------------------------------------------
 // Each lane moves whole rows with two asynchronous bulk copies (cp.async.bulk): table (or receive-buffer) row ->
@@ -402,6 +454,26 @@ extern "C" int hctr_expand_rows(size_t batch, size_t width, const int32_t *pos_r
     if (g_ > cap_) g_ = cap_;                                                            \
     expand_rows<L, V><<<(unsigned)g_, kThreads, 0, s>>>(batch, width, pos_row, idx_map,  \
                                                         recv_slot, recv_val, embedding, dst); \
+  } while (0)
+  HCTR_DISPATCH_ROWS(width, al, CALL);
+#undef CALL
+  count_launches(1);
+  return launch_status();
+}
+
+extern "C" int hctr_expand_rows_subset(size_t batch, size_t width, const int32_t *pos_row, const int64_t *keys,
+                                       const int64_t *prev_uniq, const uint32_t *prev_meta, int in_prev,
+                                       const float *embedding, float *dst, void *stream) {
+  cudaStream_t s = (cudaStream_t)stream;
+  if (batch == 0) return 0;
+  const bool al = host_aligned16(embedding) && host_aligned16(dst);
+#define CALL(L, V)                                                                       \
+  do {                                                                                   \
+    size_t g_ = (((size_t)batch + kExpandRows - 1) / kExpandRows * L + kThreads - 1) / kThreads; \
+    const size_t cap_ = (size_t)kSMs * 3;                                                \
+    if (g_ > cap_) g_ = cap_;                                                            \
+    expand_rows_subset<L, V><<<(unsigned)g_, kThreads, 0, s>>>(                          \
+        batch, width, pos_row, (const long long *)keys, (const long long *)prev_uniq, prev_meta, in_prev, embedding, dst); \
   } while (0)
   HCTR_DISPATCH_ROWS(width, al, CALL);
 #undef CALL

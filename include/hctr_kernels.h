@@ -470,6 +470,14 @@ int hctr_expand_rows(size_t batch, size_t width, const int32_t *pos_row, const i
                      const uint32_t *recv_slot, const float *recv_val, const float *embedding,
                      float *dst, void *stream);
 
+/* Half of hctr_expand_rows for a table that stores every key itself: only the positions whose key is
+ * (in_prev != 0) / is not (in_prev == 0) among prev_uniq[0 .. prev_meta[HCTR_META_UNIQUE]), the ascending unique
+ * keys of the previous batch.  The two halves together write every row of dst exactly once; the "is not" half
+ * reads no row the previous batch's gradients change. */
+int hctr_expand_rows_subset(size_t batch, size_t width, const int32_t *pos_row, const int64_t *keys,
+                            const int64_t *prev_uniq, const uint32_t *prev_meta, int in_prev,
+                            const float *embedding, float *dst, void *stream);
+
 /* Same result through the bulk-copy engine (cp.async.bulk row -> shared memory -> dst, double-buffered per warp,
  * mbarrier completion with bounded waits: a wait that runs out sets HCTR_ERR_TIMEOUT in *err).  Needs 16-byte
  * aligned buffers, width % 4 == 0 and rows of at most 4 KB; anything else goes to hctr_expand_rows. */

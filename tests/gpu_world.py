@@ -43,11 +43,13 @@ def _parallel(fns):
 
 class GpuWorld:
     def __init__(self, nrank, length, width, pull_bound, push_bound, learning_rate, root_arr, storage_arrs,
-                 init=(hb.INIT_ZERO, 0.0, 0.0), device=0, keys_on_device=True, exchange="inproc"):
+                 init=(hb.INIT_ZERO, 0.0, 0.0), device=0, keys_on_device=True, exchange="inproc",
+                 buffers="device"):
         self.nrank, self.length, self.width = nrank, length, width
         self.exchange = exchange if nrank > 1 else "none"
         self.dev = torch.device("cuda", device)
         self.keys_on_device = keys_on_device
+        self.buffers = buffers  # where gradients and pulled rows live: "device", "pinned" or "pageable" host memory
         self.tables = [None] * nrank
         port = next(_job)
 
@@ -94,6 +96,8 @@ class GpuWorld:
         self._batch = [k.size for k in keys]
 
     def push_pull(self, grads_per_rank):
+        if self.buffers != "device":
+            return self._push_pull_host(grads_per_rank)
         dsts = [torch.full((max(b, 1), self.width), float("nan"), device=self.dev) for b in self._batch]
         if grads_per_rank is None:
             grads = [None] * self.nrank
@@ -102,6 +106,18 @@ class GpuWorld:
         torch.cuda.synchronize()
         _parallel([lambda r=r: self.tables[r].push_pull(grads[r], dsts[r]) for r in range(self.nrank)])
         return [d[:b].cpu().numpy() for d, b in zip(dsts, self._batch)]
+
+    def _push_pull_host(self, grads_per_rank):
+        pin = self.buffers == "pinned"
+        dsts = [torch.full((max(b, 1), self.width), float("nan")) for b in self._batch]
+        grads = [None] * self.nrank
+        if grads_per_rank is not None:
+            grads = [torch.from_numpy(np.array(g, dtype=np.float32, order="C")) for g in grads_per_rank]
+        if pin:
+            dsts = [d.pin_memory() for d in dsts]
+            grads = [g.pin_memory() if g is not None else None for g in grads]
+        _parallel([lambda r=r: self.tables[r].push_pull(grads[r], dsts[r]) for r in range(self.nrank)])
+        return [d[:b].numpy().copy() for d, b in zip(dsts, self._batch)]
 
     def get_all(self, what, prev=False):
         """`what` of every rank, fetched by all ranks at the same time (some views are collective)."""

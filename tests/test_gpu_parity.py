@@ -123,6 +123,34 @@ def test_edge_cases_empty_repeat_inference_host_keys(oracle_mod):
     gw.close()
 
 
+@pytest.mark.parametrize("buffers", ["pinned", "pageable"])
+@pytest.mark.parametrize("width", [128, 16, 6])
+def test_single_rank_host_gradients_and_rows(oracle_mod, buffers, width):
+    # gradients and pulled rows in host memory.  With pinned memory the rows whose keys the previous batch did not
+    # contain are written before the gradients are applied and the others after: consecutive batches here share
+    # about half of their keys, contain duplicates, and one step is an inference step, one batch is empty.
+    N, B = 5000, 3000
+    root = np.zeros(N, dtype=np.uint8)
+    gw, ow = make_worlds(oracle_mod, 1, N, width, 0, 0, 0.1, root, [np.arange(N)], buffers=buffers,
+                         keys_on_device=False)
+    rng = np.random.RandomState(21)
+    hot = rng.randint(N, size=400)
+    e = np.zeros(0, dtype=np.int64)
+
+    def batch(n):
+        k = rng.randint(N, size=n)
+        m = rng.rand(n) < 0.5
+        k[m] = hot[rng.randint(len(hot), size=int(m.sum()))]
+        return k
+
+    sizes = [B, B, 700, B, 0, B, B, 40, B]
+    batches = [[batch(n) if n else e] for n in sizes]
+    grads = [None] + [[rng.normal(0, 1, size=(sizes[i - 1], width)).astype(np.float32)] for i in range(1, len(sizes))]
+    grads[4] = None  # inference step: batch 3's gradient is never applied
+    run_steps(gw, ow, batches, grads)
+    gw.close()
+
+
 def test_out_of_range_key_raises_and_table_recovers(oracle_mod):
     N, W = 300, 4
     root = np.zeros(N, dtype=np.uint8)
