@@ -113,6 +113,7 @@ HetuTable::HetuTable(const int rank, const int nrank, const int device_id, const
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_keys_, cudaEventDisableTiming));
   HCTR_CUDA(cudaEventCreateWithFlags(&ev_early_, cudaEventDisableTiming));
   if (const char *e = std::getenv("HCTR_SPLIT_HOST_EXPAND")) split_host_expand_ = std::atoi(e) != 0;
+  if (const char *e = std::getenv("HCTR_P2P_FUSED_EXPAND")) fused_refresh_expand_ = std::atoi(e) != 0;
 
   try {
     initComm(ip, port);
@@ -1069,17 +1070,28 @@ void HetuTable::exchangeP2P(embed_t *dst_dev) {
   toc(sp);
   meet();
 
-  // E. requester: wait for the owners, row index + flag of every unique key, cache refresh; then expand
-  sp = tic(kPhRefresh);
-  HCTR_LAUNCH(hctr_p2p_refresh_index(c, seq, meta, u_max, cur.uniq_owner.as<uint8_t>(), cur.uniq_row.as<int32_t>(),
-                                     kNonLocalStorageMax, d_gradient_.as<float>(), d_embedding_.as<float>(),
-                                     d_version_.as<int64_t>(), d_flag_r_.as<uint8_t>(), d_recv_idx_.as<uint32_t>(),
-                                     stream_main_));
-  toc(sp);
-  sp = tic(kPhExpand);
-  HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
-                               d_recv_idx_.as<uint32_t>(), mine.rval, d_embedding_.as<float>(), dst_dev, d_ingest_err_ + 1, stream_main_));
-  toc(sp);
+  // E. requester: wait for the owners, cache refresh and row expansion in one launch; or (HCTR_P2P_FUSED_EXPAND=0,
+  // HCTR_EXPAND=bulk) in two: row index + flag of every unique key and cache refresh, then the expansion
+  if (fused_refresh_expand_ && !expand_bulk_) {
+    sp = tic(kPhExpand);
+    HCTR_LAUNCH(hctr_p2p_refresh_expand(c, seq, meta, cur.uniq_owner.as<uint8_t>(), cur.uniq_row.as<int32_t>(),
+                                        kNonLocalStorageMax, d_gradient_.as<float>(), d_embedding_.as<float>(),
+                                        d_version_.as<int64_t>(), cur.batch_size, cur.pos_row.as<int32_t>(),
+                                        cur.idx_map.as<int32_t>(), dst_dev, stream_main_));
+    toc(sp);
+  } else {
+    sp = tic(kPhRefresh);
+    HCTR_LAUNCH(hctr_p2p_refresh_index(c, seq, meta, u_max, cur.uniq_owner.as<uint8_t>(), cur.uniq_row.as<int32_t>(),
+                                       kNonLocalStorageMax, d_gradient_.as<float>(), d_embedding_.as<float>(),
+                                       d_version_.as<int64_t>(), d_flag_r_.as<uint8_t>(), d_recv_idx_.as<uint32_t>(),
+                                       stream_main_));
+    toc(sp);
+    sp = tic(kPhExpand);
+    HCTR_LAUNCH(expandRows(cur.batch_size, W, cur.pos_row.as<int32_t>(), cur.idx_map.as<int32_t>(),
+                           d_recv_idx_.as<uint32_t>(), mine.rval, d_embedding_.as<float>(), dst_dev,
+                           d_ingest_err_ + 1, stream_main_));
+    toc(sp);
+  }
 
   // counts, wait times and the error word come back with the step's final synchronisation
   uint32_t *h_cnt = h_pinned_ + HCTR_META_WORDS + n + 1 + 4 * n;  // [5n+7] + [n] push counts + error word

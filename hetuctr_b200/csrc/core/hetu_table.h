@@ -204,6 +204,7 @@ class HetuTable {
   cudaEvent_t ev_fork_ = nullptr, ev_join_ = nullptr, ev_keys_ = nullptr;
   cudaEvent_t ev_early_ = nullptr;   // end of the gradient-independent half of a split row expansion
   bool split_host_expand_ = true;    // HCTR_SPLIT_HOST_EXPAND=0 switches the split off
+  bool fused_refresh_expand_ = true; // HCTR_P2P_FUSED_EXPAND=0: cache refresh and row expansion as two launches
   std::unique_ptr<Transport> transport_;
   std::unique_ptr<P2PMailbox> p2p_;  // device-driven exchange (one process per GPU, peer access); else NCCL groups
   bool use_p2p_ = false;

@@ -198,6 +198,143 @@ __global__ void __launch_bounds__(kPullThreads) p2p_refresh_index(hctr_p2p_ctx c
   if (threadIdx.x == 0 && s_flagged) atomicAdd(c.cnt_in + 2 * c.nrank, s_flagged);
 }
 
+// Requester, everything after the owners' answers in ONE launch: the cache refresh of p2p_refresh_index and the row
+// expansion (writeBack, csrc/core/writeback.cu:8-71) without the per-key flag / row-index arrays between them.
+// Every block waits (bounded) for the owners' phase-1 release, then takes a share of the unique keys (refresh of the
+// flagged cached rows, as above) and a share of the batch positions.  A position's row comes from
+//   the table            when the key is owned here, or cached and not flagged,
+//   the mailbox          when the key is not stored here (row owner * cap + j, j = its place among the keys sent there),
+//   mailbox + pending    when the key is cached and flagged - the same sum the refresh stores into the cache row,
+//                        computed again here so that no block has to wait for the block that refreshes that row.
+// The refresh writes only flagged cached rows, which the expansion never reads: the two parts are independent.
+constexpr int kFusedRows = 4;  // rows per lane group and iteration, as in the plain expansion
+constexpr int kFusedThreads = 256;  // >= kMaxRanks: thread s of every block polls owner s
+
+template <int LANES, bool VEC>
+__global__ void __launch_bounds__(kFusedThreads) p2p_refresh_expand(hctr_p2p_ctx c, u32 seq, const u32 *__restrict__ meta,
+                                                               const uint8_t *__restrict__ uniq_owner,
+                                                               const int32_t *__restrict__ uniq_row, size_t n_cached,
+                                                               const float *__restrict__ pending,
+                                                               float *__restrict__ embedding,
+                                                               long long *__restrict__ version, size_t batch,
+                                                               const int32_t *__restrict__ pos_row,
+                                                               const int32_t *__restrict__ idx_map,
+                                                               float *__restrict__ dst) {
+  typedef RowT<VEC> R;
+  typedef typename R::T T;
+  __shared__ u32 ret_base[kMaxRanks + 1];
+  __shared__ u32 seg[kMaxRanks + 1];
+  __shared__ u32 s_flagged, s_n;
+  __shared__ u32 s_idx[kFusedThreads], s_row[kFusedThreads];
+  if (threadIdx.x == 0) s_flagged = s_n = 0;
+  for (int i = threadIdx.x; i <= c.nrank; i += kFusedThreads) seg[i] = meta[HCTR_META_SEG + i];
+  wait_returns(c, seq, ret_base, false, blockIdx.x == 0);  // (ends with a block barrier)
+  const size_t U = meta[HCTR_META_UNIQUE];
+  const unsigned lane = threadIdx.x & 31;
+  const u32 E = (u32)R::elems(c.width);
+  const hctr_p2p_box me = c.box[c.rank];
+  const T *rval = reinterpret_cast<const T *>(me.rval);
+
+  // refresh of the flagged cached rows: the block looks at kFusedThreads unique keys at a time, one per thread, lists
+  // the rows to refresh in shared memory and then shares them out evenly among its lane groups (a few rows per
+  // block: spread over the whole block they cost one round of loads, left to the warp that found them, several)
+  {
+    const unsigned n_groups = kFusedThreads / LANES, group = threadIdx.x / LANES, gl = threadIdx.x % LANES;
+    u32 flagged = 0;
+    for (size_t base = (size_t)blockIdx.x * kFusedThreads; base < U; base += (size_t)gridDim.x * kFusedThreads) {
+      const size_t u = base + threadIdx.x;
+      bool f = false;
+      if (u < U) {
+        const unsigned p = uniq_owner[u];
+        const u32 j = (u32)u - seg[p];
+        if (j < c.cap) {  // (a larger j was reported when the query was sent)
+          const u32 idx = p * c.cap + j;
+          f = me.flag[idx] != 0;
+          const int32_t row = uniq_row[u];
+          if (f && row >= 0 && (size_t)row < n_cached) {
+            version[row] = reinterpret_cast<const long long *>(me.rver)[idx];
+            const u32 e = atomicAdd(&s_n, 1u);
+            s_idx[e] = idx;
+            s_row[e] = (u32)row;
+          }
+        }
+      }
+      flagged += f ? 1u : 0u;
+      __syncthreads();
+      const u32 n = s_n;
+      for (u32 e0 = group * kFusedRows; e0 < n; e0 += n_groups * kFusedRows) {
+        for (u32 col = gl; col < E; col += LANES) {
+          T v[kFusedRows], w[kFusedRows];
+#pragma unroll
+          for (int k = 0; k < kFusedRows; k++)
+            if (e0 + k < n) {
+              v[k] = rval[(size_t)s_idx[e0 + k] * E + col];
+              w[k] = reinterpret_cast<const T *>(pending)[(size_t)s_row[e0 + k] * E + col];
+            }
+#pragma unroll
+          for (int k = 0; k < kFusedRows; k++)
+            if (e0 + k < n) reinterpret_cast<T *>(embedding)[(size_t)s_row[e0 + k] * E + col] = R::add(v[k], w[k]);
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) s_n = 0;
+      // (the next round's first barrier orders this store before the next list is read; its appends come after the
+      // barrier below)
+      __syncthreads();
+    }
+    flagged = __reduce_add_sync(0xffffffffu, flagged);
+    if (lane == 0 && flagged) atomicAdd(&s_flagged, flagged);
+  }
+
+  // expansion: a group of LANES lanes takes kFusedRows positions per iteration
+  const size_t groups = ((size_t)gridDim.x * kFusedThreads) / LANES;
+  const unsigned gl = threadIdx.x % LANES;
+  for (size_t i0 = (((size_t)blockIdx.x * kFusedThreads + threadIdx.x) / LANES) * kFusedRows; i0 < batch;
+       i0 += groups * kFusedRows) {
+    const T *src[kFusedRows], *add[kFusedRows];
+#pragma unroll
+    for (int k = 0; k < kFusedRows; k++) {
+      src[k] = nullptr;
+      add[k] = nullptr;
+      const size_t i = i0 + k;
+      if (i < batch) {
+        const int32_t row = pos_row[i];
+        if (row >= 0 && (size_t)row >= n_cached) {
+          src[k] = reinterpret_cast<const T *>(embedding) + (size_t)row * E;
+        } else {
+          const int32_t u = idx_map[i];  // < 0: key was out of range (the host reports it); write zeros
+          if (u >= 0) {
+            const unsigned p = uniq_owner[u];
+            const u32 j = (u32)u - seg[p];
+            const u32 idx = j < c.cap ? p * c.cap + j : 0u;
+            if (row < 0) {
+              src[k] = rval + (size_t)idx * E;
+            } else if (j < c.cap && me.flag[idx] != 0) {
+              src[k] = rval + (size_t)idx * E;
+              add[k] = reinterpret_cast<const T *>(pending) + (size_t)row * E;
+            } else {
+              src[k] = reinterpret_cast<const T *>(embedding) + (size_t)row * E;
+            }
+          }
+        }
+      }
+    }
+    for (size_t col = gl; col < E; col += LANES) {
+      T v[kFusedRows];
+#pragma unroll
+      for (int k = 0; k < kFusedRows; k++) {
+        v[k] = src[k] ? src[k][col] : R::zero();
+        if (add[k]) v[k] = R::add(v[k], add[k][col]);
+      }
+#pragma unroll
+      for (int k = 0; k < kFusedRows; k++)
+        if (i0 + k < batch) R::st_once(reinterpret_cast<T *>(dst) + (i0 + k) * E + col, v[k]);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && s_flagged) atomicAdd(c.cnt_in + 2 * c.nrank, s_flagged);
+}
+
 }  // namespace hctr
 
 using namespace hctr;
@@ -240,6 +377,31 @@ extern "C" int hctr_p2p_refresh_index(const hctr_p2p_ctx *c, uint32_t seq, const
     p2p_refresh_index<false><<<(unsigned)g, kPullThreads, 0, st>>>(*c, seq, meta, uniq_owner, uniq_row, n_cached,
                                                                    pending, embedding, (long long *)version, flags,
                                                                    recv_index);
+  count_launches(1);
+  return launch_status();
+}
+
+extern "C" int hctr_p2p_refresh_expand(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *meta,
+                                       const uint8_t *uniq_owner, const int32_t *uniq_row, size_t n_cached,
+                                       const float *pending, float *embedding, int64_t *version, size_t batch,
+                                       const int32_t *pos_row, const int32_t *idx_map, float *dst, void *stream) {
+  cudaStream_t st = (cudaStream_t)stream;
+  if (c->nrank > kMaxRanks) return (int)cudaErrorInvalidValue;
+  const size_t width = c->width;
+  // (the mailbox arrays are device allocations of their own: aligned; c->box is a device array)
+  const bool al = host_aligned16(embedding) && host_aligned16(pending) && host_aligned16(dst);
+#define CALL(L, V)                                                                                         \
+  do {                                                                                                     \
+    size_t g_ = (((size_t)batch + kFusedRows - 1) / kFusedRows * L + kFusedThreads - 1) / kFusedThreads;              \
+    const size_t cap_ = (size_t)kSMs * 3; /* one resident round; every block starts by polling the headers */ \
+    if (g_ > cap_) g_ = cap_;                                                                              \
+    if (g_ == 0) g_ = 1; /* an empty batch still waits for the peers: the step's protocol */               \
+    p2p_refresh_expand<L, V><<<(unsigned)g_, kFusedThreads, 0, st>>>(*c, seq, meta, uniq_owner, uniq_row, n_cached, \
+                                                                pending, embedding, (long long *)version, batch, \
+                                                                pos_row, idx_map, dst);                    \
+  } while (0)
+  HCTR_DISPATCH_ROWS(width, al, CALL);
+#undef CALL
   count_launches(1);
   return launch_status();
 }

@@ -342,6 +342,16 @@ int hctr_p2p_refresh_index(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *
                            const uint8_t *uniq_owner, const int32_t *uniq_row, size_t n_cached, const float *pending,
                            float *embedding, int64_t *version, uint8_t *flags, uint32_t *recv_index, void *stream);
 
+/* hctr_p2p_refresh_index followed by hctr_expand_rows as ONE launch, without the flag / row-index arrays between
+ * them: after the (bounded) wait for the owners' phase-1 release the kernel refreshes the flagged cached rows and
+ * writes dst[i] for every batch position - from the table (key owned, or cached and not flagged), from the mailbox
+ * (key not stored here) or as mailbox row + pending row (key cached and flagged: the value the refresh stores).
+ * Replaces update_cache_kernel, the scan and write_back_kernel of csrc/core/writeback.cu:8-71. */
+int hctr_p2p_refresh_expand(const hctr_p2p_ctx *c, uint32_t seq, const uint32_t *meta, const uint8_t *uniq_owner,
+                            const int32_t *uniq_row, size_t n_cached, const float *pending, float *embedding,
+                            int64_t *version, size_t batch, const int32_t *pos_row, const int32_t *idx_map,
+                            float *dst, void *stream);
+
 typedef struct hctr_reduce_args {
   size_t n_unique;            /* U of the previous batch (host value) */
   size_t width;               /* W */

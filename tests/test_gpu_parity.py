@@ -212,6 +212,24 @@ def test_multi_rank_parity(oracle_mod, nrank, pull, push, frac, exchange):
     gw.close()
 
 
+@pytest.mark.parametrize("knob", ["HCTR_P2P_FUSED_EXPAND=0", "HCTR_EXPAND=bulk"])
+def test_mailbox_exchange_with_refresh_and_expansion_as_two_launches(oracle_mod, monkeypatch, knob):
+    # the requester side of the mailbox exchange is one launch by default; the two-launch form (flag / row-index
+    # arrays, then the plain or the bulk-copy expansion) stays selectable and must give the same step
+    name, value = knob.split("=")
+    monkeypatch.setenv(name, value)
+    nrank, N, W, B = 4, 3000, 32, 700
+    rng = np.random.RandomState(77)
+    root = rng.randint(nrank, size=N).astype(np.uint8)
+    storage = _hybrid_storage(root, nrank, rng, 0.3)
+    gw, ow = make_worlds(oracle_mod, nrank, N, W, 1, 2, 0.1, root, storage, exchange="p2p")
+    batches = [[(rng.zipf(1.2, size=B) - 1) % N for _ in range(nrank)] for _ in range(5)]
+    grads = [None] + [[rng.normal(0, 1, size=(len(k), W)).astype(np.float32) for k in batches[s - 1]]
+                      for s in range(1, 5)]
+    run_steps(gw, ow, batches, grads)
+    gw.close()
+
+
 @pytest.mark.parametrize("width", [128, 132, 256, 260, 512, 640])
 @pytest.mark.parametrize("exchange", EXCHANGES)
 def test_multi_rank_wide_rows(oracle_mod, width, exchange):
