@@ -307,6 +307,18 @@ def run_ours(args):
             for ph, a, b in spans:
                 print(f"timeline {ph:13s} {1e3 * (a - t_first):8.1f} -> {1e3 * (b - t_first):8.1f} us ({1e3 * (b - a):6.1f})",
                       file=sys.stderr)
+        # the same with host buffers: where the two transfers over the host link and the kernels between them lie
+        table.profile(1)
+        for i in range(3):
+            step(i, host=True)
+        barrier()
+        spans = table.timeline()
+        table.profile(0)
+        if rank == 0 and spans:
+            t_first = spans[0][1]
+            for ph, a, b in spans:
+                print(f"timeline(host buffers) {ph:13s} {1e3 * (a - t_first):8.1f} -> {1e3 * (b - t_first):8.1f} us "
+                      f"({1e3 * (b - a):6.1f})", file=sys.stderr)
 
     t = torch.tensor([ms, e2e_ms], dtype=torch.float64, device=dev)
     if world > 1:
