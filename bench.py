@@ -340,7 +340,13 @@ def run_ours(args):
         # the row-moving kernels; the dominant one (longest launch) is the line's `roofline`, all of them (and the
         # latency-bound dedupe pipeline, whose working set lives in L2) are listed under `roofline_phases`
         kernels = {"reduce": "grad_reduce_apply_pack", "expand": "expand_rows", "owner_update": "owner_mark + owner_apply",
-                   "stale_gather": "p2p_stale_scan + p2p_gather", "dedupe": "dedupe pipeline (5 launches)"}
+                   "stale_gather": "p2p_stale_gather", "dedupe": "dedupe pipeline (5 launches)"}
+        if world > 1 and per_phase.get("expand", 0.0) > 0 and per_phase.get("refresh", 0.0) == 0:
+            # requester side of the mailbox exchange as one launch: the expansion plus the per-key flag look-ups of
+            # the cache refresh (the refreshed rows themselves, 3D each, are not counted: their number stays on the
+            # device)
+            kernels["expand"] = "p2p_refresh_expand"
+            alg["expand"] += 14 * stats["unique"]
         # the owner's row pass runs on a second stream next to the staleness scan: charge it to owner_update
         per_phase["owner_update"] = per_phase.get("owner_update", 0.0) + per_phase.get("owner_apply", 0.0)
         gather_only_ms = per_phase.get("stale_gather", 0.0)  # the peer-to-peer exchange times scan and gather apart
