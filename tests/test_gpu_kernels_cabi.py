@@ -133,6 +133,47 @@ def test_expand_launchers_agree(width, batch):
         assert np.array_equal(dst.cpu().numpy(), exp), f"bulk={bulk}"
 
 
+@pytest.mark.parametrize("width", [128, 32, 6])
+@pytest.mark.parametrize("in_host_memory", [False, True])
+def test_expand_subset_halves_cover_every_position_once(width, in_host_memory):
+    """hctr_expand_rows_subset: the positions whose key is / is not among the previous batch's unique keys.  Each half
+    writes exactly its own rows (the others keep the fill value), together they equal the plain expansion; dst may
+    be pinned host memory."""
+    L = hb.lib()
+    L.hctr_expand_rows_subset.argtypes = [sz, sz, vp, vp, vp, vp, ctypes.c_int, vp, vp, vp]
+    dev = torch.device("cuda:0")
+    rng = np.random.RandomState(width)
+    n_rows, batch = 4000, 5000
+    keys = rng.randint(n_rows, size=batch).astype(np.int64)
+    prev_uniq = np.unique(rng.randint(n_rows, size=1500)).astype(np.int64)  # ascending
+    pos_row = keys.astype(np.int32)  # single rank: row = key here
+    pos_row[7] = -1  # a position without a row gets zeros from the half that owns it
+    emb = rng.normal(size=(n_rows, width)).astype(np.float32)
+    meta = np.zeros(8, dtype=np.uint32)
+    meta[0] = len(prev_uniq)
+    # more entries behind the announced count must be ignored
+    padded = np.concatenate([prev_uniq, np.full(64, n_rows + 5, dtype=np.int64)])
+    t = lambda a: torch.from_numpy(a).to(dev)  # noqa: E731
+    d_keys, d_prev, d_pos, d_emb, d_meta = t(keys), t(padded), t(pos_row), t(emb), t(meta)
+    in_prev = np.isin(keys, prev_uniq)
+    want = emb[keys]
+    want[7] = 0.0
+    fill = np.float32(-7.5)
+    outs = []
+    for half in (0, 1):
+        dst = torch.full((batch, width), float(fill))
+        dst = dst.pin_memory() if in_host_memory else dst.to(dev)
+        assert L.hctr_expand_rows_subset(batch, width, d_pos.data_ptr(), d_keys.data_ptr(), d_prev.data_ptr(),
+                                         d_meta.data_ptr(), half, d_emb.data_ptr(), dst.data_ptr(), None) == 0
+        torch.cuda.synchronize()
+        got = dst.cpu().numpy()
+        mine = in_prev == bool(half)
+        assert np.array_equal(got[mine], want[mine])
+        assert np.all(got[~mine] == fill)
+        outs.append((mine, got))
+    assert np.all(outs[0][0] ^ outs[1][0])
+
+
 def test_ingest_keys_and_deferred_ordering():
     """hctr_ingest_keys (copy + cleared meta in one launch) and the split pipeline: hctr_dedupe_map without the
     run ordering (fork event only), hctr_dedupe_order later on another stream."""
