@@ -519,9 +519,13 @@ def run_reference(args):
                           init_kind=1, init_a=0.0, init_b=c["init_std"], learning_rate=c["lr"], verbose=0)
     grad = (np.random.RandomState(1234 + rank).standard_normal((B, W)) * 0.01).astype(np.float32)
     steps, warmup = args.steps, max(args.warmup, 3)
+    clocks = ClockSampler(local) if rank == 0 else None
+    if clocks:
+        clocks.start()
     ms = table.bench_loop(batches, grad, steps, warmup, False)
     e2e_steps = max(3, min(args.e2e_steps, steps))
     e2e_ms = table.bench_loop(batches, grad, e2e_steps, 2, True)
+    clk = clocks.stop() if clocks else None
     del table
     # max over ranks through a scratch directory (no collective library in these processes)
     tag = os.environ.get("MASTER_PORT", "0")
@@ -558,7 +562,8 @@ def run_reference(args):
                                        f"(one driving host thread per rank; the reference has no CPU path)"},
             "e2e": {"value": world * B * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
                     "h2d_bytes_per_step": B * 8 + B * W * 4, "d2h_bytes_per_step": B * W * 4,
-                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps, "host_binding": binding}}
+                    "ms_per_step": e2e_ms / e2e_steps, "steps": e2e_steps, "host_binding": binding},
+            "clocks": clk}
 
 
 def main():
