@@ -393,7 +393,7 @@ extern "C" int hctr_p2p_refresh_expand(const hctr_p2p_ctx *c, uint32_t seq, cons
 #define CALL(L, V)                                                                                         \
   do {                                                                                                     \
     size_t g_ = (((size_t)batch + kFusedRows - 1) / kFusedRows * L + kFusedThreads - 1) / kFusedThreads;              \
-    const size_t cap_ = (size_t)kSMs * 3; /* one resident round; every block starts by polling the headers */ \
+    const size_t cap_ = (size_t)kSMs * 4; /* one resident round (64 registers); every block polls the headers */ \
     if (g_ > cap_) g_ = cap_;                                                                              \
     if (g_ == 0) g_ = 1; /* an empty batch still waits for the peers: the step's protocol */               \
     p2p_refresh_expand<L, V><<<(unsigned)g_, kFusedThreads, 0, st>>>(*c, seq, meta, uniq_owner, uniq_row, n_cached, \

@@ -174,6 +174,18 @@ def test_expand_subset_halves_cover_every_position_once(width, in_host_memory):
     assert np.all(outs[0][0] ^ outs[1][0])
 
 
+@pytest.mark.parametrize("ranks,width", [(4, 128), (2, 32), (8, 6), (3, 260)])
+def test_requester_side_kernel_on_synthetic_mailbox(ranks, width):
+    """hctr_p2p_refresh_expand on one rank's synthetic state (owned, cached and not-stored keys, a mailbox filled as
+    the owners would): pulled rows, refreshed cache rows, versions and the flagged count against numpy."""
+    from hetuctr_b200.requester_replay import RequesterReplay
+
+    r = RequesterReplay(ranks=ranks, batch=6000, unique=2500, width=width, owned_rows=5000, seed=ranks + width)
+    assert r.check()
+    pos = r.h["pos_row"]
+    assert (pos >= r.C).any() and ((pos >= 0) & (pos < r.C)).any() and (pos < 0).any()
+
+
 def test_ingest_keys_and_deferred_ordering():
     """hctr_ingest_keys (copy + cleared meta in one launch) and the split pipeline: hctr_dedupe_map without the
     run ordering (fork event only), hctr_dedupe_order later on another stream."""
